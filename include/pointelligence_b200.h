@@ -1,0 +1,191 @@
+/*
+ * C ABI of libpointelligence_b200.so -- the sm_100a implementation of the
+ * point-convolution hot path (sparse engines + geometry stage).
+ *
+ * Conventions
+ *   - every pointer argument named d_* is a DEVICE pointer on the current
+ *     CUDA device; h_* is a HOST pointer.  Nothing is retained after a call.
+ *   - the library allocates no device memory: outputs and scratch ("workspace")
+ *     are owned by the caller; each *_workspace_bytes() function returns the
+ *     scratch size the matching call needs.  Workspaces must be 256-byte
+ *     aligned.
+ *   - all work is enqueued on `stream` (a cudaStream_t passed as void*).
+ *     Calls that have to return a data-dependent count to the host
+ *     (pcx_radius_count, pcx_grid_sample_count) synchronise that stream once.
+ *   - every function returns PCX_OK (0) or a negative pcx_status; it never
+ *     throws and never terminates the process.  pcx_last_error_string() gives
+ *     the message of the last failure on the calling thread.
+ *   - feature rows are dense row-major; indices are int32; tap segment
+ *     offsets are int64 (K+1 entries, seg[K] == T).
+ *
+ * Each entry point cites the reference interface it stands in for (paths are
+ * relative to the reference project's root).
+ */
+#ifndef POINTELLIGENCE_B200_H
+#define POINTELLIGENCE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    PCX_OK = 0,
+    PCX_E_ARG = -1,         /* null pointer, negative size, bad enum          */
+    PCX_E_DTYPE = -2,       /* unsupported element type                        */
+    PCX_E_ALIGN = -3,       /* pointer / leading dimension not aligned         */
+    PCX_E_CAPACITY = -4,    /* workspace or output buffer too small            */
+    PCX_E_LAUNCH = -5,      /* CUDA runtime reported an error                  */
+    PCX_E_UNSUPPORTED = -6, /* shape outside what this build implements        */
+    PCX_E_DEVICE = -7       /* a kernel reported a bounded wait that ran out   */
+} pcx_status;
+
+typedef enum { PCX_F32 = 0, PCX_F16 = 1, PCX_BF16 = 2 } pcx_dtype;
+
+/* engine selector for the sparse primitives */
+typedef enum {
+    PCX_ENGINE_AUTO = 0,    /* tcgen05 tensor-core path when the shape allows  */
+    PCX_ENGINE_CUDA_CORE = 1, /* fp32 FMA path (any shape, IEEE fp32)          */
+    PCX_ENGINE_TENSOR = 2   /* tcgen05 path or PCX_E_UNSUPPORTED               */
+} pcx_engine;
+
+int pcx_version(void);
+const char *pcx_last_error_string(void);
+
+/* Device-side status word: kernels that give up on a bounded wait set a bit
+ * (1 = MVMR tensor kernel, 2 = VVOR tensor kernel).  Synchronises `stream`,
+ * copies the word to *h_status and clears it when `clear` is non-zero.
+ * No counterpart in the reference (its kernels have no device-side waits). */
+int pcx_device_status(unsigned int *h_status, int clear, void *stream);
+
+/* ------------------------------------------------------------------------
+ * MVMR:  out[scatter[t], g, :] += feat[gather[t], g, :] @ W[tap(t), g]
+ *
+ * Replaces sparse_engines/tig.py:1090-1206 (tig_forward), :1220-1309
+ * (tig_grad_input) and the public operator sparse_engines/mvmr_triton.py:148-254
+ * (extensions/sparse_engines_cuda/csrc/definitions.cpp:24 on the native side).
+ *
+ *   d_weight   (K, G, C, M) elements of `dtype`
+ *   transpose  0: feat rows have C channels, out rows M   (forward)
+ *              1: feat rows have M channels, out rows C, W used transposed
+ *                 (input gradient; same triplets with gather/scatter swapped)
+ *   d_feat     (n_feat, G*in_width)   d_out (n_out, G*out_width), `dtype`
+ *   d_gather / d_scatter  (T) int32 row indices into feat / out
+ *   d_seg_offs (K+1) int64 tap segment offsets of tap-sorted triplets, or NULL
+ *   d_tap_idx  (T) int32 tap per triplet; required when d_seg_offs is NULL
+ *              (then any order is accepted), ignored otherwise
+ *   d_ws       workspace of pcx_mvmr_workspace_bytes(); holds the fp32
+ *              accumulator that is rounded once into d_out
+ * Rows of out that no triplet touches are written as zero.
+ */
+size_t pcx_mvmr_workspace_bytes(int64_t n_out, int K, int G, int C, int M,
+                                int transpose, int dtype);
+int pcx_mvmr(const void *d_weight, const void *d_feat, const int32_t *d_gather,
+             const int32_t *d_scatter, const int64_t *d_seg_offs,
+             const int32_t *d_tap_idx, void *d_out, int64_t T, int64_t n_feat,
+             int64_t n_out, int K, int G, int C, int M, int transpose,
+             int dtype, int engine, void *d_ws, size_t ws_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
+ * VVOR:  out[o[t], g, m, c] += a[ai[t], g, m] * b[bi[t], g, c]
+ *
+ * Replaces sparse_engines/tig.py:1390-1465 (tig_grad_weight, with a = input
+ * features, b = output gradient, o = tap -> dW (K,G,C_in,C_out)) and the
+ * public operator sparse_engines/vvor_triton.py:116-223
+ * (definitions.cpp:25 on the native side).
+ *
+ *   d_a (n_a, G*Ma)  d_b (n_b, G*Cb)  d_out (n_o, G, Ma, Cb), all `dtype`
+ *   d_seg_offs (n_o+1) int64 when the triplets are sorted by o, else NULL and
+ *   d_o_idx (T) int32 gives o per triplet.
+ */
+size_t pcx_vvor_workspace_bytes(int64_t n_o, int G, int Ma, int Cb, int dtype);
+int pcx_vvor(const void *d_a, const int32_t *d_a_idx, const void *d_b,
+             const int32_t *d_b_idx, const int64_t *d_seg_offs,
+             const int32_t *d_o_idx, void *d_out, int64_t T, int64_t n_a,
+             int64_t n_b, int64_t n_o, int G, int Ma, int Cb, int dtype,
+             int engine, void *d_ws, size_t ws_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Tap bookkeeping.
+ * pcx_seg_offs: seg[k] = first position with value >= k in a sorted int32
+ *   array (sparse_engines/_seg_offs.py:21-44, kernel_offset_segments).
+ * pcx_expand_taps: k[t] = tap of position t, from segment offsets
+ *   (layers/triplets.py:673-676, the repeat_interleave that materialises k).
+ */
+int pcx_seg_offs(const int32_t *d_sorted, int64_t T, int K, int64_t *d_seg_offs,
+                 void *stream);
+int pcx_expand_taps(const int64_t *d_seg_offs, int K, int64_t T, int32_t *d_k,
+                    void *stream);
+
+/* ------------------------------------------------------------------------
+ * Exact fixed-radius search on a sorted grid of cell side 2R, optionally
+ * emitting the accepted pairs grouped by kernel tap.
+ *
+ * Replaces internals/neighbors.py:469-838 (radius_search_strided_grid in
+ * "exact8" mode; entry points radius_search_sorted_grid8 :886-916 and
+ * radius_search_sorted_grid8_segments :919-955) together with the kernels of
+ * sparse_engines/strided_grid_radius_triton_kernel.py:35-248.
+ *
+ * Two calls bracket the one device-to-host hand-over of the edge count:
+ *
+ *   pcx_radius_count  builds the sorted grid, evaluates the predicate for
+ *       every (query, candidate) pair and returns the number of accepted
+ *       pairs in *h_total.  d_num_neighbors (Q) int64 is final after this.
+ *       With kernel_size > 0 it also writes d_seg_offs (kernel_size^3+1).
+ *   pcx_radius_fill   writes the pairs.  kernel_size == 0: d_neighbors (E)
+ *       int64 query-major (+ d_distances (E) fp32 when not NULL).
+ *       kernel_size > 0: d_out_i / d_out_j (E) int32 grouped by tap, inside a
+ *       tap ordered by query; d_out_k (E) int32 optional.
+ *
+ *   d_points (P,3) / d_queries (Q,3) fp32; d_point_sample / d_query_sample
+ *   int32 sample id per row or both NULL; distance_type 0 = ball, 1 = Chebyshev.
+ *   d_ws must stay untouched between the two calls (workspace of
+ *   pcx_radius_workspace_bytes); d_ws2 is the fill-only scratch of
+ *   pcx_radius_fill_workspace_bytes(total).
+ */
+size_t pcx_radius_workspace_bytes(int64_t P, int64_t Q, int kernel_size);
+size_t pcx_radius_fill_workspace_bytes(int64_t total, int kernel_size);
+int pcx_radius_count(const float *d_points, const float *d_queries,
+                     const int32_t *d_point_sample, const int32_t *d_query_sample,
+                     int64_t P, int64_t Q, double radius, int distance_type,
+                     int kernel_size, double kernel_grid_size,
+                     int64_t *d_num_neighbors, int64_t *d_seg_offs,
+                     int64_t *h_total, void *d_ws, size_t ws_bytes, void *stream);
+int pcx_radius_fill(const float *d_points, const float *d_queries, int64_t P,
+                    int64_t Q, double radius, int distance_type, int kernel_size,
+                    double kernel_grid_size, int64_t total, int64_t *d_neighbors,
+                    float *d_distances, int32_t *d_out_i, int32_t *d_out_j,
+                    int32_t *d_out_k, void *d_ws, size_t ws_bytes, void *d_ws2,
+                    size_t ws2_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Centre-nearest grid down-sampling: one observed point per occupied cell of
+ * side `cell`, the one nearest the cell centre (ties: lowest index), cells in
+ * ascending (sample, z, y, x) order.
+ *
+ * Replaces internals/grid_sample.py:42-121 (grid_sample_filter,
+ * reduction="center_nearest"), internals/grid_indexing.py:20-111 and
+ * internals/grid_sample_triton_kernel.py:55-151.
+ *
+ *   pcx_grid_sample_count   bins and sorts the points, returns the number of
+ *       occupied cells in *h_num_cells.
+ *   pcx_grid_sample_select  writes d_indices (S) int64, d_out_points (S,3),
+ *       d_out_sample (S) int32 (may be NULL) and, when not NULL, d_mapping (N)
+ *       int64 = cell ordinal of every input point.
+ */
+size_t pcx_grid_sample_workspace_bytes(int64_t N);
+int pcx_grid_sample_count(const float *d_points, const int32_t *d_sample,
+                          int64_t N, double cell, int64_t *h_num_cells,
+                          void *d_ws, size_t ws_bytes, void *stream);
+int pcx_grid_sample_select(const float *d_points, const int32_t *d_sample,
+                           int64_t N, double cell, int64_t num_cells,
+                           int64_t *d_indices, float *d_out_points,
+                           int32_t *d_out_sample, int64_t *d_mapping,
+                           void *d_ws, size_t ws_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POINTELLIGENCE_B200_H */

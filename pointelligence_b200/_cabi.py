@@ -1,0 +1,260 @@
+"""ctypes binding of ``libpointelligence_b200.so`` (see
+``include/pointelligence_b200.h``) and the marshalling helpers used by the
+host-side mirrors of the reference modules.
+
+The library is mandatory: if it cannot be loaded every operator raises
+``RuntimeError`` -- there is no CPU or PyTorch fallback.  Tensors are passed as
+raw device pointers; outputs and workspaces are allocated here with PyTorch so
+the caching allocator and the caller's current stream stay in charge.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_double, c_int, c_int64, c_size_t, c_void_p
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libpointelligence_b200.so")
+
+PCX_F32, PCX_F16, PCX_BF16 = 0, 1, 2
+ENGINE_AUTO, ENGINE_CUDA_CORE, ENGINE_TENSOR = 0, 1, 2
+
+_DTYPES = {torch.float32: PCX_F32, torch.float16: PCX_F16, torch.bfloat16: PCX_BF16}
+
+_STATUS_EXC = {
+    -1: ValueError,          # PCX_E_ARG
+    -2: TypeError,           # PCX_E_DTYPE
+    -3: ValueError,          # PCX_E_ALIGN
+    -4: RuntimeError,        # PCX_E_CAPACITY
+    -5: RuntimeError,        # PCX_E_LAUNCH
+    -6: NotImplementedError, # PCX_E_UNSUPPORTED
+    -7: RuntimeError,        # PCX_E_DEVICE
+}
+
+# name -> (restype, argtypes); every symbol declared in the header
+SIGNATURES = {
+    "pcx_version": (c_int, []),
+    "pcx_last_error_string": (ctypes.c_char_p, []),
+    "pcx_device_status": (c_int, [c_void_p, c_int, c_void_p]),
+    "pcx_mvmr_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "pcx_mvmr": (c_int, [c_void_p] * 7 + [c_int64] * 3 + [c_int] * 7 + [c_void_p, c_size_t, c_void_p]),
+    "pcx_vvor_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
+    "pcx_vvor": (c_int, [c_void_p] * 7 + [c_int64] * 4 + [c_int] * 5 + [c_void_p, c_size_t, c_void_p]),
+    "pcx_seg_offs": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
+    "pcx_expand_taps": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
+    "pcx_radius_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),
+    "pcx_radius_fill_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "pcx_radius_count": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_double, c_int, c_int, c_double]
+                         + [c_void_p] * 3 + [c_void_p, c_size_t, c_void_p]),
+    "pcx_radius_fill": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_int, c_double,
+                                c_int64] + [c_void_p] * 5 + [c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
+    "pcx_grid_sample_workspace_bytes": (c_size_t, [c_int64]),
+    "pcx_grid_sample_count": (c_int, [c_void_p, c_void_p, c_int64, c_double, c_void_p, c_void_p, c_size_t,
+                                      c_void_p]),
+    "pcx_grid_sample_select": (c_int, [c_void_p, c_void_p, c_int64, c_double, c_int64] + [c_void_p] * 4
+                               + [c_void_p, c_size_t, c_void_p]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m pointelligence_b200.build` "
+                "(the operators have no fallback implementation)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc):
+    if rc == 0:
+        return
+    msg = lib().pcx_last_error_string().decode("utf-8", "replace")
+    raise _STATUS_EXC.get(rc, RuntimeError)(f"{msg} [pcx status {rc}]")
+
+
+def dtype_code(dtype):
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise TypeError(f"unsupported feature dtype {dtype}; expected float32, float16 or bfloat16")
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "pointelligence_b200 operators run on CUDA tensors only (no CPU fallback); "
+                f"got a tensor on {t.device}")
+
+
+def ptr(t):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def stream_ptr():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def as_i32(t):
+    if t is None:
+        return None
+    return t.contiguous() if t.dtype == torch.int32 else t.to(torch.int32).contiguous()
+
+
+def device_status(clear=True):
+    """Status word set by kernels whose bounded waits ran out (0 = healthy)."""
+    out = ctypes.c_uint(0)
+    check(lib().pcx_device_status(ctypes.byref(out), 1 if clear else 0, stream_ptr()))
+    return int(out.value)
+
+
+# ---------------------------------------------------------------- sparse ----
+def mvmr(weight, feat, gather, scatter, seg_offs, tap_idx, n_out, transpose, engine=ENGINE_AUTO):
+    """``out[scatter[t]] += feat[gather[t]] @ W[tap(t)]`` (``transpose``: use W^T).
+
+    weight (K,G,C,M); feat (n_feat, G*inw); returns (n_out, G*outw) in feat.dtype.
+    """
+    require_cuda(weight, feat, gather, scatter, seg_offs, tap_idx)
+    K, G, C, M = weight.shape
+    code = dtype_code(feat.dtype)
+    assert weight.dtype == feat.dtype, (weight.dtype, feat.dtype)
+    weight, feat = weight.contiguous(), feat.contiguous()
+    gather, scatter, tap_idx = as_i32(gather), as_i32(scatter), as_i32(tap_idx)
+    if seg_offs is not None:
+        seg_offs = seg_offs.to(torch.int64).contiguous()
+    outw = C if transpose else M
+    n_out = int(n_out)
+    out = torch.empty((n_out, G * outw), dtype=feat.dtype, device=feat.device)
+    L = lib()
+    with torch.cuda.device(feat.device):
+        nbytes = L.pcx_mvmr_workspace_bytes(n_out, K, G, C, M, int(bool(transpose)), code)
+        ws = workspace(nbytes, feat.device)
+        check(L.pcx_mvmr(ptr(weight), ptr(feat), ptr(gather), ptr(scatter), ptr(seg_offs), ptr(tap_idx),
+                         ptr(out), gather.numel(), feat.shape[0], n_out, K, G, C, M,
+                         int(bool(transpose)), code, engine, ptr(ws), ws.numel(), stream_ptr()))
+    return out
+
+
+def vvor(a, a_idx, b, b_idx, seg_offs, o_idx, n_o, engine=ENGINE_AUTO):
+    """``out[o[t], g, m, c] += a[a_idx[t], g, m] * b[b_idx[t], g, c]``.
+
+    a (n_a, G, Ma); b (n_b, G, Cb); returns (n_o, G, Ma, Cb) in a.dtype.
+    """
+    require_cuda(a, b, a_idx, b_idx, seg_offs, o_idx)
+    code = dtype_code(a.dtype)
+    assert a.dtype == b.dtype, (a.dtype, b.dtype)
+    a, b = a.contiguous(), b.contiguous()
+    G, Ma, Cb = a.shape[1], a.shape[2], b.shape[2]
+    a_idx, b_idx, o_idx = as_i32(a_idx), as_i32(b_idx), as_i32(o_idx)
+    if seg_offs is not None:
+        seg_offs = seg_offs.to(torch.int64).contiguous()
+    n_o = int(n_o)
+    out = torch.empty((n_o, G, Ma, Cb), dtype=a.dtype, device=a.device)
+    L = lib()
+    with torch.cuda.device(a.device):
+        ws = workspace(L.pcx_vvor_workspace_bytes(n_o, G, Ma, Cb, code), a.device)
+        check(L.pcx_vvor(ptr(a), ptr(a_idx), ptr(b), ptr(b_idx), ptr(seg_offs), ptr(o_idx), ptr(out),
+                         a_idx.numel(), a.shape[0], b.shape[0], n_o, G, Ma, Cb, code, engine,
+                         ptr(ws), ws.numel(), stream_ptr()))
+    return out
+
+
+def seg_offs_from_sorted(idx_sorted, K):
+    require_cuda(idx_sorted)
+    idx = as_i32(idx_sorted)
+    out = torch.empty(int(K) + 1, dtype=torch.int64, device=idx.device)
+    with torch.cuda.device(idx.device):
+        check(lib().pcx_seg_offs(ptr(idx), idx.numel(), int(K), ptr(out), stream_ptr()))
+    return out
+
+
+def expand_taps(seg_offs, K, T):
+    require_cuda(seg_offs)
+    out = torch.empty(int(T), dtype=torch.int32, device=seg_offs.device)
+    with torch.cuda.device(seg_offs.device):
+        check(lib().pcx_expand_taps(ptr(seg_offs), int(K), int(T), ptr(out), stream_ptr()))
+    return out
+
+
+# -------------------------------------------------------------- geometry ----
+def radius_search(points, queries, radius, point_sample, query_sample, distance_type,
+                  kernel_size=0, kernel_grid_size=0.0, return_distances=False, want_k=False):
+    """Sorted-grid fixed-radius search.
+
+    ``kernel_size == 0``: returns ``(neighbors int64, num_neighbors int64, distances|None)``.
+    ``kernel_size > 0``: returns ``(i int32, j int32, k int32|None, seg_offs int64, num_neighbors int64)``.
+    Inputs must be non-empty fp32 (P,3)/(Q,3) CUDA tensors.
+    """
+    require_cuda(points, queries, point_sample, query_sample)
+    dev = points.device
+    points, queries = points.contiguous(), queries.contiguous()
+    ps, qs = as_i32(point_sample), as_i32(query_sample)
+    P, Q = points.shape[0], queries.shape[0]
+    L = lib()
+    k3 = kernel_size ** 3
+    with torch.cuda.device(dev):
+        ws = workspace(L.pcx_radius_workspace_bytes(P, Q, kernel_size), dev)
+        num_neighbors = torch.empty(Q, dtype=torch.int64, device=dev)
+        seg = torch.empty(k3 + 1, dtype=torch.int64, device=dev) if kernel_size > 0 else None
+        total = c_int64(0)
+        check(L.pcx_radius_count(ptr(points), ptr(queries), ptr(ps), ptr(qs), P, Q, float(radius),
+                                 distance_type, kernel_size, float(kernel_grid_size), ptr(num_neighbors),
+                                 ptr(seg), ctypes.byref(total), ptr(ws), ws.numel(), stream_ptr()))
+        total = int(total.value)
+        if kernel_size == 0:
+            neighbors = torch.empty(total, dtype=torch.int64, device=dev)
+            dist = torch.empty(total, dtype=torch.float32, device=dev) if return_distances else None
+            check(L.pcx_radius_fill(ptr(points), ptr(queries), P, Q, float(radius), distance_type, 0, 0.0,
+                                    total, ptr(neighbors), ptr(dist), None, None, None, ptr(ws), ws.numel(),
+                                    None, 0, stream_ptr()))
+            return neighbors, num_neighbors, dist
+        if total > 2 ** 31 - 1:
+            raise RuntimeError("prepared kernel-segment output currently requires fewer "
+                               f"than 2^31 edges; got {total}")
+        out_i = torch.empty(total, dtype=torch.int32, device=dev)
+        out_j = torch.empty(total, dtype=torch.int32, device=dev)
+        out_k = torch.empty(total, dtype=torch.int32, device=dev) if want_k else None
+        ws2 = workspace(L.pcx_radius_fill_workspace_bytes(total, kernel_size), dev)
+        check(L.pcx_radius_fill(ptr(points), ptr(queries), P, Q, float(radius), distance_type, kernel_size,
+                                float(kernel_grid_size), total, None, None, ptr(out_i), ptr(out_j), ptr(out_k),
+                                ptr(ws), ws.numel(), ptr(ws2), ws2.numel(), stream_ptr()))
+    return out_i, out_j, out_k, seg, num_neighbors
+
+
+def grid_sample_center_nearest(points, cell, sample, return_mapping):
+    """Returns ``(indices int64 (S,), points_f (S,3), sample_f int32 (S,)|None, mapping int64|None)``."""
+    require_cuda(points, sample)
+    dev = points.device
+    points = points.contiguous()
+    smp = as_i32(sample)
+    N = points.shape[0]
+    L = lib()
+    with torch.cuda.device(dev):
+        ws = workspace(L.pcx_grid_sample_workspace_bytes(N), dev)
+        ncells = c_int64(0)
+        check(L.pcx_grid_sample_count(ptr(points), ptr(smp), N, float(cell), ctypes.byref(ncells), ptr(ws),
+                                      ws.numel(), stream_ptr()))
+        S = int(ncells.value)
+        indices = torch.empty(S, dtype=torch.int64, device=dev)
+        out_pts = torch.empty((S, 3), dtype=torch.float32, device=dev)
+        out_smp = torch.empty(S, dtype=torch.int32, device=dev) if smp is not None else None
+        mapping = torch.empty(N, dtype=torch.int64, device=dev) if return_mapping else None
+        check(L.pcx_grid_sample_select(ptr(points), ptr(smp), N, float(cell), S, ptr(indices), ptr(out_pts),
+                                       ptr(out_smp), ptr(mapping), ptr(ws), ws.numel(), stream_ptr()))
+    return indices, out_pts, out_smp, mapping

@@ -1,0 +1,138 @@
+"""Point convolution layer (mirror of ``layers/conv.py``: ``GeneralConv``
+:85-465, ``PointConv3d`` :468-510, ``conv_with_stride`` :513-546).
+
+Parameters keep the reference layout ``(K, G, C_in/G, C_out/G)`` and
+initialisation ``U(+-1/sqrt((C_out/G) * K))`` so checkpoints interchange; a
+legacy ``(C_in, C_out/G, K)`` weight is converted on load.  The forward routes
+tap-sorted triplets (the contract every builder here produces) to the
+tap-sorted engine and anything else to the public per-triplet operator.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Optional, Tuple
+
+import torch
+from torch import Tensor
+from torch.nn import Module, init
+from torch.nn.modules.utils import _triple
+from torch.nn.parameter import Parameter
+
+from ..sparse_engines._dispatch_override import current_mode, resolve_input_precision, warn_pt_fallback
+from ..sparse_engines.ops import sparse_matrix_vector_multiplication_reduction
+from ..sparse_engines.tig import TigIndex, tig_mvmr
+from .contract import TripletContract
+from .metadata import MetaData
+from .triplets import handle_stride_and_build_triplets
+
+
+class GeneralConv(Module):
+    __constants__ = ["groups", "in_channels", "out_channels", "kernel_size"]
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: int, groups: int, bias: bool,
+                 device=None, dtype=None) -> None:
+        super().__init__()
+        if groups <= 0:
+            raise ValueError("groups must be a positive integer")
+        if in_channels % groups != 0:
+            raise ValueError("in_channels must be divisible by groups")
+        if out_channels % groups != 0:
+            raise ValueError("out_channels must be divisible by groups")
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size, self.groups = kernel_size, groups
+        kw = {"device": device, "dtype": dtype}
+        self.weight = Parameter(torch.empty(
+            (kernel_size, groups, in_channels // groups, out_channels // groups), **kw))
+        if bias:
+            self.bias = Parameter(torch.empty(out_channels, **kw))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        fan_in = (self.out_channels // self.groups) * self.kernel_size
+        bound = 1.0 / math.sqrt(fan_in) if fan_in > 0 else 0.0
+        init.uniform_(self.weight, -bound, bound)
+        if self.bias is not None and fan_in != 0:
+            init.uniform_(self.bias, -bound, bound)
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys,
+                              unexpected_keys, error_msgs):
+        key = prefix + "weight"
+        w = state_dict.get(key)
+        legacy = (self.in_channels, self.out_channels // self.groups, self.kernel_size)
+        if w is not None and tuple(w.shape) == legacy:
+            state_dict[key] = (w.reshape(self.groups, self.in_channels // self.groups,
+                                         self.out_channels // self.groups, self.kernel_size)
+                               .permute(3, 0, 1, 2).contiguous())
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys,
+                                      unexpected_keys, error_msgs)
+
+    def extra_repr(self):
+        s = f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}"
+        if self.groups != 1:
+            s += f", groups={self.groups}"
+        if self.bias is None:
+            s += ", bias=False"
+        return s
+
+    def _conv_forward(self, input: Tensor, i: Tensor, j: Tensor, k: Tensor, n: int, weight: Tensor,
+                      bias: Optional[Tensor], *, contract: Optional[TripletContract] = None,
+                      seg_offs: Optional[Tensor] = None) -> Tensor:
+        x3 = input.view(input.shape[0], self.groups, -1) if input.dim() == 2 else input
+        x3 = x3.contiguous()
+        if contract is None:
+            contract = TripletContract.submanifold()
+        mode = current_mode()
+        if mode == "auto":
+            use_sorted = contract.k_sorted
+            if not use_sorted:
+                warn_pt_fallback("PointConv3d", "triplets are not k-sorted (contract)",
+                                 K=weight.shape[0], C=self.in_channels, M=self.out_channels, G=self.groups)
+        else:
+            use_sorted = mode != "force_pt" and contract.k_sorted
+        if use_sorted:
+            n_in, K = x3.shape[0], weight.shape[0]
+            if seg_offs is not None:
+                idx = TigIndex.from_flat(
+                    i, j, seg_offs, n_out=n, n_in=n_in, num_kernel_offsets=K,
+                    exact_cover_out=contract.exact_cover_out, exact_cover_in=contract.exact_cover_in,
+                    uniform_seg_len=contract.uniform_seg_len if contract.uniform_seg_len is not None else -1)
+            else:
+                idx = TigIndex(i, j, k, n, K, build_hybrid=False, assume_sorted=True, n_in=n_in,
+                               uniform_seg_len=contract.uniform_seg_len,
+                               exact_cover_out=contract.exact_cover_out,
+                               exact_cover_in=contract.exact_cover_in)
+            output = tig_mvmr(weight, x3.view(n_in, -1), idx,
+                              input_precision=resolve_input_precision(x3.dtype))
+        else:
+            output = sparse_matrix_vector_multiplication_reduction(weight, k, x3, j, i, n)
+        output = output.reshape(-1, self.out_channels)
+        if bias is not None:
+            output = output + bias
+        return output
+
+
+class PointConv3d(GeneralConv):
+    """Convolution on native points (PointCNN++): ``out[i] += x[j] @ W[k]``."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, groups: int = 1,
+                 bias: bool = True, device=None, dtype=None) -> None:
+        self.kernel_size_3 = _triple(kernel_size)
+        super().__init__(in_channels, out_channels, math.prod(self.kernel_size_3), groups, bias,
+                         device=device, dtype=dtype)
+
+    def forward(self, input: Tensor, i: Tensor, j: Tensor, k: Tensor, n: int,
+                contract: Optional[TripletContract] = None, seg_offs: Optional[Tensor] = None) -> Tensor:
+        return self._conv_forward(input, i, j, k, n, self.weight, self.bias, contract=contract,
+                                  seg_offs=seg_offs)
+
+
+def conv_with_stride(conv_op: Callable, x: Tensor, m: MetaData, stride: float,
+                     receptive_field_scaler=1.0, distance_type: str = "ball") -> Tuple[Tensor, MetaData]:
+    """Strided convolution: down-sample ``m`` by ``stride``, build the triplets
+    from the parent cloud to the down-sampled cloud, convolve."""
+    m = handle_stride_and_build_triplets(m, stride, conv_op.kernel_size_3, receptive_field_scaler,
+                                         distance_type=distance_type)
+    x = conv_op(x, m.i, m.j, m.k, m.num_points(), contract=m.contract, seg_offs=m.seg_offs)
+    return x, m

@@ -1,0 +1,198 @@
+"""Triplet (rulebook) construction (mirror of ``layers/triplets.py``).
+
+``(i, j, k)``: input point ``j`` contributes to output point ``i`` through
+kernel tap ``k``.  The convolution path uses ``build_triplets_segmented``
+(:584-682): one sorted-grid radius search that emits the pairs already grouped
+by tap, with the tap computed on the device exactly like ``voxelize_3d``
+(:547-561).  ``build_triplets`` (:686-764) is the generic builder for custom
+indexers and other sort orders.
+"""
+from __future__ import annotations
+
+import math
+from functools import partial
+from typing import Callable, Optional
+
+import torch
+from torch.nn.modules.utils import _triple
+
+from ..internals.indexing import cumsum_exclusive, repeat_interleave_indices
+from ..internals.neighbors import radius_search, radius_search_sorted_grid8_segments
+from ..sparse_engines._seg_offs import kernel_offset_segments
+from .contract import TripletContract
+from .downsample import downsample
+from .metadata import MetaData
+
+_NO_NEIGHBOR_MSG = (
+    "Neighborhood search failed for some points, consider increase the neighbor_radius. "
+    "It is likely that this happens in an *upsample* phase, where the query_points are not "
+    "a subset of the points.")
+
+
+def full_cover_radius_scaler(stride, radius_margin=1e-2):
+    if stride <= 0:
+        raise ValueError(f"stride must be positive; got {stride}")
+    if radius_margin < 0:
+        raise ValueError(f"radius_margin must be non-negative; got {radius_margin}")
+    return (math.sqrt(3.0) / 2.0) * float(stride) * (1.0 + float(radius_margin))
+
+
+def minimum_full_cover_kernel_size(radius_scaler):
+    return 2 * int(math.ceil(float(radius_scaler))) + 1
+
+
+def radius_scaler_for_kernel_size(kernel_size, receptive_field_scaler=1.0, distance_type="ball"):
+    """``neighbor_radius = grid_size * radius_scaler``: the ball (or cube) whose
+    volume is ``receptive_field_scaler`` times the kernel cube's."""
+    kmax = max(_triple(kernel_size))
+    if distance_type == "cube":
+        return kmax * math.pow(receptive_field_scaler, 1 / 3) / 2.0
+    volume = math.pow(kmax, 3) * receptive_field_scaler
+    return math.pow(3 * volume / (4 * math.pi), 1 / 3)
+
+
+def voxelize_3d(kernel_size, points, grid_size=None):
+    """Tap of every offset: round-half-even of ``offset / grid_size``, shifted
+    by ``K // 2``, clamped to the kernel, x most significant."""
+    with torch.no_grad():
+        ks = _triple(kernel_size)[0]
+        cell = (points / grid_size).round().int()
+        cell = torch.clamp(cell + (ks // 2), min=0, max=ks - 1)
+        mult = torch.tensor([ks * ks, ks, 1], device=points.device, dtype=torch.int32)
+        return torch.sum(cell * mult, dim=1)
+
+
+def should_use_direct_segmented_triplets(kernel_size):
+    s = _triple(kernel_size)
+    return s[0] == s[1] == s[2] and int(s[0]) >= 1 and int(s[0]) % 2 == 1
+
+
+def _resolve_queries(points, sample_inds, sample_sizes, query_points, query_sample_inds, query_sample_sizes):
+    if query_points is None or query_sample_inds is None or query_sample_sizes is None:
+        assert query_points is None and query_sample_inds is None and query_sample_sizes is None
+        return points, sample_inds, sample_sizes
+    return query_points, query_sample_inds, query_sample_sizes
+
+
+@torch.compiler.disable
+def build_triplets_segmented(points, sample_inds, sample_sizes, neighbor_radius, kernel_size,
+                             query_points=None, query_sample_inds=None, query_sample_sizes=None,
+                             return_num_neighbors=False, radius_scaler=None, tap_stripes=32):
+    """Returns ``(i, j, k int32, seg_offs int64, num_neighbors or None)`` with the
+    triplets grouped by tap.  Raises when a query has no neighbour."""
+    sizes = _triple(kernel_size)
+    if not (sizes[0] == sizes[1] == sizes[2]):
+        raise ValueError(f"segmented triplet construction requires a cubic kernel; got {sizes}")
+    ks = int(sizes[0])
+    if ks <= 0 or ks % 2 == 0:
+        raise ValueError(f"segmented triplet construction requires a positive odd kernel; got {ks}")
+    if radius_scaler is None or float(radius_scaler) <= 0:
+        raise ValueError("segmented triplet construction requires a positive radius_scaler")
+    kernel_grid_size = float(neighbor_radius) / float(radius_scaler)
+    with torch.no_grad():
+        query_points, query_sample_inds, query_sample_sizes = _resolve_queries(
+            points, sample_inds, sample_sizes, query_points, query_sample_inds, query_sample_sizes)
+        i, j, seg_offs, num_neighbors, k = radius_search_sorted_grid8_segments(
+            points=points, queries=query_points, radius=neighbor_radius, kernel_size=ks,
+            kernel_grid_size=kernel_grid_size, sample_inds=sample_inds,
+            query_sample_inds=query_sample_inds, dtype_num_neighbors=torch.int64,
+            distance_type="ball", tap_stripes=tap_stripes, return_k=True)
+        if num_neighbors.numel() and bool((num_neighbors == 0).any().item()):
+            raise AssertionError(_NO_NEIGHBOR_MSG)
+        return i, j, k, seg_offs, (num_neighbors if return_num_neighbors else None)
+
+
+def _triplets_from_pairs(points, query_points, neighbor_indices, num_neighbors, kernel_indexer,
+                         neighbor_radius, radius_scaler, sort_by, return_num_neighbors):
+    with torch.no_grad():
+        assert torch.min(num_neighbors) > 0, _NO_NEIGHBOR_MSG
+        starts, total = cumsum_exclusive(num_neighbors, return_sum=True)
+        i = repeat_interleave_indices(repeats_cumsum=starts, output_size=int(total))
+        j = neighbor_indices.long()
+        offsets = points[j] - query_points[i]
+        k = kernel_indexer(points=offsets, grid_size=neighbor_radius / radius_scaler)
+        if sort_by == "j":
+            j, order = torch.sort(j)
+            i, k = i[order], k[order]
+        elif sort_by == "k":
+            k, order = torch.sort(k, stable=True)
+            i, j = i[order], j[order]
+        elif sort_by != "i":
+            raise AssertionError(f'Unknown sort_by argument "{sort_by}", it should be i, j, or k!')
+        dt = torch.int32 if max(query_points.shape[0], points.shape[0]) <= 2147483647 else torch.int64
+        return i.to(dt), j.to(dt), k.to(dt), (num_neighbors if return_num_neighbors else None)
+
+
+@torch.compiler.disable
+def build_triplets(points, sample_inds, sample_sizes, neighbor_radius, kernel_indexer: Callable,
+                   query_points=None, query_sample_inds=None, query_sample_sizes=None, sort_by="k",
+                   return_num_neighbors=False, radius_scaler: Optional[float] = None):
+    """Generic builder: query-major search, tap from ``kernel_indexer``, global sort."""
+    with torch.no_grad():
+        query_points, query_sample_inds, query_sample_sizes = _resolve_queries(
+            points, sample_inds, sample_sizes, query_points, query_sample_inds, query_sample_sizes)
+        grid_size = neighbor_radius / radius_scaler if radius_scaler is not None else None
+        neighbor_indices, num_neighbors = radius_search(
+            points=points, query_points=query_points, radius=neighbor_radius, sample_inds=sample_inds,
+            sample_sizes=sample_sizes, query_sample_inds=query_sample_inds,
+            query_sample_sizes=query_sample_sizes, grid_size=grid_size)
+    return _triplets_from_pairs(points, query_points, neighbor_indices, num_neighbors, kernel_indexer,
+                                neighbor_radius, radius_scaler, sort_by, return_num_neighbors)
+
+
+def _same_cloud(a: MetaData, b: MetaData):
+    return (a is not None and a.points.shape == b.points.shape and a.grid_size == b.grid_size
+            and torch.equal(a.points, b.points) and torch.equal(a.sample_inds, b.sample_inds))
+
+
+def _build_for(m_points, m_sample_inds, m_sample_sizes, neighbor_radius, kernel_size, radius_scaler,
+               sort_by, distance_type, return_num_neighbors, query=None):
+    qp, qi, qs = query if query is not None else (None, None, None)
+    if sort_by == "k" and distance_type == "ball" and should_use_direct_segmented_triplets(kernel_size):
+        return build_triplets_segmented(
+            points=m_points, sample_inds=m_sample_inds, sample_sizes=m_sample_sizes,
+            neighbor_radius=neighbor_radius, kernel_size=kernel_size, query_points=qp,
+            query_sample_inds=qi, query_sample_sizes=qs, return_num_neighbors=return_num_neighbors,
+            radius_scaler=radius_scaler)
+    i, j, k, nn = build_triplets(
+        points=m_points, sample_inds=m_sample_inds, sample_sizes=m_sample_sizes,
+        neighbor_radius=neighbor_radius, kernel_indexer=partial(voxelize_3d, kernel_size=kernel_size),
+        query_points=qp, query_sample_inds=qi, query_sample_sizes=qs, sort_by=sort_by,
+        return_num_neighbors=return_num_neighbors, radius_scaler=radius_scaler)
+    seg = kernel_offset_segments(k, math.prod(_triple(kernel_size))) if sort_by == "k" else None
+    return i, j, k, seg, nn
+
+
+@torch.compiler.disable
+def handle_stride_and_build_triplets(m: MetaData, stride, kernel_size=_triple(3),
+                                     receptive_field_scaler=1.0, sort_by="k",
+                                     return_num_neighbors=False, distance_type="ball") -> MetaData:
+    """Down-sample ``m`` by ``stride`` (when != 1) and attach the triplets that
+    connect the parent cloud to the (down-sampled) query cloud.  The mirrored
+    edges are cached on the parent for a later up-sampling layer."""
+    with torch.no_grad():
+        radius_scaler = radius_scaler_for_kernel_size(kernel_size, receptive_field_scaler, distance_type)
+        if stride != 1:
+            if _same_cloud(m.parent, m):
+                parent = m.parent
+            else:
+                parent = MetaData(points=m.points, sample_inds=m.sample_inds, sample_sizes=m.sample_sizes,
+                                  grid_size=m.grid_size, parent=m.parent)
+                m.parent = parent
+            neighbor_radius = parent.grid_size * radius_scaler
+            m.points, m.sample_inds, m.grid_size, m.downsample_indices = downsample(
+                m.points, m.sample_inds, m.grid_size, stride)
+            m.sample_sizes = torch.bincount(m.sample_inds)
+            m.i, m.j, m.k, m.seg_offs, m.num_neighbors = _build_for(
+                parent.points, parent.sample_inds, parent.sample_sizes, neighbor_radius, kernel_size,
+                radius_scaler, sort_by, distance_type, return_num_neighbors,
+                query=(m.points, m.sample_inds, m.sample_sizes))
+            parent.i_upsample, parent.j_upsample = m.j, m.i
+            parent.k_upsample, parent.seg_offs_upsample = m.k, m.seg_offs
+        if m.empty_triplets():
+            neighbor_radius = m.grid_size * radius_scaler
+            m.i, m.j, m.k, m.seg_offs, m.num_neighbors = _build_for(
+                m.points, m.sample_inds, m.sample_sizes, neighbor_radius, kernel_size, radius_scaler,
+                sort_by, distance_type, return_num_neighbors)
+    m.contract = TripletContract(k_sorted=(sort_by == "k"))
+    return m

@@ -1,0 +1,173 @@
+"""CPU-only tests: the C-ABI library loads and exports what the header
+declares, host-side logic, loud failure without CUDA, data-parallel plumbing
+over gloo with two ranks."""
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    import ctypes
+
+    from pointelligence_b200 import _cabi, build
+
+    build.build()
+    header = open(os.path.join(ROOT, "include", "pointelligence_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(pcx_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 16
+    handle = ctypes.CDLL(_cabi.LIB_PATH)
+    for name in declared:
+        assert hasattr(handle, name), f"{name} is declared but not exported"
+        assert name in _cabi.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(_cabi.SIGNATURES) == declared
+    assert _cabi.lib().pcx_version() >= 10000
+
+
+def test_operators_fail_loudly_without_cuda():
+    from pointelligence_b200.internals.grid_sample import grid_sample_filter
+    from pointelligence_b200.internals.neighbors import radius_search
+    from pointelligence_b200.sparse_engines.ops import sparse_matrix_vector_multiplication_reduction as mvmr
+
+    p = torch.rand(10, 3)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        radius_search(p, p, 0.5)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        grid_sample_filter(p, 0.1)
+    a = torch.rand(3, 1, 4, 4)
+    b = torch.rand(5, 1, 4)
+    idx = torch.zeros(2, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        mvmr(a, idx, b, idx, idx, 5, torch.tensor([0, 2, 2, 2]))
+
+
+def test_dispatch_and_precision_modes():
+    from pointelligence_b200.sparse_engines._dispatch_override import (current_engine, current_mode,
+                                                                       current_precision, dispatch_mode,
+                                                                       precision_mode, resolve_input_precision)
+
+    assert current_mode() == "auto" and current_engine() == 0
+    with dispatch_mode("force_pt"):
+        assert current_mode() == "force_pt" and current_engine() == 1
+        with dispatch_mode("force_fgs"):
+            assert current_mode() == "force_fused_gather_sum"
+    assert current_mode() == "auto"
+    with pytest.raises(ValueError, match="renamed"):
+        with dispatch_mode("force_smig"):
+            pass
+    with pytest.raises(ValueError, match="unknown dispatch mode"):
+        with dispatch_mode("nope"):
+            pass
+    assert resolve_input_precision(torch.bfloat16) == "tf32"
+    with precision_mode("ieee"):
+        assert current_precision() == "ieee" and resolve_input_precision(torch.float32) == "ieee"
+    with pytest.raises(ValueError):
+        with precision_mode("fp8"):
+            pass
+
+
+def test_host_formulas_and_voxelize(golden):
+    from pointelligence_b200.layers import (full_cover_radius_scaler, minimum_full_cover_kernel_size,
+                                            radius_scaler_for_kernel_size, voxelize_3d)
+
+    z = golden("voxelize")
+    got = [radius_scaler_for_kernel_size(3), radius_scaler_for_kernel_size(3, 2.5),
+           radius_scaler_for_kernel_size(5, 2.5), radius_scaler_for_kernel_size(3, 1.0, "cube"),
+           radius_scaler_for_kernel_size((1, 3, 5), 2.0)]
+    assert np.array_equal(np.array(got), z["radius_scaler"])
+    assert full_cover_radius_scaler(8, 1e-2) == pytest.approx(6.99748526, rel=1e-7)
+    assert minimum_full_cover_kernel_size(full_cover_radius_scaler(8, 1e-2)) == 15
+    offs = torch.from_numpy(z["offsets"])
+    for ks in (1, 3, 5, 7, 15):
+        assert np.array_equal(voxelize_3d(ks, offs, torch.tensor(0.02)).numpy(), z[f"k{ks}"])
+
+
+def test_pointconv3d_parameters_and_legacy_checkpoint():
+    from pointelligence_b200.layers import PointConv3d, TripletContract
+
+    torch.manual_seed(0)
+    conv = PointConv3d(8, 12, 3, groups=2, bias=True)
+    assert conv.weight.shape == (27, 2, 4, 6) and conv.bias.shape == (12,)
+    bound = 1.0 / np.sqrt(6 * 27)
+    assert float(conv.weight.abs().max()) <= bound
+    legacy = torch.randn(8, 6, 27)
+    conv.load_state_dict({"weight": legacy, "bias": torch.zeros(12)})
+    expect = legacy.reshape(2, 4, 6, 27).permute(3, 0, 1, 2)
+    assert torch.equal(conv.weight.data, expect)
+    c = TripletContract.submanifold()
+    assert c.k_sorted and not c.exact_cover_out and c.uniform_seg_len is None
+    with pytest.raises(ValueError):
+        PointConv3d(7, 12, 3, groups=2)
+
+
+def test_synthetic_generators_are_deterministic():
+    from pointelligence_b200.synthetic import indoor_scene, lidar_sweep, ragged_batch
+
+    a, b = indoor_scene(5000, 3), indoor_scene(5000, 3)
+    assert a.dtype == np.float32 and a.shape == (5000, 3) and np.array_equal(a, b)
+    cells = np.floor(a / np.float32(0.02)).astype(np.int64)
+    assert len(np.unique(cells, axis=0)) == 5000          # voxel de-duplicated
+    l = lidar_sweep(100)
+    assert 80000 < len(l) < 131072 and np.array_equal(l, lidar_sweep(100))
+    pts, inds, sizes = ragged_batch([a, l[:100]])
+    assert pts.shape == (5100, 3) and sizes.tolist() == [5000, 100] and inds[-1] == 1
+
+
+def test_partition_scenes_balances_and_covers():
+    from pointelligence_b200.dist import partition_scenes
+
+    rng = np.random.default_rng(1000)
+    sizes = rng.integers(80000, 200001, 16).tolist()
+    for world in (1, 2, 4, 8):
+        owned = partition_scenes(sizes, world)
+        assert sorted(s for o in owned for s in o) == list(range(16))
+        loads = [sum(sizes[s] for s in o) for o in owned]
+        assert max(loads) <= sum(sizes) / world + max(sizes)
+    assert partition_scenes(sizes, 2) == partition_scenes(sizes, 2)
+
+
+_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from pointelligence_b200.dist import allreduce_gradients, partition_scenes
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%s" % sys.argv[2],
+                        rank=int(sys.argv[3]), world_size=2)
+rank = dist.get_rank()
+torch.manual_seed(0)
+params = [torch.nn.Parameter(torch.zeros(27, 1, 8, 8)), torch.nn.Parameter(torch.zeros(8)),
+          torch.nn.Parameter(torch.zeros(3, 3))]
+params[0].grad = torch.full_like(params[0], float(rank + 1))
+params[1].grad = torch.arange(8.0) * (rank + 1)
+# params[2] has no gradient on rank 1 only
+if rank == 0:
+    params[2].grad = torch.ones(3, 3)
+allreduce_gradients(params, average=True, bucket_bytes=4096)
+assert torch.allclose(params[0].grad, torch.full_like(params[0], 1.5))
+assert torch.allclose(params[1].grad, torch.arange(8.0) * 1.5)
+assert torch.allclose(params[2].grad, torch.full((3, 3), 0.5))
+owned = partition_scenes([5, 9, 7, 3], 2)
+assert sorted(owned[0] + owned[1]) == [0, 1, 2, 3]
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+'''
+
+
+def test_gradient_allreduce_two_ranks_gloo(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    port = str(29500 + os.getpid() % 2000)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, port, str(r)],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, o
+        assert f"rank {r} ok" in o
