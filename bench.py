@@ -1,0 +1,374 @@
+"""Benchmark of the point-convolution hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): one PointConv3d layer on a synthetic indoor scene of 150 000
+points (room + 20 boxes, 2 cm voxel de-duplication), radius 5 cm, 27 taps on a
+2 cm tap grid, C_in = C_out = 64 bf16 with fp32 accumulation.  A step is one
+pass of forward (MVMR), input gradient (transposed MVMR) and weight gradient
+(VVOR) over the scene's tap-sorted triplets; the rulebook is built once by the
+CUDA geometry stage and stays resident.  With N > 1 ranks every rank owns one
+scene (seed = rank, weak scaling) and the step ends with the all-reduce of the
+weight gradient, the path's only collective.
+
+Printed JSON (rank 0, one line):
+  value     triplets of all ranks / max-over-ranks device time per step, inputs
+            resident in HBM, CUDA events per step, L2 flushed between steps
+  e2e       the same metric through the public operator API with HOST buffers:
+            features and output gradients are copied in from pinned memory and
+            the three results copied back inside the timed region
+  roofline  the dominant kernel's algorithmic bytes / its event-timed duration
+            against the measured HBM copy bandwidth
+  cpu_baseline  the reference's own CPU operators timed on a bounded spatial
+            crop of the same scene (single-threaded by construction)
+
+``--impl reference`` times those CPU operators alone (no GPU work).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_POINTS = 150_000
+CHANNELS = 64
+RADIUS = 0.05
+TAP_GRID = 0.02
+KERNEL = 3
+METRIC = "pointconv3d_fwd_dgrad_wgrad_throughput"
+UNIT = "Gtriplets/s"
+WORKLOAD = ("indoor150k_c64_bf16: PointConv3d fwd+dgrad+wgrad, 150000-point synthetic indoor scene, "
+            "R=5cm, 27 taps, C_in=C_out=64 bf16, fp32 accumulate")
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def algorithmic_bytes(T, n_in, n_out, C, M, K=27, e=2):
+    """Per-pass algorithmic HBM bytes: one gathered row per triplet, both index
+    arrays once, every output row written once in the feature dtype, weights once."""
+    w = K * C * M * e
+    return {
+        "fwd": T * (C * e + 8) + n_out * M * e + w + 8 * (K + 1),
+        "dgrad": T * (M * e + 8) + n_in * C * e + w + 8 * (K + 1),
+        "wgrad": T * (C * e + M * e + 8) + 4 * K * C * M,
+    }
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason sampler running during the timed region."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        self.file.flush()
+        rows = [r.split(",") for r in open(self.file.name).read().strip().splitlines() if r.strip()]
+        os.unlink(self.file.name)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.strip().lower() == "active":
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------- CPU reference arm
+def _crop(points, target):
+    """Spatial crop (smallest x first) that keeps the scene's local density."""
+    order = np.argsort(points[:, 0], kind="stable")
+    return np.ascontiguousarray(points[order[:target]])
+
+
+def cpu_reference_step_inputs(seed, crop_points):
+    from oracle import geometry as og
+    from pointelligence_b200.synthetic import indoor_scene
+
+    pts = _crop(indoor_scene(N_POINTS, seed), crop_points)
+    i, j, seg, _ = og.radius_search_sorted_grid8_segments(pts, pts, RADIUS, KERNEL, TAP_GRID)
+    k = np.repeat(np.arange(KERNEL ** 3), np.diff(seg)).astype(np.int32)
+    rng = np.random.default_rng(seed + 1)
+    n = len(pts)
+    x = rng.standard_normal((n, 1, CHANNELS)).astype(np.float32)
+    go = rng.standard_normal((n, 1, CHANNELS)).astype(np.float32)
+    bound = 1.0 / np.sqrt(CHANNELS * KERNEL ** 3)
+    w = rng.uniform(-bound, bound, (KERNEL ** 3, 1, CHANNELS, CHANNELS)).astype(np.float32)
+    return dict(n=n, i=i, j=j, k=k, x=x, go=go, w=w, wt=np.ascontiguousarray(np.swapaxes(w, 2, 3)))
+
+
+def cpu_reference_step(d):
+    """fwd + dgrad + wgrad with the reference's CPU operators (or the C port)."""
+    from oracle import sparse_ops as oso
+
+    if oso.reference_ops_available():
+        mv, vv, kind = oso.mvmr_ref, oso.vvor_ref, "reference"
+    else:
+        mv, vv, kind = oso.mvmr_c, oso.vvor_c, "port"
+    t0 = time.perf_counter()
+    mv(d["w"], d["k"], d["x"], d["j"], d["i"], d["n"])
+    mv(d["wt"], d["k"], d["go"], d["i"], d["j"], d["n"])
+    vv(d["x"], d["j"], d["go"], d["i"], d["k"], KERNEL ** 3)
+    return time.perf_counter() - t0, kind
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    crop = 8000
+    d = cpu_reference_step_inputs(0, crop)
+    T = len(d["i"])
+    for _ in range(args.warmup):
+        cpu_reference_step(d)
+    times = []
+    kind = "port"
+    for _ in range(args.steps):
+        dt, kind = cpu_reference_step(d)
+        times.append(dt)
+    t = sum(times) / len(times)
+    value = T / t / 1e9
+    sample = (f"spatial crop of {d['n']} points / {T} triplets of the 150000-point scene per step, fp32, "
+              "reference CPU operators compiled from its sources" if kind == "reference" else
+              f"spatial crop of {d['n']} points / {T} triplets per step, fp32, C restatement of the reference loops")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------- GPU arm
+def run_ours(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from pointelligence_b200 import _cabi
+    from pointelligence_b200.layers.triplets import build_triplets_segmented
+    from pointelligence_b200.sparse_engines.tig import TigIndex, tig_mvmr
+    from pointelligence_b200.synthetic import indoor_scene
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (the operators have no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- scene, rulebook (geometry stage on the GPU), operands
+    pts_np = indoor_scene(N_POINTS, rank)
+    pts = torch.from_numpy(pts_np).to(dev)
+    n = pts.shape[0]
+    sample = torch.zeros(n, dtype=torch.int64, device=dev)
+    sizes = torch.tensor([n], device=dev)
+    i, j, k, seg, _ = build_triplets_segmented(pts, sample, sizes, RADIUS, KERNEL, radius_scaler=RADIUS / TAP_GRID)
+    T = int(i.numel())
+    K = KERNEL ** 3
+    g = torch.Generator(device=dev).manual_seed(rank + 1)
+    C = M = CHANNELS
+    bound = 1.0 / np.sqrt(M * K)
+    x = torch.randn(n, C, device=dev, generator=g).bfloat16()
+    go = torch.randn(n, M, device=dev, generator=g).bfloat16()
+    w = ((torch.rand(K, 1, C, M, device=dev, generator=g) * 2 - 1) * bound).bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
+
+    def step_resident():
+        out = _cabi.mvmr(w, x, j, i, seg, None, n, False)
+        gx = _cabi.mvmr(w, go, i, j, seg, None, n, True)
+        gw = _cabi.vvor(x.view(n, 1, C), j, go.view(n, 1, M), i, seg, None, K)
+        if world > 1:
+            dist.all_reduce(gw)
+        return out, gx, gw
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    barrier()
+
+    # ---- timed region: K steps, one event pair per step, L2 flushed between steps
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    _cabi.launch_count(reset=True)
+    _cabi.profile_enable(True)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for a, b in ev:
+        flush.fill_(1)
+        a.record()
+        step_resident()
+        b.record()
+    barrier()
+    launches = _cabi.launch_count()
+    records = _cabi.profile_records()
+    _cabi.profile_enable(False)
+    step_ms = [a.elapsed_time(b) for a, b in ev]
+    total_ms = float(sum(step_ms))
+
+    # ---- e2e: public operator API, host buffers in, results out, inside the timed region
+    x_h = x.cpu().pin_memory()
+    go_h = go.cpu().pin_memory()
+    out_h = torch.empty((n, M), dtype=torch.bfloat16).pin_memory()
+    gx_h = torch.empty((n, C), dtype=torch.bfloat16).pin_memory()
+    gw_h = torch.empty((K, 1, C, M), dtype=torch.bfloat16).pin_memory()
+    index = TigIndex.from_flat(i, j, seg, n_out=n, n_in=n, num_kernel_offsets=K)
+    w_param = w.clone().requires_grad_(True)
+
+    def step_e2e():
+        xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
+        god = go_h.to(dev, non_blocking=True)
+        y = tig_mvmr(w_param, xd, index)
+        w_param.grad = None
+        y.backward(god)
+        if world > 1:
+            dist.all_reduce(w_param.grad)
+        out_h.copy_(y.detach(), non_blocking=True)
+        gx_h.copy_(xd.grad, non_blocking=True)
+        gw_h.copy_(w_param.grad, non_blocking=True)
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in ev2:
+        flush.fill_(1)
+        a.record()
+        step_e2e()
+        b.record()
+    barrier()
+    clock_info = clocks.stop()
+    e2e_ms = float(sum(a.elapsed_time(b) for a, b in ev2))
+    h2d = (x_h.numel() + go_h.numel()) * 2
+    d2h = (out_h.numel() + gx_h.numel() + gw_h.numel()) * 2
+
+    # ---- reduce over ranks: max time, sum of triplets
+    stats = torch.tensor([total_ms, e2e_ms, float(T)], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, e2e_ms, T_all = float(mx[0]), float(mx[1]), float(sm[2])
+    else:
+        T_all = float(T)
+
+    if rank == 0:
+        per_kernel = {}
+        for name, ms in records:
+            per_kernel.setdefault(name, []).append(ms)
+        avg = {name: sum(v) / len(v) for name, v in per_kernel.items()}
+        hbm, peak_kind = _peaks()
+        balg = algorithmic_bytes(T, n, n, C, M, K)
+        label_to_pass = {"mvmr_tc_kernel(fwd)": "fwd", "mvmr_tc_kernel(dgrad)": "dgrad", "vvor_tc_kernel": "wgrad",
+                         "mvmr_sorted_kernel(fwd)": "fwd", "mvmr_sorted_kernel(dgrad)": "dgrad",
+                         "vvor_sorted_kernel": "wgrad"}
+        dominant = max(avg, key=avg.get)
+        dom_pass = label_to_pass[dominant]
+        achieved = balg[dom_pass] / (avg[dominant] * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm, "unit": "GB/s",
+                    "frac": achieved / hbm, "peak_source": peak_kind, "traffic": None,
+                    "algorithmic_bytes": balg[dom_pass], "kernel_ms": avg[dominant],
+                    "all_kernels_ms": avg,
+                    "all_passes_frac": {label_to_pass[kname]: balg[label_to_pass[kname]] / (ms * 1e-3) / 1e9 / hbm
+                                        for kname, ms in avg.items()}}
+        per_step_ms = total_ms / args.steps
+        value = T_all / (per_step_ms * 1e-3) / 1e9
+        e2e_value = T_all / (e2e_ms / args.steps * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": per_step_ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "points_per_rank": n, "triplets_rank0": T,
+                       "triplets_per_point": T / n, "l2": "flushed between steps (256 MiB write)",
+                       "collective": "all-reduce of dW per step" if world > 1 else "none"},
+            "tflops": 6.0 * T_all * C * M / (per_step_ms * 1e-3) / 1e12,
+            "roofline": roofline,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": int(launches),
+            "clocks": clock_info,
+        }
+        if world == 1:
+            d = cpu_reference_step_inputs(0, 40000)
+            dt, kind = cpu_reference_step(d)
+            dt2, _ = cpu_reference_step(d)
+            dt = min(dt, dt2)
+            line["cpu_baseline"] = {
+                "value": len(d["i"]) / dt / 1e9, "unit": UNIT, "cores": 1, "kind": kind,
+                "sample": f"spatial crop of {d['n']} points / {len(d['i'])} triplets of the same scene, "
+                          "fp32 operands, fwd+dgrad+wgrad, best of 2",
+                "host_cpus": os.cpu_count()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

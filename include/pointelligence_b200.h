@@ -60,6 +60,17 @@ const char *pcx_last_error_string(void);
  * No counterpart in the reference (its kernels have no device-side waits). */
 int pcx_device_status(unsigned int *h_status, int clear, void *stream);
 
+/* Measurement hooks (no counterpart in the reference, whose benchmarks time
+ * from Python).  pcx_launch_count: kernels this library has launched (reset
+ * when `reset` is non-zero).  pcx_profile_enable(1) makes every sparse entry
+ * point bracket its dominant kernel with CUDA events on the launch stream;
+ * pcx_profile_get returns the kernel's label and duration of record `index`
+ * (it waits for that record's stop event); pcx_profile_enable(0) stops. */
+long long pcx_launch_count(int reset);
+int pcx_profile_enable(int on);
+int pcx_profile_count(void);
+int pcx_profile_get(int index, const char **name, float *milliseconds);
+
 /* ------------------------------------------------------------------------
  * MVMR:  out[scatter[t], g, :] += feat[gather[t], g, :] @ W[tap(t), g]
  *

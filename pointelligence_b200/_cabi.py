@@ -38,6 +38,10 @@ SIGNATURES = {
     "pcx_version": (c_int, []),
     "pcx_last_error_string": (ctypes.c_char_p, []),
     "pcx_device_status": (c_int, [c_void_p, c_int, c_void_p]),
+    "pcx_launch_count": (ctypes.c_longlong, [c_int]),
+    "pcx_profile_enable": (c_int, [c_int]),
+    "pcx_profile_count": (c_int, []),
+    "pcx_profile_get": (c_int, [c_int, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_float)]),
     "pcx_mvmr_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int]),
     "pcx_mvmr": (c_int, [c_void_p] * 7 + [c_int64] * 3 + [c_int] * 7 + [c_void_p, c_size_t, c_void_p]),
     "pcx_vvor_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
@@ -122,6 +126,26 @@ def device_status(clear=True):
     out = ctypes.c_uint(0)
     check(lib().pcx_device_status(ctypes.byref(out), 1 if clear else 0, stream_ptr()))
     return int(out.value)
+
+
+def launch_count(reset=False):
+    """Kernels launched by the library so far (optionally resetting the counter)."""
+    return int(lib().pcx_launch_count(1 if reset else 0))
+
+
+def profile_enable(on=True):
+    check(lib().pcx_profile_enable(1 if on else 0))
+
+
+def profile_records():
+    """[(kernel label, milliseconds)] recorded since ``profile_enable(True)``."""
+    L = lib()
+    out = []
+    for i in range(L.pcx_profile_count()):
+        name, ms = ctypes.c_char_p(), ctypes.c_float()
+        check(L.pcx_profile_get(i, ctypes.byref(name), ctypes.byref(ms)))
+        out.append((name.value.decode(), float(ms.value)))
+    return out
 
 
 # ---------------------------------------------------------------- sparse ----

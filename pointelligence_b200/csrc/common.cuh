@@ -7,11 +7,16 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "../../include/pointelligence_b200.h"
 
 namespace pcx {
 
 void set_error(const char *fmt, ...);
+extern std::atomic<long long> g_launches;               // kernels launched by this library
+void prof_begin(const char *name, cudaStream_t stream); // event timer around a dominant kernel
+void prof_end(cudaStream_t stream);
 
 #define PCX_FAIL(code, ...)            \
     do {                               \
@@ -27,7 +32,11 @@ void set_error(const char *fmt, ...);
                      cudaGetErrorString(_e), __FILE__, __LINE__);               \
     } while (0)
 
-#define PCX_LAUNCH_CHECK() PCX_CUDA(cudaGetLastError())
+#define PCX_LAUNCH_CHECK()            \
+    do {                              \
+        ::pcx::g_launches.fetch_add(1); \
+        PCX_CUDA(cudaGetLastError()); \
+    } while (0)
 
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 

@@ -248,6 +248,7 @@ int mvmr_generic_t(const MvmrArgs &a, cudaStream_t stream) {
     if (a.seg_offs) {
         chunk_table_kernel<<<1, 32, 0, stream>>>(a.seg_offs, a.K, GL, a.chunk_table);
         PCX_LAUNCH_CHECK();
+        prof_begin(a.transpose ? "mvmr_sorted_kernel(dgrad)" : "mvmr_sorted_kernel(fwd)", stream);
         int64_t upper = (a.T + GL - 1) / GL + a.K;
         dim3 grid((unsigned)upper, (unsigned)((outw + GN - 1) / GN), (unsigned)a.G);
         if (a.transpose)
@@ -261,6 +262,7 @@ int mvmr_generic_t(const MvmrArgs &a, cudaStream_t stream) {
         else
             mvmr_unsorted_kernel<T, false><<<blocks, 256, 0, stream>>>(W, feat, a.gather, a.scatter, a.tap_idx, a.acc, a.T, a.G, a.C, a.M);
     }
+    if (a.seg_offs) prof_end(stream);
     PCX_LAUNCH_CHECK();
     return PCX_OK;
 }
@@ -274,11 +276,13 @@ int vvor_generic_t(const VvorArgs &a, cudaStream_t stream) {
         int64_t upper = (a.T + VL - 1) / VL + a.n_o;
         int tiles = ((a.Ma + VT - 1) / VT) * ((a.Cb + VT - 1) / VT);
         dim3 grid((unsigned)upper, (unsigned)tiles, (unsigned)a.G);
+        prof_begin("vvor_sorted_kernel", stream);
         vvor_sorted_kernel<T><<<grid, 256, 0, stream>>>(A, a.a_idx, B, a.b_idx, a.seg_offs, a.chunk_table, a.acc, (int)a.n_o, a.G, a.Ma, a.Cb);
     } else {
         unsigned blocks = (unsigned)((a.T + 7) / 8);
         vvor_unsorted_kernel<T><<<blocks, 256, 0, stream>>>(A, a.a_idx, B, a.b_idx, a.o_idx, a.acc, a.T, a.G, a.Ma, a.Cb);
     }
+    if (a.seg_offs) prof_end(stream);
     PCX_LAUNCH_CHECK();
     return PCX_OK;
 }

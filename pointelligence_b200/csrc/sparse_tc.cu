@@ -469,7 +469,9 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     if (occ < 1) PCX_FAIL(PCX_E_UNSUPPORTED, "mvmr tensor kernel does not fit (smem %zu)", smem);
     int64_t upper = a.T / CH + a.K + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
+    prof_begin(a.transpose ? "mvmr_tc_kernel(dgrad)" : "mvmr_tc_kernel(fwd)", stream);
     mvmr_tc_kernel<<<(unsigned)grid, 128, smem, stream>>>(p);
+    prof_end(stream);
     PCX_LAUNCH_CHECK();
     return PCX_OK;
 }
@@ -492,7 +494,9 @@ int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
     if (occ < 1) PCX_FAIL(PCX_E_UNSUPPORTED, "vvor tensor kernel does not fit (smem %zu)", smem);
     int64_t upper = a.T / CH + a.n_o + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
+    prof_begin("vvor_tc_kernel", stream);
     vvor_tc_kernel<<<(unsigned)grid, 128, smem, stream>>>(p);
+    prof_end(stream);
     PCX_LAUNCH_CHECK();
     return PCX_OK;
 }

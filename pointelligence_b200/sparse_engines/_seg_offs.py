@@ -38,16 +38,27 @@ def kernel_offset_segments_cached(idx_sorted, num_kernel_offsets):
     return seg
 
 
+def _memo(cache, key, idx, compute):
+    """Verdict memo keyed by (address, version, ...) and guarded by a weak
+    reference to the tensor, so a new tensor at a recycled address re-checks."""
+    hit = cache.get(key)
+    if hit is not None:
+        ref, verdict = hit
+        if ref() is idx:
+            return verdict
+        del cache[key]
+    verdict = compute()
+    if len(cache) >= _MAX:
+        cache.pop(next(iter(cache)))
+    cache[key] = (weakref.ref(idx), verdict)
+    return verdict
+
+
 def is_sorted_cached(idx):
     """Memoised non-decreasing check (one device reduction + host sync per new tensor)."""
     key = (idx.data_ptr(), idx._version, idx.numel())
-    hit = _SORTED.get(key)
-    if hit is None:
-        hit = bool((idx[1:] >= idx[:-1]).all().item()) if idx.numel() > 1 else True
-        if len(_SORTED) >= _MAX:
-            _SORTED.pop(next(iter(_SORTED)))
-        _SORTED[key] = hit
-    return hit
+    return _memo(_SORTED, key, idx,
+                 lambda: bool((idx[1:] >= idx[:-1]).all().item()) if idx.numel() > 1 else True)
 
 
 def exact_cover_cached(idx, n):
@@ -55,10 +66,5 @@ def exact_cover_cached(idx, n):
     if idx.numel() != n:
         return False
     key = (idx.data_ptr(), idx._version, n)
-    hit = _COVER.get(key)
-    if hit is None:
-        hit = bool((torch.bincount(idx.long(), minlength=n).max() <= 1).item()) if n else True
-        if len(_COVER) >= _MAX:
-            _COVER.pop(next(iter(_COVER)))
-        _COVER[key] = hit
-    return hit
+    return _memo(_COVER, key, idx,
+                 lambda: bool((torch.bincount(idx.long(), minlength=n).max() <= 1).item()) if n else True)
