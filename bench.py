@@ -203,7 +203,7 @@ def run_ours(args, rank, local_rank, world):
         dist.init_process_group("nccl", device_id=dev)
 
     # ---- scene, rulebook (geometry stage on the GPU), operands
-    pts_np = indoor_scene(N_POINTS, rank)
+    pts_np = indoor_scene(args.points, rank)
     pts = torch.from_numpy(pts_np).to(dev)
     n = pts.shape[0]
     sample = torch.zeros(n, dtype=torch.int64, device=dev)
@@ -212,7 +212,7 @@ def run_ours(args, rank, local_rank, world):
     T = int(i.numel())
     K = KERNEL ** 3
     g = torch.Generator(device=dev).manual_seed(rank + 1)
-    C = M = CHANNELS
+    C = M = args.channels
     bound = 1.0 / np.sqrt(M * K)
     x = torch.randn(n, C, device=dev, generator=g).bfloat16()
     go = torch.randn(n, M, device=dev, generator=g).bfloat16()
@@ -255,41 +255,43 @@ def run_ours(args, rank, local_rank, world):
     step_ms = [a.elapsed_time(b) for a, b in ev]
     total_ms = float(sum(step_ms))
 
-    # ---- e2e: public operator API, host buffers in, results out, inside the timed region
-    x_h = x.cpu().pin_memory()
-    go_h = go.cpu().pin_memory()
-    out_h = torch.empty((n, M), dtype=torch.bfloat16).pin_memory()
-    gx_h = torch.empty((n, C), dtype=torch.bfloat16).pin_memory()
-    gw_h = torch.empty((K, 1, C, M), dtype=torch.bfloat16).pin_memory()
-    index = TigIndex.from_flat(i, j, seg, n_out=n, n_in=n, num_kernel_offsets=K)
-    w_param = w.clone().requires_grad_(True)
+    e2e_ms, h2d, d2h = 0.0, 0, 0
+    if not args.resident_only:
+        # ---- e2e: public operator API, host buffers in, results out, inside the timed region
+        x_h = x.cpu().pin_memory()
+        go_h = go.cpu().pin_memory()
+        out_h = torch.empty((n, M), dtype=torch.bfloat16).pin_memory()
+        gx_h = torch.empty((n, C), dtype=torch.bfloat16).pin_memory()
+        gw_h = torch.empty((K, 1, C, M), dtype=torch.bfloat16).pin_memory()
+        index = TigIndex.from_flat(i, j, seg, n_out=n, n_in=n, num_kernel_offsets=K)
+        w_param = w.clone().requires_grad_(True)
 
-    def step_e2e():
-        xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
-        god = go_h.to(dev, non_blocking=True)
-        y = tig_mvmr(w_param, xd, index)
-        w_param.grad = None
-        y.backward(god)
-        if world > 1:
-            dist.all_reduce(w_param.grad)
-        out_h.copy_(y.detach(), non_blocking=True)
-        gx_h.copy_(xd.grad, non_blocking=True)
-        gw_h.copy_(w_param.grad, non_blocking=True)
+        def step_e2e():
+            xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
+            god = go_h.to(dev, non_blocking=True)
+            y = tig_mvmr(w_param, xd, index)
+            w_param.grad = None
+            y.backward(god)
+            if world > 1:
+                dist.all_reduce(w_param.grad)
+            out_h.copy_(y.detach(), non_blocking=True)
+            gx_h.copy_(xd.grad, non_blocking=True)
+            gw_h.copy_(w_param.grad, non_blocking=True)
 
-    for _ in range(3):
-        step_e2e()
-    barrier()
-    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    for a, b in ev2:
-        flush.fill_(1)
-        a.record()
-        step_e2e()
-        b.record()
-    barrier()
+        for _ in range(3):
+            step_e2e()
+        barrier()
+        ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b in ev2:
+            flush.fill_(1)
+            a.record()
+            step_e2e()
+            b.record()
+        barrier()
+        e2e_ms = float(sum(a.elapsed_time(b) for a, b in ev2))
+        h2d = (x_h.numel() + go_h.numel()) * 2
+        d2h = (out_h.numel() + gx_h.numel() + gw_h.numel()) * 2
     clock_info = clocks.stop()
-    e2e_ms = float(sum(a.elapsed_time(b) for a, b in ev2))
-    h2d = (x_h.numel() + go_h.numel()) * 2
-    d2h = (out_h.numel() + gx_h.numel() + gw_h.numel()) * 2
 
     # ---- reduce over ranks: max time, sum of triplets
     stats = torch.tensor([total_ms, e2e_ms, float(T)], dtype=torch.float64, device=dev)
@@ -323,7 +325,7 @@ def run_ours(args, rank, local_rank, world):
                                         for kname, ms in avg.items()}}
         per_step_ms = total_ms / args.steps
         value = T_all / (per_step_ms * 1e-3) / 1e9
-        e2e_value = T_all / (e2e_ms / args.steps * 1e-3) / 1e9
+        e2e_value = None if args.resident_only else T_all / (e2e_ms / args.steps * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": per_step_ms, "higher_is_better": True,
@@ -334,11 +336,11 @@ def run_ours(args, rank, local_rank, world):
             "tflops": 6.0 * T_all * C * M / (per_step_ms * 1e-3) / 1e12,
             "roofline": roofline,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / args.steps},
+                    "ms_per_step": None if args.resident_only else e2e_ms / args.steps},
             "gpu_launches": int(launches),
             "clocks": clock_info,
         }
-        if world == 1:
+        if world == 1 and not args.resident_only:
             d = cpu_reference_step_inputs(0, 40000)
             dt, kind = cpu_reference_step(d)
             dt2, _ = cpu_reference_step(d)
@@ -360,6 +362,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--points", type=int, default=N_POINTS, help="points per scene (default: the headline 150000)")
+    ap.add_argument("--channels", type=int, default=CHANNELS, help="C_in = C_out (default: the headline 64)")
+    ap.add_argument("--resident-only", action="store_true",
+                    help="skip the host-buffer and CPU legs (for profiler captures of the kernels)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
