@@ -119,6 +119,27 @@ int pcx_vvor(const void *d_a, const int32_t *d_a_idx, const void *d_b,
              int engine, void *d_ws, size_t ws_bytes, void *stream);
 
 /* ------------------------------------------------------------------------
+ * VVOR without a workspace.  No counterpart in the reference.
+ *
+ * Same result as pcx_vvor for triplets sorted by output row (d_seg_offs is
+ * required), but the scratch lives in a fixed __device__ array inside the
+ * library (about 8 MiB per GPU that loads it), so the call allocates nothing
+ * and needs no caller-owned workspace.  For hosts that cannot allocate device
+ * memory where the gradient is needed (allocator callbacks, no-cudaMalloc
+ * regions, plugins that only own the tensors they were handed).
+ * Limits: n_o <= 4095 and n_o*G*Ma*Cb <= pcx_vvor_static_scratch_max_elements()
+ * (2^21); larger shapes return PCX_E_CAPACITY.  The first call with a given
+ * device current looks the array's address up (do it before any stream
+ * capture).  All calls share the array: calls that overlap on the GPU race.
+ */
+size_t pcx_vvor_static_scratch_max_elements(void);
+int pcx_vvor_static_scratch(const void *d_a, const int32_t *d_a_idx, const void *d_b,
+                            const int32_t *d_b_idx, const int64_t *d_seg_offs,
+                            void *d_out, int64_t T, int64_t n_a, int64_t n_b,
+                            int64_t n_o, int G, int Ma, int Cb, int dtype,
+                            void *stream);
+
+/* ------------------------------------------------------------------------
  * Tap bookkeeping.
  * pcx_seg_offs: seg[k] = first position with value >= k in a sorted int32
  *   array (sparse_engines/_seg_offs.py:21-44, kernel_offset_segments).

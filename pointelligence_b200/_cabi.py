@@ -46,6 +46,8 @@ SIGNATURES = {
     "pcx_mvmr": (c_int, [c_void_p] * 7 + [c_int64] * 3 + [c_int] * 7 + [c_void_p, c_size_t, c_void_p]),
     "pcx_vvor_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
     "pcx_vvor": (c_int, [c_void_p] * 7 + [c_int64] * 4 + [c_int] * 5 + [c_void_p, c_size_t, c_void_p]),
+    "pcx_vvor_static_scratch_max_elements": (c_size_t, []),
+    "pcx_vvor_static_scratch": (c_int, [c_void_p] * 6 + [c_int64] * 4 + [c_int] * 4 + [c_void_p]),
     "pcx_seg_offs": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "pcx_expand_taps": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "pcx_radius_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),
@@ -196,6 +198,25 @@ def vvor(a, a_idx, b, b_idx, seg_offs, o_idx, n_o, engine=ENGINE_AUTO):
         check(L.pcx_vvor(ptr(a), ptr(a_idx), ptr(b), ptr(b_idx), ptr(seg_offs), ptr(o_idx), ptr(out),
                          a_idx.numel(), a.shape[0], b.shape[0], n_o, G, Ma, Cb, code, engine,
                          ptr(ws), ws.numel(), stream_ptr()))
+    return out
+
+
+def vvor_static_scratch(a, a_idx, b, b_idx, seg_offs, out):
+    """VVOR into the caller's ``out`` (n_o, G, Ma, Cb) using the library's built-in
+    scratch array: nothing is allocated by the call, here or in the library.
+    For embedders that cannot allocate device memory at the call site; see
+    ``pcx_vvor_static_scratch`` in the header for the size limits and for the
+    rule that calls must not overlap on the GPU."""
+    require_cuda(a, b, a_idx, b_idx, seg_offs, out)
+    code = dtype_code(a.dtype)
+    for t in (a, b, out):
+        assert t.is_contiguous() and t.dtype == a.dtype
+    assert a_idx.dtype == torch.int32 and b_idx.dtype == torch.int32 and seg_offs.dtype == torch.int64
+    n_o, G, Ma, Cb = out.shape
+    with torch.cuda.device(a.device):
+        check(lib().pcx_vvor_static_scratch(ptr(a), ptr(a_idx), ptr(b), ptr(b_idx), ptr(seg_offs), ptr(out),
+                                            a_idx.numel(), a.shape[0], b.shape[0], n_o, G, Ma, Cb, code,
+                                            stream_ptr()))
     return out
 
 
