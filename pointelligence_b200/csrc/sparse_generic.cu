@@ -12,15 +12,36 @@
 
 namespace pcx {
 
+// cum[k] = number of L-triplet chunks in the taps before k (one block, any K)
 __global__ void chunk_table_kernel(const int64_t *__restrict__ seg, int K, int L, int32_t *cum) {
-    if (threadIdx.x == 0 && blockIdx.x == 0) {
-        int32_t run = 0;
-        for (int k = 0; k < K; ++k) {
-            cum[k] = run;
-            run += (int32_t)((seg[k + 1] - seg[k] + L - 1) / L);
+    __shared__ int32_t warp_sums[32];
+    __shared__ int32_t carry;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    if (tid == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < K; base += blockDim.x) {
+        int k = base + tid;
+        int32_t v = k < K ? (int32_t)((seg[k + 1] - seg[k] + L - 1) / L) : 0;
+        int32_t inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += n;
         }
-        cum[K] = run;
+        if (lane == 31) warp_sums[warp] = inc;
+        __syncthreads();
+        int32_t before = carry;
+        for (int w = 0; w < warp; ++w) before += warp_sums[w];
+        if (k < K) cum[k] = before + inc - v;
+        __syncthreads();
+        if (tid == 0) {
+            int32_t t = carry;
+            for (int w = 0; w < nwarps; ++w) t += warp_sums[w];
+            carry = t;
+        }
+        __syncthreads();
     }
+    if (tid == 0) cum[K] = carry;
 }
 
 namespace {
@@ -246,7 +267,7 @@ int mvmr_generic_t(const MvmrArgs &a, cudaStream_t stream) {
     const T *W = (const T *)a.weight, *feat = (const T *)a.feat;
     const int outw = a.transpose ? a.C : a.M;
     if (a.seg_offs) {
-        chunk_table_kernel<<<1, 32, 0, stream>>>(a.seg_offs, a.K, GL, a.chunk_table);
+        chunk_table_kernel<<<1, 128, 0, stream>>>(a.seg_offs, a.K, GL, a.chunk_table);
         PCX_LAUNCH_CHECK();
         prof_begin(a.transpose ? "mvmr_sorted_kernel(dgrad)" : "mvmr_sorted_kernel(fwd)", stream);
         int64_t upper = (a.T + GL - 1) / GL + a.K;
@@ -271,7 +292,7 @@ template <typename T>
 int vvor_generic_t(const VvorArgs &a, cudaStream_t stream) {
     const T *A = (const T *)a.a, *B = (const T *)a.b;
     if (a.seg_offs) {
-        chunk_table_kernel<<<1, 32, 0, stream>>>(a.seg_offs, (int)a.n_o, VL, a.chunk_table);
+        chunk_table_kernel<<<1, 128, 0, stream>>>(a.seg_offs, (int)a.n_o, VL, a.chunk_table);
         PCX_LAUNCH_CHECK();
         int64_t upper = (a.T + VL - 1) / VL + a.n_o;
         int tiles = ((a.Ma + VT - 1) / VT) * ((a.Cb + VT - 1) / VT);

@@ -136,34 +136,54 @@ __device__ __forceinline__ uint32_t instr_desc(int fmt /*0 f16, 1 bf16*/, int m,
     return d;
 }
 
+// Position of a CTA in the chunk sequence; the bounds of the current tap are
+// kept in registers and reloaded only when the chunk index leaves the tap.
 struct ChunkCursor {
     int tap;
-    __device__ __forceinline__ void seek(const int32_t *__restrict__ cum, int K, int chunk) {
+    int cum_lo, cum_hi;
+    int64_t seg_lo, seg_hi;
+    __device__ __forceinline__ void load(const int32_t *__restrict__ cum, const int64_t *__restrict__ seg) {
+        cum_lo = cum[tap], cum_hi = cum[tap + 1];
+        seg_lo = seg[tap], seg_hi = seg[tap + 1];
+    }
+    __device__ __forceinline__ void seek(const int32_t *__restrict__ cum, const int64_t *__restrict__ seg,
+                                         int K, int chunk) {
         int lo = 0, hi = K;
         while (hi - lo > 1) {
             int mid = (lo + hi) >> 1;
             if (cum[mid] <= chunk) lo = mid; else hi = mid;
         }
         tap = lo;
+        load(cum, seg);
     }
-    __device__ __forceinline__ void advance(const int32_t *__restrict__ cum, int K, int chunk) {
+    __device__ __forceinline__ void advance(const int32_t *__restrict__ cum, const int64_t *__restrict__ seg,
+                                            int K, int chunk) {
+        if (chunk < cum_hi) return;
         while (tap + 1 < K && cum[tap + 1] <= chunk) ++tap;
+        load(cum, seg);
     }
+    __device__ __forceinline__ int64_t first(int chunk) const { return seg_lo + (int64_t)(chunk - cum_lo) * CH; }
+    __device__ __forceinline__ int rows(int chunk) const {
+        int64_t left = seg_hi - first(chunk);
+        return (int)(left < CH ? left : CH);
+    }
+    __device__ __forceinline__ bool last_of_tap(int chunk) const { return chunk + 1 >= cum_hi; }
 };
 
-// Gather `rows` rows of `width` 2-byte channels into a swizzled tile.
-// Rows past `rows` are zero-filled when ZERO_TAIL (needed when the row index is
-// the contraction index), left untouched otherwise.
+// Gather `rows` rows of `width` 2-byte channels into a swizzled tile; the row
+// indices were staged in shared memory beforehand so that the copy loop issues
+// cp.async back to back.  Rows past `rows` are zero-filled when ZERO_TAIL
+// (needed when the row index is the contraction index), untouched otherwise.
 template <bool ZERO_TAIL>
 __device__ __forceinline__ void gather_tile(uint32_t tile, const uint16_t *__restrict__ src,
-                                            const int32_t *__restrict__ idx, int64_t t0, int rows, int width,
-                                            int tid, int nthreads) {
+                                            const int32_t *s_idx, int rows, int width, int tid, int nthreads) {
     const int cpr = width >> 3;  // 16-byte pieces per row
-    for (int e = tid; e < CH * cpr; e += nthreads) {
+    const int total = (ZERO_TAIL ? CH : rows) * cpr;
+    for (int e = tid; e < total; e += nthreads) {
         int r = e / cpr, ch = e - r * cpr;
         uint32_t dst = tile + (uint32_t)(ch >> 3) * BLK_BYTES + (uint32_t)r * 128 + (uint32_t)(((ch & 7) ^ (r & 7)) << 4);
         if (r < rows) {
-            cp_async16(dst, src + (int64_t)idx[t0 + r] * width + ch * 8);
+            cp_async16(dst, src + (int64_t)s_idx[r] * width + ch * 8);
         } else if (ZERO_TAIL) {
             asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0) : "memory");
         }
@@ -185,7 +205,7 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t s_bar;
     __shared__ uint32_t s_tmem;
-    __shared__ int32_t s_scatter[CH];
+    __shared__ int32_t s_scatter[CH], s_gather[CH];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int kb = (p.inw + 63) >> 6;
@@ -214,14 +234,17 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     int loaded_tap = -1;
     bool alive = true;
     ChunkCursor cur;
-    if (lo < hi) cur.seek(p.cum, p.K, lo);
+    if (lo < hi) cur.seek(p.cum, p.seg, p.K, lo);
 
     for (int chunk = lo; chunk < hi && alive; ++chunk) {
-        cur.advance(p.cum, p.K, chunk);
+        cur.advance(p.cum, p.seg, p.K, chunk);
         const int tap = cur.tap;
-        const int64_t t0 = p.seg[tap] + (int64_t)(chunk - p.cum[tap]) * CH;
-        const int64_t left = p.seg[tap + 1] - t0;
-        const int rows = (int)(left < CH ? left : CH);
+        const int64_t t0 = cur.first(chunk);
+        const int rows = cur.rows(chunk);
+        if (tid < rows) {
+            s_gather[tid] = p.gather[t0 + tid];
+            s_scatter[tid] = p.scatter[t0 + tid];
+        }
 
         if (tap != loaded_tap) {  // weight tile of this tap, rows = output channels
             const uint16_t *w = p.bmat + (int64_t)tap * p.outw * p.inw;
@@ -233,8 +256,8 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
             }
             loaded_tap = tap;
         }
-        gather_tile<false>(a_tile, p.feat, p.gather, t0, rows, p.inw, tid, 128);
-        if (tid < rows) s_scatter[tid] = p.scatter[t0 + tid];
+        __syncthreads();
+        gather_tile<false>(a_tile, p.feat, s_gather, rows, p.inw, tid, 128);
         cp_async_wait_all();
         fence_async_smem();
         __syncthreads();
@@ -300,6 +323,7 @@ __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t s_bar;
     __shared__ uint32_t s_tmem;
+    __shared__ int32_t s_ia[CH], s_ib[CH];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int row_tiles = (p.Ma + 127) >> 7;
@@ -328,18 +352,21 @@ __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
     bool alive = true;
     bool fresh = true;  // next MMA starts a new accumulation
     ChunkCursor cur;
-    if (lo < hi) cur.seek(p.cum, p.n_o, lo);
+    if (lo < hi) cur.seek(p.cum, p.seg, p.n_o, lo);
 
     for (int chunk = lo; chunk < hi && alive; ++chunk) {
-        cur.advance(p.cum, p.n_o, chunk);
+        cur.advance(p.cum, p.seg, p.n_o, chunk);
         const int o = cur.tap;
-        const int64_t t0 = p.seg[o] + (int64_t)(chunk - p.cum[o]) * CH;
-        const int64_t left = p.seg[o + 1] - t0;
-        const int rows = (int)(left < CH ? left : CH);
-        const bool last_of_tap = (chunk + 1 == hi) || (chunk + 1 >= p.cum[o + 1]);
-
-        gather_tile<true>(a_tile, p.a, p.a_idx, t0, rows, p.Ma, tid, 128);
-        gather_tile<true>(b_tile, p.b, p.b_idx, t0, rows, p.Cb, tid, 128);
+        const int64_t t0 = cur.first(chunk);
+        const int rows = cur.rows(chunk);
+        const bool last_of_tap = (chunk + 1 == hi) || cur.last_of_tap(chunk);
+        if (tid < rows) {
+            s_ia[tid] = p.a_idx[t0 + tid];
+            s_ib[tid] = p.b_idx[t0 + tid];
+        }
+        __syncthreads();
+        gather_tile<true>(a_tile, p.a, s_ia, rows, p.Ma, tid, 128);
+        gather_tile<true>(b_tile, p.b, s_ib, rows, p.Cb, tid, 128);
         cp_async_wait_all();
         fence_async_smem();
         __syncthreads();
@@ -412,8 +439,18 @@ uint32_t pow2_cols(int n) {
     return c;
 }
 
-// Dynamic shared memory so that at most 512 / ncols CTAs share an SM (their
-// TMEM allocations then always fit).
+// CTAs per SM: bounded by shared memory (227 KiB usable, 1 KiB reserved per
+// CTA), by TMEM (512 columns) and by registers / warp slots.
+int ctas_per_sm(size_t smem, uint32_t ncols) {
+    int by_smem = (int)((size_t)232448 / (smem + 1024));
+    int by_tmem = (int)(512 / ncols);
+    int occ = by_smem < by_tmem ? by_smem : by_tmem;
+    if (occ > 8) occ = 8;
+    return occ < 1 ? 1 : occ;
+}
+
+// Dynamic shared memory padded so that at most 512 / ncols CTAs share an SM
+// (their TMEM allocations then always fit).
 size_t pad_for_tmem(size_t smem, uint32_t ncols) {
     size_t max_ctas = 512 / ncols;
     size_t floor_bytes = (size_t)232448 / (max_ctas + 1) + 1024;
@@ -453,7 +490,7 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
         PCX_LAUNCH_CHECK();
         bmat = (const uint16_t *)a.weight_t;
     }
-    chunk_table_kernel<<<1, 32, 0, stream>>>(a.seg_offs, a.K, CH, a.chunk_table);
+    chunk_table_kernel<<<1, 128, 0, stream>>>(a.seg_offs, a.K, CH, a.chunk_table);
     PCX_LAUNCH_CHECK();
     MvmrTcParams p;
     p.bmat = bmat, p.feat = (const uint16_t *)a.feat, p.gather = a.gather, p.scatter = a.scatter;
@@ -463,10 +500,10 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     const int kb = (inw + 63) / 64;
     size_t smem = 1024 + (size_t)kb * BLK_BYTES + (size_t)kb * outw * 128 + (size_t)CH * STAGE_PITCH * 4;
     smem = pad_for_tmem(smem, p.ncols);
+    if (smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "mvmr tensor kernel does not fit (smem %zu)", smem);
     PCX_CUDA(cudaFuncSetAttribute(mvmr_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int occ = 0;
-    PCX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, mvmr_tc_kernel, 128, smem));
-    if (occ < 1) PCX_FAIL(PCX_E_UNSUPPORTED, "mvmr tensor kernel does not fit (smem %zu)", smem);
+    PCX_CUDA(cudaFuncSetAttribute(mvmr_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    const int occ = ctas_per_sm(smem, p.ncols);
     int64_t upper = a.T / CH + a.K + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
     prof_begin(a.transpose ? "mvmr_tc_kernel(dgrad)" : "mvmr_tc_kernel(fwd)", stream);
@@ -477,7 +514,7 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
 }
 
 int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
-    chunk_table_kernel<<<1, 32, 0, stream>>>(a.seg_offs, (int)a.n_o, CH, a.chunk_table);
+    chunk_table_kernel<<<1, 128, 0, stream>>>(a.seg_offs, (int)a.n_o, CH, a.chunk_table);
     PCX_LAUNCH_CHECK();
     VvorTcParams p;
     p.a = (const uint16_t *)a.a, p.b = (const uint16_t *)a.b, p.a_idx = a.a_idx, p.b_idx = a.b_idx;
@@ -488,10 +525,10 @@ int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
     size_t smem = 1024 + (size_t)(row_tiles * 2) * BLK_BYTES + (size_t)((a.Cb + 63) / 64) * BLK_BYTES +
                   (size_t)CH * STAGE_PITCH * 4;
     smem = pad_for_tmem(smem, p.ncols);
+    if (smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "vvor tensor kernel does not fit (smem %zu)", smem);
     PCX_CUDA(cudaFuncSetAttribute(vvor_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int occ = 0;
-    PCX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, vvor_tc_kernel, 128, smem));
-    if (occ < 1) PCX_FAIL(PCX_E_UNSUPPORTED, "vvor tensor kernel does not fit (smem %zu)", smem);
+    PCX_CUDA(cudaFuncSetAttribute(vvor_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    const int occ = ctas_per_sm(smem, p.ncols);
     int64_t upper = a.T / CH + a.n_o + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
     prof_begin("vvor_tc_kernel", stream);
