@@ -11,7 +11,6 @@ namespace {
 struct MvmrWs {
     float *acc;
     int32_t *chunk_table;
-    void *weight_t;
 };
 
 size_t carve_mvmr(void *ws, int64_t n_out, int K, int G, int C, int M, int transpose, int dtype, MvmrWs *out) {
@@ -20,7 +19,6 @@ size_t carve_mvmr(void *ws, int64_t n_out, int K, int G, int C, int M, int trans
     const int outw = transpose ? C : M;
     w.acc = c.take<float>(dtype == PCX_F32 ? 1 : (size_t)n_out * G * outw);
     w.chunk_table = c.take<int32_t>((size_t)K + 1);
-    w.weight_t = c.take<char>((!transpose && dtype != PCX_F32) ? (size_t)K * G * C * M * 2 : 1);
     if (out) *out = w;
     return c.off;
 }
@@ -87,7 +85,7 @@ int pcx_mvmr(const void *d_weight, const void *d_feat, const int32_t *d_gather, 
     a.weight = d_weight, a.feat = d_feat, a.gather = d_gather, a.scatter = d_scatter;
     a.seg_offs = d_seg_offs, a.tap_idx = d_tap_idx;
     a.acc = dtype == PCX_F32 ? (float *)d_out : w.acc;
-    a.chunk_table = w.chunk_table, a.weight_t = w.weight_t;
+    a.chunk_table = w.chunk_table;
     a.T = T, a.n_feat = n_feat, a.n_out = n_out;
     a.K = K, a.G = G, a.C = C, a.M = M, a.transpose = transpose ? 1 : 0, a.dtype = dtype;
     PCX_CUDA(cudaMemsetAsync(a.acc, 0, (size_t)out_elems * sizeof(float), stream));

@@ -12,8 +12,7 @@ struct MvmrArgs {
     const int64_t *seg_offs; // (K+1) or null
     const int32_t *tap_idx;  // (T) when seg_offs is null
     float *acc;              // (n_out, G*outw) fp32, zeroed by the caller
-    int32_t *chunk_table;    // (K+1) scratch
-    void *weight_t;          // (K,M,C) scratch for the forward tensor path
+    int32_t *chunk_table;    // (K+1) scratch of the CUDA-core engine
     int64_t T, n_feat, n_out;
     int K, G, C, M, transpose, dtype;
 };

@@ -8,18 +8,23 @@
 //   smem tile  = [64-channel block][row][128 bytes], 16-byte pieces XOR-swizzled
 //                with (row & 7)  (the SWIZZLE_128B canonical layout)
 //
-//   MVMR   D[128 triplets x N] = A[128 x Kc] * B[N x Kc]^T
+//   MVMR   D[128 triplets x N] = A[128 x Kc] * B[Kc x N]
 //          A = gathered feature rows   (K-major: a row is contiguous along Kc)
-//          B = weight tile of the tap  (K-major rows of the output channel)
+//          B = W[tap] exactly as stored, (C, M) row-major: read MN-major in the
+//              forward (its rows are the contraction index) and K-major in the
+//              input gradient (its rows are the output channels)
+//          two A tiles alternate: the gather of the next chunk overlaps the
+//          multiply and the scatter of the current one
 //          epilogue: TMEM -> registers -> padded smem -> per-row run-merged
 //          red.global.add.f32 (128 contiguous bytes per warp instruction).
 //   VVOR   D[Ma x Cb] += X[t x Ma]^T * G[t x Cb], t = triplets of the chunk
 //          both operands MN-major (a gathered row is contiguous along M / N,
 //          the triplet index is the contraction), accumulated in TMEM over all
-//          chunks of a tap and flushed once per (CTA, tap).
+//          chunks of a tap and flushed once per (CTA, tap); a ring of 2-4
+//          operand buffers keeps the next gathers in flight.
 //
 // One thread issues tcgen05.mma; completion is signalled with tcgen05.commit on
-// an mbarrier.  Every wait is bounded: after the limit the kernel raises a flag
+// an mbarrier.  Every wait is bounded (one second): after the limit the kernel raises a flag
 // in the status word, frees its TMEM and returns.
 #include "sparse_kernels.cuh"
 
@@ -31,8 +36,8 @@ namespace {
 
 constexpr int CH = 128;            // triplets per chunk
 constexpr int BLK_BYTES = CH * 128; // one 64-channel block of a 128-row tile
-constexpr int STAGE_PITCH = 33;    // floats per row of the epilogue staging tile
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr int STAGE_PITCH = 36;    // floats per row of the epilogue staging tile (16-byte aligned rows)
+constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;  // one second per wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -64,10 +69,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait; false (and the status flag) when the limit is hit.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: gives up after WAIT_LIMIT_NS of wall time (checked every 64
+// polls), raises `flag` in the status word and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned flag) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it)
+    for (int it = 0; it < 64; ++it)
         if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        for (int it = 0; it < 64; ++it)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+    }
     atomicOr(&g_device_status, flag);
     return false;
 }
@@ -138,16 +155,17 @@ __device__ __forceinline__ uint32_t instr_desc(int fmt /*0 f16, 1 bf16*/, int m,
 
 // Position of a CTA in the chunk sequence; the bounds of the current tap are
 // kept in registers and reloaded only when the chunk index leaves the tap.
+// The cumulative chunk table lives in shared memory (built by every CTA from
+// the segment offsets), so no separate kernel and no global table are needed.
 struct ChunkCursor {
     int tap;
     int cum_lo, cum_hi;
     int64_t seg_lo, seg_hi;
-    __device__ __forceinline__ void load(const int32_t *__restrict__ cum, const int64_t *__restrict__ seg) {
+    __device__ __forceinline__ void load(const int32_t *cum, const int64_t *__restrict__ seg) {
         cum_lo = cum[tap], cum_hi = cum[tap + 1];
         seg_lo = seg[tap], seg_hi = seg[tap + 1];
     }
-    __device__ __forceinline__ void seek(const int32_t *__restrict__ cum, const int64_t *__restrict__ seg,
-                                         int K, int chunk) {
+    __device__ __forceinline__ void seek(const int32_t *cum, const int64_t *__restrict__ seg, int K, int chunk) {
         int lo = 0, hi = K;
         while (hi - lo > 1) {
             int mid = (lo + hi) >> 1;
@@ -156,8 +174,7 @@ struct ChunkCursor {
         tap = lo;
         load(cum, seg);
     }
-    __device__ __forceinline__ void advance(const int32_t *__restrict__ cum, const int64_t *__restrict__ seg,
-                                            int K, int chunk) {
+    __device__ __forceinline__ void advance(const int32_t *cum, const int64_t *__restrict__ seg, int K, int chunk) {
         if (chunk < cum_hi) return;
         while (tap + 1 < K && cum[tap + 1] <= chunk) ++tap;
         load(cum, seg);
@@ -170,6 +187,37 @@ struct ChunkCursor {
     __device__ __forceinline__ bool last_of_tap(int chunk) const { return chunk + 1 >= cum_hi; }
 };
 
+constexpr int MAX_TAPS_SMEM = 1024;  // taps whose chunk table fits the shared-memory copy
+
+// cum[k] = chunks of CH triplets in the taps before k; all threads of the CTA call this.
+__device__ __forceinline__ void build_chunk_table(const int64_t *__restrict__ seg, int K, int32_t *cum,
+                                                  int32_t *warp_sums) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    int32_t carry = 0;
+    for (int base = 0; base < K; base += blockDim.x) {
+        int k = base + tid;
+        int32_t v = k < K ? (int32_t)((seg[k + 1] - seg[k] + CH - 1) / CH) : 0;
+        int32_t inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += n;
+        }
+        if (lane == 31) warp_sums[warp] = inc;
+        __syncthreads();
+        int32_t before = carry, all = carry;
+        for (int w = 0; w < nwarps; ++w) {
+            if (w < warp) before += warp_sums[w];
+            all += warp_sums[w];
+        }
+        if (k < K) cum[k] = before + inc - v;
+        carry = all;
+        __syncthreads();
+    }
+    if (tid == 0) cum[K] = carry;
+    __syncthreads();
+}
+
 // Gather `rows` rows of `width` 2-byte channels into a swizzled tile; the row
 // indices were staged in shared memory beforehand so that the copy loop issues
 // cp.async back to back.  Rows past `rows` are zero-filled when ZERO_TAIL
@@ -178,8 +226,25 @@ template <bool ZERO_TAIL>
 __device__ __forceinline__ void gather_tile(uint32_t tile, const uint16_t *__restrict__ src,
                                             const int32_t *s_idx, int rows, int width, int tid, int nthreads) {
     const int cpr = width >> 3;  // 16-byte pieces per row
-    const int total = (ZERO_TAIL ? CH : rows) * cpr;
-    for (int e = tid; e < total; e += nthreads) {
+    const int rmax = ZERO_TAIL ? CH : rows;
+    if ((cpr & (cpr - 1)) == 0) {
+        // power-of-two row length: a thread keeps its 16-byte column and walks down the rows
+        const int sh = __ffs(cpr) - 1;
+        const int ch = tid & (cpr - 1), rpp = nthreads >> sh;
+        const uint32_t dcol = tile + (uint32_t)(ch >> 3) * BLK_BYTES;
+        const uint16_t *scol = src + ch * 8;
+#pragma unroll 4
+        for (int r = tid >> sh; r < rmax; r += rpp) {
+            const uint32_t dst = dcol + (uint32_t)r * 128 + (uint32_t)(((ch ^ r) & 7) << 4);
+            if (r < rows) {
+                cp_async16(dst, scol + (int64_t)s_idx[r] * width);
+            } else if (ZERO_TAIL) {
+                asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0) : "memory");
+            }
+        }
+        return;
+    }
+    for (int e = tid; e < rmax * cpr; e += nthreads) {
         int r = e / cpr, ch = e - r * cpr;
         uint32_t dst = tile + (uint32_t)(ch >> 3) * BLK_BYTES + (uint32_t)r * 128 + (uint32_t)(((ch & 7) ^ (r & 7)) << 4);
         if (r < rows) {
@@ -190,29 +255,54 @@ __device__ __forceinline__ void gather_tile(uint32_t tile, const uint16_t *__res
     }
 }
 
+// Epilogue helper: the warp's 32 accumulator rows x 32 columns go from
+// registers to a padded shared-memory tile (row pitch 36 floats keeps both the
+// 16-byte row stores and the column reads free of bank conflicts).
+__device__ __forceinline__ void stage_rows(float *my, int lane, const float *v) {
+    float4 *row = reinterpret_cast<float4 *>(my + lane * STAGE_PITCH);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) row[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 struct MvmrTcParams {
-    const uint16_t *bmat;   // (K, outw, inw) rows of output channel, contraction contiguous
+    const uint16_t *weight;  // (K, C, M) as stored
     const uint16_t *feat;
     const int32_t *gather, *scatter;
     const int64_t *seg;
-    const int32_t *cum;
     float *acc;
-    int K, inw, outw, fmt;
+    int K, C, M, transpose, fmt, nbuf;
     uint32_t ncols;
 };
 
+// A-tile ring of two: the gather of chunk c+1 is in flight while chunk c is
+// multiplied and scattered; the indices of chunk c+2 are already on their way
+// into registers.  When two A tiles do not fit next to the weight tile
+// (nbuf == 1) the next gather is issued as soon as the multiply has finished,
+// so it still overlaps the scatter.
 __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t s_bar;
     __shared__ uint32_t s_tmem;
-    __shared__ int32_t s_scatter[CH], s_gather[CH];
+    __shared__ __align__(16) int32_t s_scatter[2][CH];
+    __shared__ int32_t s_gather[2][CH];
+    __shared__ int32_t s_cum[MAX_TAPS_SMEM + 1];
+    __shared__ int32_t s_warp_sums[4];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int inw = p.transpose ? p.M : p.C, outw = p.transpose ? p.C : p.M;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int kb = (p.inw + 63) >> 6;
-    const uint32_t a_tile = base;
-    const uint32_t b_tile = a_tile + (uint32_t)kb * BLK_BYTES;
-    const uint32_t b_blk = (uint32_t)p.outw * 128;
-    float *stage = reinterpret_cast<float *>(smem_raw + (b_tile + (uint32_t)kb * b_blk - smem_u32(smem_raw)));
+    const int kb = (inw + 63) >> 6;
+    const uint32_t a_bytes = (uint32_t)kb * BLK_BYTES;
+    const uint32_t a_tile0 = base;
+    const uint32_t b_tile = a_tile0 + (uint32_t)p.nbuf * a_bytes;
+    const bool two = p.nbuf == 2;
+    // the weight tile is W[tap] as stored: C rows of M channels, 64-channel blocks
+    const int wb = (p.M + 63) >> 6;
+    const uint32_t w_blk = (uint32_t)p.C * 128;
+    float *stage = reinterpret_cast<float *>(smem_raw + (b_tile + (uint32_t)wb * w_blk - smem_u32(smem_raw)));
     const uint32_t bar = smem_u32(&s_bar);
 
     if (tid == 0) {
@@ -220,54 +310,92 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(&s_tmem), p.ncols);
+    build_chunk_table(p.seg, p.K, s_cum, s_warp_sums);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
 
-    const int total = p.cum[p.K];
+    const int total = s_cum[p.K];
     const int per = (total + gridDim.x - 1) / gridDim.x;
     const int lo = blockIdx.x * per, hi = min(total, lo + per);
-    const uint32_t idesc = instr_desc(p.fmt, 128, p.outw, 0, 0);
-    const int ksteps = p.inw >> 4;
+    // forward: B = W[tap] read MN-major (its rows are the contraction index c);
+    // input gradient: B = W[tap] read K-major (its rows are the output index c)
+    const uint32_t idesc = instr_desc(p.fmt, 128, outw, 0, p.transpose ? 0 : 1);
+    const int ksteps = inw >> 4;
     uint32_t phase = 0;
     int loaded_tap = -1;
     bool alive = true;
-    ChunkCursor cur;
-    if (lo < hi) cur.seek(p.cum, p.seg, p.K, lo);
+
+    auto load_weight = [&](int tap) {
+        const uint16_t *w = p.weight + (int64_t)tap * p.C * p.M;
+        const int cpr = p.M >> 3;
+        for (int e = tid; e < p.C * cpr; e += 128) {
+            int c = e / cpr, ch = e - c * cpr;
+            uint32_t dst = b_tile + (uint32_t)(ch >> 3) * w_blk + (uint32_t)c * 128 + (uint32_t)(((ch & 7) ^ (c & 7)) << 4);
+            cp_async16(dst, w + (int64_t)c * p.M + ch * 8);
+        }
+    };
+
+    ChunkCursor c0, c1, c2;  // chunk, chunk + 1, chunk + 2
+    int pre_g = 0, pre_s = 0;
+    if (lo < hi) {
+        c0.seek(s_cum, p.seg, p.K, lo);
+        c1 = c0;
+        c2 = c0;
+        const int rows = c0.rows(lo);
+        if (tid < rows) {
+            s_gather[0][tid] = p.gather[c0.first(lo) + tid];
+            s_scatter[0][tid] = p.scatter[c0.first(lo) + tid];
+        }
+        load_weight(c0.tap);
+        loaded_tap = c0.tap;
+        __syncthreads();
+        gather_tile<false>(a_tile0, p.feat, s_gather[0], rows, inw, tid, 128);
+        cp_async_commit();
+        if (lo + 1 < hi) {
+            c1.advance(s_cum, p.seg, p.K, lo + 1);
+            c2 = c1;
+            if (tid < c1.rows(lo + 1)) {
+                pre_g = p.gather[c1.first(lo + 1) + tid];
+                pre_s = p.scatter[c1.first(lo + 1) + tid];
+            }
+        }
+    }
 
     for (int chunk = lo; chunk < hi && alive; ++chunk) {
-        cur.advance(p.cum, p.seg, p.K, chunk);
-        const int tap = cur.tap;
-        const int64_t t0 = cur.first(chunk);
-        const int rows = cur.rows(chunk);
-        if (tid < rows) {
-            s_gather[tid] = p.gather[t0 + tid];
-            s_scatter[tid] = p.scatter[t0 + tid];
-        }
-
-        if (tap != loaded_tap) {  // weight tile of this tap, rows = output channels
-            const uint16_t *w = p.bmat + (int64_t)tap * p.outw * p.inw;
-            const int cpr = p.inw >> 3;
-            for (int e = tid; e < p.outw * cpr; e += 128) {
-                int n = e / cpr, ch = e - n * cpr;
-                uint32_t dst = b_tile + (uint32_t)(ch >> 3) * b_blk + (uint32_t)n * 128 + (uint32_t)(((ch & 7) ^ (n & 7)) << 4);
-                cp_async16(dst, w + (int64_t)n * p.inw + ch * 8);
-            }
-            loaded_tap = tap;
+        const int b = (chunk - lo) & 1;
+        const int rows = c0.rows(chunk);
+        const bool have_next = chunk + 1 < hi;
+        const int rows_next = have_next ? c1.rows(chunk + 1) : 0;
+        if (have_next && tid < rows_next) {
+            s_gather[b ^ 1][tid] = pre_g;
+            s_scatter[b ^ 1][tid] = pre_s;
         }
         __syncthreads();
-        gather_tile<false>(a_tile, p.feat, s_gather, rows, p.inw, tid, 128);
-        cp_async_wait_all();
+        if (have_next && two)
+            gather_tile<false>(a_tile0 + (uint32_t)(b ^ 1) * a_bytes, p.feat, s_gather[b ^ 1], rows_next, inw, tid, 128);
+        cp_async_commit();
+        if (chunk + 2 < hi) {
+            c2.advance(s_cum, p.seg, p.K, chunk + 2);
+            if (tid < c2.rows(chunk + 2)) {
+                pre_g = p.gather[c2.first(chunk + 2) + tid];
+                pre_s = p.scatter[c2.first(chunk + 2) + tid];
+            }
+        }
+        if (two) cp_async_wait<1>();  // everything but the gather just issued has landed
+        else cp_async_wait<0>();
         fence_async_smem();
         __syncthreads();
 
         if (tid == 0) {
             tc_fence_after();
+            const uint32_t a_tile = a_tile0 + (two ? (uint32_t)b * a_bytes : 0u);
             for (int s = 0; s < ksteps; ++s) {
-                uint32_t off = (uint32_t)(s >> 2);
-                uint64_t ad = smem_desc(a_tile + off * BLK_BYTES + (uint32_t)(s & 3) * 32, 16, 1024);
-                uint64_t bd = smem_desc(b_tile + off * b_blk + (uint32_t)(s & 3) * 32, 16, 1024);
+                uint64_t ad = smem_desc(a_tile + (uint32_t)(s >> 2) * BLK_BYTES + (uint32_t)(s & 3) * 32, 16, 1024);
+                uint64_t bd = p.transpose
+                                  ? smem_desc(b_tile + (uint32_t)(s >> 2) * w_blk + (uint32_t)(s & 3) * 32, 16, 1024)
+                                  : smem_desc(b_tile + (uint32_t)s * 2048, w_blk, 1024);
                 tc_mma(tmem, ad, bd, idesc, s > 0 ? 1u : 0u);
             }
             tc_commit(bar);
@@ -275,36 +403,58 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
         alive = mbar_wait(bar, phase, 1u);
         phase ^= 1u;
         tc_fence_after();
+        // the weight tile is free now: fetch the next tap's if the next chunk needs it
+        if (have_next && c1.tap != loaded_tap) {
+            load_weight(c1.tap);
+            loaded_tap = c1.tap;
+            cp_async_commit();
+        }
+        if (have_next && !two) {  // single A tile: it is free as well
+            gather_tile<false>(a_tile0, p.feat, s_gather[b ^ 1], rows_next, inw, tid, 128);
+            cp_async_commit();
+        }
         if (alive) {
             float *my = stage + (warp * 32) * STAGE_PITCH;
-            for (int c0 = 0; c0 < p.outw; c0 += 32) {
+            const int32_t *sc = s_scatter[b];
+            for (int col0 = 0; col0 < outw; col0 += 32) {
                 float v[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) my[lane * STAGE_PITCH + c] = v[c];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)col0, v);
+                stage_rows(my, lane, v);
                 __syncwarp();
-                const bool col_ok = c0 + lane < p.outw;
+                const bool col_ok = col0 + lane < outw;
+                float *dst_col = p.acc + col0 + lane;
                 float run = 0.f;
                 int cur_row = -1;
                 const int rend = min(32, rows - warp * 32);
-                for (int r = 0; r < rend; ++r) {
-                    int dst = s_scatter[warp * 32 + r];
-                    float x = my[r * STAGE_PITCH + lane];
-                    if (dst != cur_row) {
-                        if (cur_row >= 0 && col_ok) atomicAdd(p.acc + (int64_t)cur_row * p.outw + c0 + lane, run);
-                        cur_row = dst;
-                        run = x;
-                    } else {
-                        run += x;
+                for (int r4 = 0; r4 < rend; r4 += 4) {
+                    const int4 d4 = *reinterpret_cast<const int4 *>(sc + warp * 32 + r4);
+                    const int d[4] = {d4.x, d4.y, d4.z, d4.w};
+                    float x[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) x[q] = my[(r4 + q) * STAGE_PITCH + lane];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (r4 + q < rend) {
+                            if (d[q] != cur_row) {
+                                if (cur_row >= 0 && col_ok) atomicAdd(dst_col + (int64_t)cur_row * outw, run);
+                                cur_row = d[q];
+                                run = x[q];
+                            } else {
+                                run += x[q];
+                            }
+                        }
                     }
                 }
-                if (cur_row >= 0 && col_ok) atomicAdd(p.acc + (int64_t)cur_row * p.outw + c0 + lane, run);
+                if (cur_row >= 0 && col_ok) atomicAdd(dst_col + (int64_t)cur_row * outw, run);
                 __syncwarp();
             }
         }
+        c0 = c1;
+        c1 = c2;
         tc_fence_before();
         __syncthreads();
     }
+    cp_async_wait<0>();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, p.ncols);
 }
@@ -313,25 +463,31 @@ struct VvorTcParams {
     const uint16_t *a, *b;  // (n_a, Ma), (n_b, Cb)
     const int32_t *a_idx, *b_idx;
     const int64_t *seg;
-    const int32_t *cum;
     float *acc;             // (n_o, Ma, Cb)
-    int n_o, Ma, Cb, fmt;
+    int n_o, Ma, Cb, fmt, stages;
     uint32_t ncols;
 };
 
+constexpr int MAX_STAGES = 4;
+
+// Ring of `stages` operand buffers: the gathers of the next stages-1 chunks are
+// in flight while the tensor core contracts the current one (a single stage,
+// for the widest channel counts, degenerates to gather-then-multiply).
 __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t s_bar;
     __shared__ uint32_t s_tmem;
-    __shared__ int32_t s_ia[CH], s_ib[CH];
+    __shared__ int32_t s_ia[MAX_STAGES][CH], s_ib[MAX_STAGES][CH];
+    __shared__ int32_t s_cum[MAX_TAPS_SMEM + 1];
+    __shared__ int32_t s_warp_sums[4];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int row_tiles = (p.Ma + 127) >> 7;
-    const int ablk = row_tiles * 2;           // 64-channel blocks held for A (padded to 128 rows per tile)
+    const int ablk = (p.Ma + 63) >> 6;  // blocks actually filled; an odd count borrows the next block as padding
     const int bblk = (p.Cb + 63) >> 6;
-    const uint32_t a_tile = base;
-    const uint32_t b_tile = a_tile + (uint32_t)ablk * BLK_BYTES;
-    float *stage = reinterpret_cast<float *>(smem_raw + (b_tile + (uint32_t)bblk * BLK_BYTES - smem_u32(smem_raw)));
+    const uint32_t buf_bytes = (uint32_t)(ablk + bblk) * BLK_BYTES;
+    const int NS = p.stages;
+    float *stage = reinterpret_cast<float *>(smem_raw + (base + (uint32_t)NS * buf_bytes - smem_u32(smem_raw)));
     const uint32_t bar = smem_u32(&s_bar);
 
     if (tid == 0) {
@@ -339,40 +495,111 @@ __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(&s_tmem), p.ncols);
+    build_chunk_table(p.seg, p.n_o, s_cum, s_warp_sums);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
 
-    const int total = p.cum[p.n_o];
+    const int total = s_cum[p.n_o];
     const int per = (total + gridDim.x - 1) / gridDim.x;
     const int lo = blockIdx.x * per, hi = min(total, lo + per);
     const uint32_t idesc = instr_desc(p.fmt, 128, p.Cb, 1, 1);
     uint32_t phase = 0;
     bool alive = true;
     bool fresh = true;  // next MMA starts a new accumulation
-    ChunkCursor cur;
-    if (lo < hi) cur.seek(p.cum, p.seg, p.n_o, lo);
 
-    for (int chunk = lo; chunk < hi && alive; ++chunk) {
-        cur.advance(p.cum, p.seg, p.n_o, chunk);
-        const int o = cur.tap;
-        const int64_t t0 = cur.first(chunk);
-        const int rows = cur.rows(chunk);
-        const bool last_of_tap = (chunk + 1 == hi) || cur.last_of_tap(chunk);
+    ChunkCursor cur, pre;  // chunk being multiplied; chunk whose indices are being fetched
+    int pre_a = 0, pre_b = 0;
+    auto issue_gather = [&](const ChunkCursor &cc, int chunk, int slot, bool from_regs) {
+        const int rows = cc.rows(chunk);
         if (tid < rows) {
-            s_ia[tid] = p.a_idx[t0 + tid];
-            s_ib[tid] = p.b_idx[t0 + tid];
+            s_ia[slot][tid] = from_regs ? pre_a : p.a_idx[cc.first(chunk) + tid];
+            s_ib[slot][tid] = from_regs ? pre_b : p.b_idx[cc.first(chunk) + tid];
         }
         __syncthreads();
-        gather_tile<true>(a_tile, p.a, s_ia, rows, p.Ma, tid, 128);
-        gather_tile<true>(b_tile, p.b, s_ib, rows, p.Cb, tid, 128);
-        cp_async_wait_all();
+        const uint32_t a_tile = base + (uint32_t)slot * buf_bytes;
+        gather_tile<true>(a_tile, p.a, s_ia[slot], rows, p.Ma, tid, 128);
+        gather_tile<true>(a_tile + (uint32_t)ablk * BLK_BYTES, p.b, s_ib[slot], rows, p.Cb, tid, 128);
+    };
+    auto flush_tap = [&](int o) {
+        float *my = stage + (warp * 32) * STAGE_PITCH;
+        float *dst_o = p.acc + (int64_t)o * p.Ma * p.Cb;
+        for (int rt = 0; rt < row_tiles; ++rt) {
+            const int m_base = rt * 128 + warp * 32;
+            for (int c0 = 0; c0 < p.Cb; c0 += 32) {
+                float v[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(rt * p.Cb + c0), v);
+                stage_rows(my, lane, v);
+                __syncwarp();
+                if (c0 + lane < p.Cb) {
+                    const int rend = min(32, p.Ma - m_base);
+                    for (int r = 0; r < rend; ++r)
+                        atomicAdd(dst_o + (int64_t)(m_base + r) * p.Cb + c0 + lane, my[r * STAGE_PITCH + lane]);
+                }
+                __syncwarp();
+            }
+        }
+    };
+
+    if (lo < hi) {
+        cur.seek(s_cum, p.seg, p.n_o, lo);
+        pre = cur;
+        for (int s = 0; s < NS - 1; ++s) {  // prologue: chunks lo .. lo+NS-2
+            if (lo + s < hi) {
+                pre.advance(s_cum, p.seg, p.n_o, lo + s);
+                issue_gather(pre, lo + s, s, false);
+            }
+            cp_async_commit();
+        }
+        if (lo + NS - 1 < hi) {
+            pre.advance(s_cum, p.seg, p.n_o, lo + NS - 1);
+            if (tid < pre.rows(lo + NS - 1)) {
+                pre_a = p.a_idx[pre.first(lo + NS - 1) + tid];
+                pre_b = p.b_idx[pre.first(lo + NS - 1) + tid];
+            }
+        }
+    }
+    int pending_tap = -1;  // tap whose last MMA has been issued but whose sums are still in TMEM
+
+    for (int chunk = lo; chunk < hi && alive; ++chunk) {
+        const int n = chunk - lo;
+        // the MMA of the previous chunk must be done before its buffer is refilled
+        if (n > 0) {
+            alive = mbar_wait(bar, phase, 2u);
+            phase ^= 1u;
+            tc_fence_after();
+            if (alive && pending_tap >= 0) {
+                flush_tap(pending_tap);
+                pending_tap = -1;
+                fresh = true;
+                tc_fence_before();
+            }
+        }
+        const int refill = chunk + NS - 1;
+        if (refill < hi) issue_gather(pre, refill, (n + NS - 1) % NS, true);
+        cp_async_commit();
+        if (refill + 1 < hi) {
+            pre.advance(s_cum, p.seg, p.n_o, refill + 1);
+            if (tid < pre.rows(refill + 1)) {
+                pre_a = p.a_idx[pre.first(refill + 1) + tid];
+                pre_b = p.b_idx[pre.first(refill + 1) + tid];
+            }
+        }
+        // chunk `chunk` has landed once at most NS-1 newer groups are pending
+        if (NS == 1) cp_async_wait<0>();
+        else if (NS == 2) cp_async_wait<1>();
+        else if (NS == 3) cp_async_wait<2>();
+        else cp_async_wait<3>();
         fence_async_smem();
         __syncthreads();
 
-        if (tid == 0) {
+        cur.advance(s_cum, p.seg, p.n_o, chunk);
+        const int rows = cur.rows(chunk);
+        if (tid == 0 && alive) {
             tc_fence_after();
+            const uint32_t a_tile = base + (uint32_t)(n % NS) * buf_bytes;
+            const uint32_t b_tile = a_tile + (uint32_t)ablk * BLK_BYTES;
             const int ksteps = (rows + 15) >> 4;
             for (int rt = 0; rt < row_tiles; ++rt) {
                 for (int s = 0; s < ksteps; ++s) {
@@ -384,53 +611,17 @@ __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
             tc_commit(bar);
         }
         fresh = false;
-        alive = mbar_wait(bar, phase, 2u);
-        phase ^= 1u;
-        tc_fence_after();
-        if (alive && last_of_tap) {
-            float *my = stage + (warp * 32) * STAGE_PITCH;
-            float *dst_o = p.acc + (int64_t)o * p.Ma * p.Cb;
-            for (int rt = 0; rt < row_tiles; ++rt) {
-                const int m_base = rt * 128 + warp * 32;
-                for (int c0 = 0; c0 < p.Cb; c0 += 32) {
-                    float v[32];
-                    tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(rt * p.Cb + c0), v);
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) my[lane * STAGE_PITCH + c] = v[c];
-                    __syncwarp();
-                    if (c0 + lane < p.Cb) {
-                        const int rend = min(32, p.Ma - m_base);
-                        for (int r = 0; r < rend; ++r)
-                            atomicAdd(dst_o + (int64_t)(m_base + r) * p.Cb + c0 + lane, my[r * STAGE_PITCH + lane]);
-                    }
-                    __syncwarp();
-                }
-            }
-            fresh = true;
-        }
-        tc_fence_before();
-        __syncthreads();
+        if ((chunk + 1 == hi) || cur.last_of_tap(chunk)) pending_tap = cur.tap;
     }
+    if (lo < hi && alive) {
+        alive = mbar_wait(bar, phase, 2u);
+        tc_fence_after();
+        if (alive && pending_tap >= 0) flush_tap(pending_tap);
+    }
+    cp_async_wait<0>();
+    tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, p.ncols);
-}
-
-__global__ void transpose_weight_kernel(const uint16_t *__restrict__ w, uint16_t *__restrict__ wt, int K, int C, int M) {
-    // wt[k][m][c] = w[k][c][m]
-    __shared__ uint16_t tile[32][33];
-    const int k = blockIdx.z;
-    const int c0 = blockIdx.y * 32, m0 = blockIdx.x * 32;
-    const uint16_t *src = w + (int64_t)k * C * M;
-    uint16_t *dst = wt + (int64_t)k * C * M;
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        int c = c0 + r, m = m0 + threadIdx.x;
-        if (c < C && m < M) tile[r][threadIdx.x] = src[(int64_t)c * M + m];
-    }
-    __syncthreads();
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        int m = m0 + r, c = c0 + threadIdx.x;
-        if (c < C && m < M) dst[(int64_t)m * C + c] = tile[threadIdx.x][r];
-    }
 }
 
 uint32_t pow2_cols(int n) {
@@ -463,7 +654,7 @@ bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 bool mvmr_tensor_supported(const MvmrArgs &a) {
     if (a.dtype != PCX_F16 && a.dtype != PCX_BF16) return false;
-    if (a.G != 1 || !a.seg_offs || a.T <= 0) return false;
+    if (a.G != 1 || !a.seg_offs || a.T <= 0 || a.K > MAX_TAPS_SMEM) return false;
     const int inw = a.transpose ? a.M : a.C, outw = a.transpose ? a.C : a.M;
     if (inw % 16 || outw % 16 || inw < 16 || outw < 16 || inw > 256 || outw > 256) return false;
     if (!aligned16(a.weight) || !aligned16(a.feat)) return false;
@@ -473,37 +664,34 @@ bool mvmr_tensor_supported(const MvmrArgs &a) {
 
 bool vvor_tensor_supported(const VvorArgs &a) {
     if (a.dtype != PCX_F16 && a.dtype != PCX_BF16) return false;
-    if (a.G != 1 || !a.seg_offs || a.T <= 0) return false;
+    if (a.G != 1 || !a.seg_offs || a.T <= 0 || a.n_o > MAX_TAPS_SMEM) return false;
     if (a.Ma % 16 || a.Cb % 16 || a.Ma < 16 || a.Cb < 16 || a.Ma > 256 || a.Cb > 256) return false;
     if (((a.Ma + 127) / 128) * a.Cb > 512) return false;
     if (!aligned16(a.a) || !aligned16(a.b)) return false;
-    if (a.n_o > 65536) return false;
     return true;
 }
 
 int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     const int inw = a.transpose ? a.M : a.C, outw = a.transpose ? a.C : a.M;
-    const uint16_t *bmat = (const uint16_t *)a.weight;
-    if (!a.transpose) {  // forward: rows of the B tile are output channels -> (K, M, C)
-        dim3 grid((a.M + 31) / 32, (a.C + 31) / 32, a.K), block(32, 8);
-        transpose_weight_kernel<<<grid, block, 0, stream>>>((const uint16_t *)a.weight, (uint16_t *)a.weight_t, a.K, a.C, a.M);
-        PCX_LAUNCH_CHECK();
-        bmat = (const uint16_t *)a.weight_t;
-    }
-    chunk_table_kernel<<<1, 128, 0, stream>>>(a.seg_offs, a.K, CH, a.chunk_table);
-    PCX_LAUNCH_CHECK();
     MvmrTcParams p;
-    p.bmat = bmat, p.feat = (const uint16_t *)a.feat, p.gather = a.gather, p.scatter = a.scatter;
-    p.seg = a.seg_offs, p.cum = a.chunk_table, p.acc = a.acc;
-    p.K = a.K, p.inw = inw, p.outw = outw, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
+    p.weight = (const uint16_t *)a.weight, p.feat = (const uint16_t *)a.feat;
+    p.gather = a.gather, p.scatter = a.scatter, p.seg = a.seg_offs, p.acc = a.acc;
+    p.K = a.K, p.C = a.C, p.M = a.M, p.transpose = a.transpose, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
     p.ncols = pow2_cols(outw);
-    const int kb = (inw + 63) / 64;
-    size_t smem = 1024 + (size_t)kb * BLK_BYTES + (size_t)kb * outw * 128 + (size_t)CH * STAGE_PITCH * 4;
+    const int kb = (inw + 63) / 64, wb = (a.M + 63) / 64;
+    const size_t static_smem = 6656;  // index rings, chunk table, barrier
+    const size_t rest = 1024 + (size_t)wb * a.C * 128 + (size_t)CH * STAGE_PITCH * 4;
+    // One A tile: it is free again as soon as the multiply has finished, so the
+    // next gather still overlaps the scatter, and more CTAs fit on an SM.
+    p.nbuf = 1;
+    if (const char *e = getenv("PCX_MVMR_NBUF"))
+        if (atoi(e) == 2 && rest + 2 * (size_t)kb * BLK_BYTES + static_smem <= 232448 - 1024) p.nbuf = 2;
+    size_t smem = rest + (size_t)p.nbuf * kb * BLK_BYTES;
     smem = pad_for_tmem(smem, p.ncols);
-    if (smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "mvmr tensor kernel does not fit (smem %zu)", smem);
+    if (smem + static_smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "mvmr tensor kernel does not fit (smem %zu)", smem);
     PCX_CUDA(cudaFuncSetAttribute(mvmr_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     PCX_CUDA(cudaFuncSetAttribute(mvmr_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-    const int occ = ctas_per_sm(smem, p.ncols);
+    const int occ = ctas_per_sm(smem + static_smem, p.ncols);
     int64_t upper = a.T / CH + a.K + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
     prof_begin(a.transpose ? "mvmr_tc_kernel(dgrad)" : "mvmr_tc_kernel(fwd)", stream);
@@ -514,21 +702,36 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
 }
 
 int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
-    chunk_table_kernel<<<1, 128, 0, stream>>>(a.seg_offs, (int)a.n_o, CH, a.chunk_table);
-    PCX_LAUNCH_CHECK();
     VvorTcParams p;
     p.a = (const uint16_t *)a.a, p.b = (const uint16_t *)a.b, p.a_idx = a.a_idx, p.b_idx = a.b_idx;
-    p.seg = a.seg_offs, p.cum = a.chunk_table, p.acc = a.acc;
+    p.seg = a.seg_offs, p.acc = a.acc;
     p.n_o = (int)a.n_o, p.Ma = a.Ma, p.Cb = a.Cb, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
     const int row_tiles = (a.Ma + 127) / 128;
     p.ncols = pow2_cols(row_tiles * a.Cb);
-    size_t smem = 1024 + (size_t)(row_tiles * 2) * BLK_BYTES + (size_t)((a.Cb + 63) / 64) * BLK_BYTES +
-                  (size_t)CH * STAGE_PITCH * 4;
+    const size_t buf = (size_t)((a.Ma + 63) / 64 + (a.Cb + 63) / 64) * BLK_BYTES;
+    const size_t fixed = 1024 + (size_t)CH * STAGE_PITCH * 4;
+    const size_t static_smem = 10240;  // index rings, chunk table, barrier
+    // deepest ring (1..4 stages) that fits
+    int stages = 1;
+    for (int ns = MAX_STAGES; ns >= 1; --ns) {
+        size_t need = fixed + ns * buf + static_smem + 1024;
+        size_t budget = (ns * buf <= 100 * 1024) ? (232448 / 2) : 232448;
+        if (need <= budget) {
+            stages = ns;
+            break;
+        }
+    }
+    if (const char *e = getenv("PCX_VVOR_STAGES")) {
+        int want = atoi(e);
+        if (want >= 1 && want < stages) stages = want;
+    }
+    p.stages = stages;
+    size_t smem = fixed + stages * buf;
     smem = pad_for_tmem(smem, p.ncols);
-    if (smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "vvor tensor kernel does not fit (smem %zu)", smem);
+    if (smem + static_smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "vvor tensor kernel does not fit (smem %zu)", smem);
     PCX_CUDA(cudaFuncSetAttribute(vvor_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     PCX_CUDA(cudaFuncSetAttribute(vvor_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-    const int occ = ctas_per_sm(smem, p.ncols);
+    const int occ = ctas_per_sm(smem + static_smem, p.ncols);
     int64_t upper = a.T / CH + a.n_o + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
     prof_begin("vvor_tc_kernel", stream);
