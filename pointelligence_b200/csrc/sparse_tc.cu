@@ -126,6 +126,46 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 16 accumulator rows x 64 columns: thread T receives, for every group n of 8
+// columns, row T/4 (registers 4n, 4n+1) and row T/4 + 8 (registers 4n+2, 4n+3)
+// at columns 8n + 2*(T%4) + {0,1}.  Four neighbouring lanes therefore own 32
+// contiguous bytes of one row, and a two-float vector reduction per lane
+// touches whole 32-byte sectors without a shared-memory transpose.
+__device__ __forceinline__ void tmem_ld_16x64(uint32_t taddr, float *v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void red_add_v2(float *addr, float a, float b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+// Adds one 16 x 64 accumulator block to fp32 rows in global memory.
+//   row_a / row_b: destination rows of this thread's two accumulator rows (-1 = skip)
+//   width: row length of the destination; col0: first column of the block
+__device__ __forceinline__ void scatter_block(float *dst, int64_t row_a, int64_t row_b, int width, int col0,
+                                              int lane, const float *v) {
+    const int c = col0 + 2 * (lane & 3);
+    float *pa = dst + row_a * width + c, *pb = dst + row_b * width + c;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        if (col0 + 8 * n < width) {
+            if (row_a >= 0) red_add_v2(pa + 8 * n, v[4 * n], v[4 * n + 1]);
+            if (row_b >= 0) red_add_v2(pb + 8 * n, v[4 * n + 2], v[4 * n + 3]);
+        }
+    }
+}
+
 // Shared-memory matrix descriptor, SWIZZLE_128B, descriptor version 1.
 //   K-major operand : lbo = 1 (unused), sbo = bytes between 8-row groups
 //   MN-major operand: lbo = bytes between 64-element blocks along M/N,
@@ -302,7 +342,6 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     // the weight tile is W[tap] as stored: C rows of M channels, 64-channel blocks
     const int wb = (p.M + 63) >> 6;
     const uint32_t w_blk = (uint32_t)p.C * 128;
-    float *stage = reinterpret_cast<float *>(smem_raw + (b_tile + (uint32_t)wb * w_blk - smem_u32(smem_raw)));
     const uint32_t bar = smem_u32(&s_bar);
 
     if (tid == 0) {
@@ -414,39 +453,17 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
             cp_async_commit();
         }
         if (alive) {
-            float *my = stage + (warp * 32) * STAGE_PITCH;
             const int32_t *sc = s_scatter[b];
-            for (int col0 = 0; col0 < outw; col0 += 32) {
-                float v[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)col0, v);
-                stage_rows(my, lane, v);
-                __syncwarp();
-                const bool col_ok = col0 + lane < outw;
-                float *dst_col = p.acc + col0 + lane;
-                float run = 0.f;
-                int cur_row = -1;
-                const int rend = min(32, rows - warp * 32);
-                for (int r4 = 0; r4 < rend; r4 += 4) {
-                    const int4 d4 = *reinterpret_cast<const int4 *>(sc + warp * 32 + r4);
-                    const int d[4] = {d4.x, d4.y, d4.z, d4.w};
-                    float x[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) x[q] = my[(r4 + q) * STAGE_PITCH + lane];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        if (r4 + q < rend) {
-                            if (d[q] != cur_row) {
-                                if (cur_row >= 0 && col_ok) atomicAdd(dst_col + (int64_t)cur_row * outw, run);
-                                cur_row = d[q];
-                                run = x[q];
-                            } else {
-                                run += x[q];
-                            }
-                        }
-                    }
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                const int ra = warp * 32 + half * 16 + (lane >> 2), rb = ra + 8;
+                const int64_t da = ra < rows ? sc[ra] : -1, db = rb < rows ? sc[rb] : -1;
+                if (warp * 32 + half * 16 >= rows) break;  // warp-uniform: nothing left in this chunk
+                for (int col0 = 0; col0 < outw; col0 += 64) {
+                    float v[32];
+                    tmem_ld_16x64(tmem + ((uint32_t)(warp * 32 + half * 16) << 16) + (uint32_t)col0, v);
+                    scatter_block(p.acc, da, db, outw, col0, lane, v);
                 }
-                if (cur_row >= 0 && col_ok) atomicAdd(dst_col + (int64_t)cur_row * outw, run);
-                __syncwarp();
             }
         }
         c0 = c1;
@@ -487,7 +504,6 @@ __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
     const int bblk = (p.Cb + 63) >> 6;
     const uint32_t buf_bytes = (uint32_t)(ablk + bblk) * BLK_BYTES;
     const int NS = p.stages;
-    float *stage = reinterpret_cast<float *>(smem_raw + (base + (uint32_t)NS * buf_bytes - smem_u32(smem_raw)));
     const uint32_t bar = smem_u32(&s_bar);
 
     if (tid == 0) {
@@ -523,21 +539,19 @@ __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
         gather_tile<true>(a_tile + (uint32_t)ablk * BLK_BYTES, p.b, s_ib[slot], rows, p.Cb, tid, 128);
     };
     auto flush_tap = [&](int o) {
-        float *my = stage + (warp * 32) * STAGE_PITCH;
         float *dst_o = p.acc + (int64_t)o * p.Ma * p.Cb;
         for (int rt = 0; rt < row_tiles; ++rt) {
-            const int m_base = rt * 128 + warp * 32;
-            for (int c0 = 0; c0 < p.Cb; c0 += 32) {
-                float v[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(rt * p.Cb + c0), v);
-                stage_rows(my, lane, v);
-                __syncwarp();
-                if (c0 + lane < p.Cb) {
-                    const int rend = min(32, p.Ma - m_base);
-                    for (int r = 0; r < rend; ++r)
-                        atomicAdd(dst_o + (int64_t)(m_base + r) * p.Cb + c0 + lane, my[r * STAGE_PITCH + lane]);
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                const int m0 = rt * 128 + warp * 32 + half * 16;
+                if (m0 >= p.Ma) break;
+                const int ma = m0 + (lane >> 2), mb = ma + 8;
+                const int64_t da = ma < p.Ma ? ma : -1, db = mb < p.Ma ? mb : -1;
+                for (int c0 = 0; c0 < p.Cb; c0 += 64) {
+                    float v[32];
+                    tmem_ld_16x64(tmem + ((uint32_t)(warp * 32 + half * 16) << 16) + (uint32_t)(rt * p.Cb + c0), v);
+                    scatter_block(dst_o, da, db, p.Cb, c0, lane, v);
                 }
-                __syncwarp();
             }
         }
     };
@@ -666,7 +680,7 @@ bool vvor_tensor_supported(const VvorArgs &a) {
     if (a.dtype != PCX_F16 && a.dtype != PCX_BF16) return false;
     if (a.G != 1 || !a.seg_offs || a.T <= 0 || a.n_o > MAX_TAPS_SMEM) return false;
     if (a.Ma % 16 || a.Cb % 16 || a.Ma < 16 || a.Cb < 16 || a.Ma > 256 || a.Cb > 256) return false;
-    if (((a.Ma + 127) / 128) * a.Cb > 512) return false;
+    if (((a.Ma + 127) / 128 - 1) * a.Cb + (a.Cb + 63) / 64 * 64 > 512) return false;
     if (!aligned16(a.a) || !aligned16(a.b)) return false;
     return true;
 }
@@ -677,10 +691,10 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     p.weight = (const uint16_t *)a.weight, p.feat = (const uint16_t *)a.feat;
     p.gather = a.gather, p.scatter = a.scatter, p.seg = a.seg_offs, p.acc = a.acc;
     p.K = a.K, p.C = a.C, p.M = a.M, p.transpose = a.transpose, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
-    p.ncols = pow2_cols(outw);
+    p.ncols = pow2_cols((outw + 63) / 64 * 64);  // the epilogue reads blocks of 64 columns
     const int kb = (inw + 63) / 64, wb = (a.M + 63) / 64;
     const size_t static_smem = 6656;  // index rings, chunk table, barrier
-    const size_t rest = 1024 + (size_t)wb * a.C * 128 + (size_t)CH * STAGE_PITCH * 4;
+    const size_t rest = 1024 + (size_t)wb * a.C * 128;
     // One A tile: it is free again as soon as the multiply has finished, so the
     // next gather still overlaps the scatter, and more CTAs fit on an SM.
     p.nbuf = 1;
@@ -707,23 +721,24 @@ int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
     p.seg = a.seg_offs, p.acc = a.acc;
     p.n_o = (int)a.n_o, p.Ma = a.Ma, p.Cb = a.Cb, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
     const int row_tiles = (a.Ma + 127) / 128;
-    p.ncols = pow2_cols(row_tiles * a.Cb);
+    p.ncols = pow2_cols((row_tiles - 1) * a.Cb + (a.Cb + 63) / 64 * 64);  // flushed in blocks of 64 columns
     const size_t buf = (size_t)((a.Ma + 63) / 64 + (a.Cb + 63) / 64) * BLK_BYTES;
-    const size_t fixed = 1024 + (size_t)CH * STAGE_PITCH * 4;
+    const size_t fixed = 1024;
     const size_t static_smem = 10240;  // index rings, chunk table, barrier
-    // deepest ring (1..4 stages) that fits
-    int stages = 1;
+    // One stage by default: measured on B200, more resident CTAs hide the gather
+    // latency better than a deeper ring inside fewer CTAs (PCX_VVOR_STAGES raises it).
+    int stages = 1, max_fit = 1;
     for (int ns = MAX_STAGES; ns >= 1; --ns) {
         size_t need = fixed + ns * buf + static_smem + 1024;
         size_t budget = (ns * buf <= 100 * 1024) ? (232448 / 2) : 232448;
         if (need <= budget) {
-            stages = ns;
+            max_fit = ns;
             break;
         }
     }
     if (const char *e = getenv("PCX_VVOR_STAGES")) {
         int want = atoi(e);
-        if (want >= 1 && want < stages) stages = want;
+        if (want >= 1 && want <= max_fit) stages = want;
     }
     p.stages = stages;
     size_t smem = fixed + stages * buf;
