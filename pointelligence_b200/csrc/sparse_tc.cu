@@ -295,14 +295,16 @@ __device__ __forceinline__ void gather_tile(uint32_t tile, const uint16_t *__res
     }
 }
 
-// Epilogue helper: the warp's 32 accumulator rows x 32 columns go from
-// registers to a padded shared-memory tile (row pitch 36 floats keeps both the
-// 16-byte row stores and the column reads free of bank conflicts).
-__device__ __forceinline__ void stage_rows(float *my, int lane, const float *v) {
-    float4 *row = reinterpret_cast<float4 *>(my + lane * STAGE_PITCH);
-#pragma unroll
-    for (int c = 0; c < 8; ++c) row[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+// Scatter through the copy engine: every accumulator row is parked in shared
+// memory and handed to one bulk reduction (fp32 add into global memory), so the
+// scatter neither occupies the load/store pipeline nor needs one instruction
+// per 32-byte piece.
+__device__ __forceinline__ void bulk_reduce_add_f32(float *gdst, uint32_t ssrc, uint32_t bytes) {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                 ::"l"(gdst), "r"(ssrc), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -314,7 +316,7 @@ struct MvmrTcParams {
     const int32_t *gather, *scatter;
     const int64_t *seg;
     float *acc;
-    int K, C, M, transpose, fmt, nbuf;
+    int K, C, M, transpose, fmt, nbuf, slab;  // slab: columns parked per bulk reduction (32 or 64)
     uint32_t ncols;
 };
 
@@ -343,6 +345,9 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     const int wb = (p.M + 63) >> 6;
     const uint32_t w_blk = (uint32_t)p.C * 128;
     const uint32_t bar = smem_u32(&s_bar);
+    // per-warp parking area of the scatter: 32 rows of slab floats, rows padded by 16 bytes
+    const uint32_t park_pitch = (uint32_t)p.slab * 4 + 16;
+    const uint32_t park = b_tile + (uint32_t)wb * w_blk + (uint32_t)warp * 32 * park_pitch;
 
     if (tid == 0) {
         mbar_init(bar, 1);
@@ -452,18 +457,26 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
             gather_tile<false>(a_tile0, p.feat, s_gather[b ^ 1], rows_next, inw, tid, 128);
             cp_async_commit();
         }
-        if (alive) {
-            const int32_t *sc = s_scatter[b];
-#pragma unroll 1
-            for (int half = 0; half < 2; ++half) {
-                const int ra = warp * 32 + half * 16 + (lane >> 2), rb = ra + 8;
-                const int64_t da = ra < rows ? sc[ra] : -1, db = rb < rows ? sc[rb] : -1;
-                if (warp * 32 + half * 16 >= rows) break;  // warp-uniform: nothing left in this chunk
-                for (int col0 = 0; col0 < outw; col0 += 64) {
+        if (alive && warp * 32 < rows) {
+            const int row = warp * 32 + lane;
+            const bool row_ok = row < rows;
+            float *dst_row = p.acc + (int64_t)(row_ok ? s_scatter[b][row] : 0) * outw;
+            const uint32_t my_park = park + (uint32_t)lane * park_pitch;
+            for (int col0 = 0; col0 < outw; col0 += p.slab) {
+                bulk_wait_read();  // the previous reductions have read this warp's parking area
+                __syncwarp();
+                for (int c32 = 0; c32 < p.slab; c32 += 32) {
                     float v[32];
-                    tmem_ld_16x64(tmem + ((uint32_t)(warp * 32 + half * 16) << 16) + (uint32_t)col0, v);
-                    scatter_block(p.acc, da, db, outw, col0, lane, v);
+                    tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(col0 + c32), v);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(my_park + (uint32_t)(c32 + 4 * q) * 4),
+                                     "f"(v[4 * q]), "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
                 }
+                fence_async_smem();
+                const int cols = min(p.slab, outw - col0);
+                if (row_ok) bulk_reduce_add_f32(dst_row + col0, my_park, (uint32_t)cols * 4);
+                bulk_commit();
             }
         }
         c0 = c1;
@@ -472,6 +485,7 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
         __syncthreads();
     }
     cp_async_wait<0>();
+    bulk_wait_read();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, p.ncols);
 }
@@ -691,10 +705,13 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     p.weight = (const uint16_t *)a.weight, p.feat = (const uint16_t *)a.feat;
     p.gather = a.gather, p.scatter = a.scatter, p.seg = a.seg_offs, p.acc = a.acc;
     p.K = a.K, p.C = a.C, p.M = a.M, p.transpose = a.transpose, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
-    p.ncols = pow2_cols((outw + 63) / 64 * 64);  // the epilogue reads blocks of 64 columns
+    p.ncols = pow2_cols((outw + 31) / 32 * 32);  // the epilogue reads blocks of 32 columns
     const int kb = (inw + 63) / 64, wb = (a.M + 63) / 64;
     const size_t static_smem = 6656;  // index rings, chunk table, barrier
-    const size_t rest = 1024 + (size_t)wb * a.C * 128;
+    // parking area of the scatter: 64 columns per row when it fits, else 32
+    const size_t fixed_part = 1024 + (size_t)wb * a.C * 128 + (size_t)kb * BLK_BYTES;
+    p.slab = (outw >= 64 && fixed_part + (size_t)CH * (64 * 4 + 16) + static_smem <= 232448 - 1024) ? 64 : 32;
+    const size_t rest = 1024 + (size_t)wb * a.C * 128 + (size_t)CH * (p.slab * 4 + 16);
     // One A tile: it is free again as soon as the multiply has finished, so the
     // next gather still overlaps the scatter, and more CTAs fit on an SM.
     p.nbuf = 1;
