@@ -177,6 +177,13 @@ int pcx_expand_taps(const int64_t *d_seg_offs, int K, int64_t T, int32_t *d_k,
  *   pcx_radius_workspace_bytes); d_ws2 is the fill-only scratch of
  *   pcx_radius_fill_workspace_bytes(total).
  */
+/* fp32 arithmetic of the radius predicate: 0 = every operation rounded (the
+ * expression of sparse_engines/strided_grid_radius_triton_kernel.py:25-31 as
+ * written), 1 = sum of squares contracted into FMAs (what that expression
+ * compiles to on a B200; the default), 2 = 1 with the approximate square root.
+ * Process-wide; only pairs within an ulp or two of the radius are affected. */
+int pcx_set_radius_predicate(int variant);
+int pcx_get_radius_predicate(void);
 size_t pcx_radius_workspace_bytes(int64_t P, int64_t Q, int kernel_size);
 size_t pcx_radius_fill_workspace_bytes(int64_t total, int kernel_size);
 int pcx_radius_count(const float *d_points, const float *d_queries,

@@ -59,14 +59,23 @@ def _as_f32(x):
     return np.ascontiguousarray(np.asarray(x, dtype=F32))
 
 
-def radius_distance(q, p, distance_type="ball"):
-    """Distance of the predicate, float32, one rounding per operation.
+def radius_distance(q, p, distance_type="ball", fma=False):
+    """Distance of the predicate, float32.
 
     sparse_engines/strided_grid_radius_triton_kernel.py:25-31: ``d = q - p``
     per axis, ``sqrt((dx*dx + dy*dy) + dz*dz)`` for the ball, ``max |d|`` for
-    the Chebyshev variant.
+    the Chebyshev variant.  ``fma=False`` rounds every operation (the
+    expression as written; Triton's CPU interpreter).  ``fma=True`` restates
+    what the GPU compiler makes of it, ``fma(dz,dz, fma(dx,dx, dy*dy))``: the
+    products are exact in float64 and each fused step is rounded once to fp32.
     """
     d = (q - p).astype(F32)
+    if distance_type == "ball" and fma:
+        d64 = d.astype(np.float64)
+        s = (d[..., 1] * d[..., 1]).astype(F32)
+        s = (d64[..., 0] * d64[..., 0] + s.astype(np.float64)).astype(F32)
+        s = (d64[..., 2] * d64[..., 2] + s.astype(np.float64)).astype(F32)
+        return np.sqrt(s).astype(F32)
     if distance_type == "ball":
         s = (d[..., 0] * d[..., 0]).astype(F32)
         s = (s + (d[..., 1] * d[..., 1]).astype(F32)).astype(F32)
@@ -138,7 +147,7 @@ def _candidate_pairs(points, queries, radius, sample_inds, query_sample_inds):
 
 def radius_search_sorted_grid8(points, queries, radius, sample_inds=None,
                                query_sample_inds=None, return_distances=False,
-                               distance_type="ball"):
+                               distance_type="ball", fma=False):
     """Exact fixed-radius neighbours, query-major.
 
     internals/neighbors.py:886-916 (→ 469-838).  Membership: fp32
@@ -154,7 +163,7 @@ def radius_search_sorted_grid8(points, queries, radius, sample_inds=None,
         out = (np.zeros(0, np.int64), np.zeros(Q, np.int64))
         return out + ((np.zeros(0, F32),) if return_distances else ())
     cq, cp = _candidate_pairs(points, queries, radius, sample_inds, query_sample_inds)
-    dist = radius_distance(queries[cq], points[cp], distance_type)
+    dist = radius_distance(queries[cq], points[cp], distance_type, fma)
     keep = dist <= F32(float(radius))
     cq, cp, dist = cq[keep], cp[keep], dist[keep]
     order = np.lexsort((cp, cq))
@@ -168,7 +177,7 @@ def radius_search_sorted_grid8(points, queries, radius, sample_inds=None,
 def radius_search_sorted_grid8_segments(points, queries, radius, kernel_size,
                                         kernel_grid_size, sample_inds=None,
                                         query_sample_inds=None,
-                                        distance_type="ball"):
+                                        distance_type="ball", fma=False):
     """Neighbour pairs grouped by kernel tap.
 
     internals/neighbors.py:919-955 (→ 469-838, prepared-segment branch).
@@ -191,7 +200,7 @@ def radius_search_sorted_grid8_segments(points, queries, radius, kernel_size,
         e = np.zeros(0, np.int32)
         return e, e.copy(), np.zeros(nk + 1, np.int64), np.zeros(Q, np.int64)
     cq, cp = _candidate_pairs(points, queries, radius, sample_inds, query_sample_inds)
-    dist = radius_distance(queries[cq], points[cp], distance_type)
+    dist = radius_distance(queries[cq], points[cp], distance_type, fma)
     keep = dist <= F32(float(radius))
     cq, cp = cq[keep], cp[keep]
     k = tap_index(points[cp], queries[cq], kernel_grid_size, K)

@@ -50,6 +50,8 @@ SIGNATURES = {
     "pcx_vvor_static_scratch": (c_int, [c_void_p] * 6 + [c_int64] * 4 + [c_int] * 4 + [c_void_p]),
     "pcx_seg_offs": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "pcx_expand_taps": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
+    "pcx_set_radius_predicate": (c_int, [c_int]),
+    "pcx_get_radius_predicate": (c_int, []),
     "pcx_radius_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),
     "pcx_radius_fill_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "pcx_radius_count": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_double, c_int, c_int, c_double]

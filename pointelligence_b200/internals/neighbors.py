@@ -11,9 +11,34 @@ the contract.
 """
 from __future__ import annotations
 
+from contextlib import contextmanager
+
 import torch
 
 from .. import _cabi
+
+_PREDICATES = {"ieee": 0, "fma": 1, "fma_approx_sqrt": 2}
+
+
+@contextmanager
+def radius_predicate(mode):
+    """Scope the fp32 arithmetic of the distance predicate.
+
+    ``"fma"`` (default) is what the reference's Triton kernels compute on a
+    B200 (the compiler contracts the sum of squares into fused multiply-adds);
+    ``"ieee"`` rounds every operation, which is what the same kernels compute
+    under Triton's CPU interpreter.  The two differ only for pairs within an
+    ulp or two of the radius."""
+    if mode not in _PREDICATES:
+        raise ValueError(f"radius predicate must be one of {sorted(_PREDICATES)}; got {mode!r}")
+    lib = _cabi.lib()
+    prev = lib.pcx_get_radius_predicate()
+    _cabi.check(lib.pcx_set_radius_predicate(_PREDICATES[mode]))
+    try:
+        yield
+    finally:
+        _cabi.check(lib.pcx_set_radius_predicate(prev))
+
 
 _BACKENDS = {"auto", "sorted8_materialized", "sorted27_materialized", "tiled", "sorted_grid8", "fixed_grid"}
 

@@ -23,7 +23,7 @@ from ..sparse_engines.ops import sparse_matrix_vector_multiplication_reduction
 from ..sparse_engines.tig import TigIndex, tig_mvmr
 from .contract import TripletContract
 from .metadata import MetaData
-from .triplets import handle_stride_and_build_triplets
+from .triplets import build_full_cover_strided_rulebook, handle_stride_and_build_triplets
 
 
 class GeneralConv(Module):
@@ -134,5 +134,51 @@ def conv_with_stride(conv_op: Callable, x: Tensor, m: MetaData, stride: float,
     from the parent cloud to the down-sampled cloud, convolve."""
     m = handle_stride_and_build_triplets(m, stride, conv_op.kernel_size_3, receptive_field_scaler,
                                          distance_type=distance_type)
+    x = conv_op(x, m.i, m.j, m.k, m.num_points(), contract=m.contract, seg_offs=m.seg_offs)
+    return x, m
+
+
+def conv_with_stride_full_cover(conv_op: Callable, x: Tensor, m: MetaData, stride: float,
+                                radius_margin: float = 1e-2, radius_backend: str = "auto") -> Tuple[Tensor, MetaData]:
+    """Overlapping strided convolution with guaranteed input coverage (mirror of
+    ``layers/conv.py:549-632``): output centres are observed input points chosen
+    by ``build_full_cover_strided_rulebook``; the mirrored rulebook is cached on
+    the parent for the matching up-sampling layer."""
+    if stride <= 1:
+        raise ValueError(f"conv_with_stride_full_cover requires stride > 1; got {stride}.")
+    import math
+
+    from ..sparse_engines._seg_offs import kernel_offset_segments
+
+    with torch.no_grad():
+        pm = m.parent
+        if not (pm is not None and pm.points.shape == m.points.shape and pm.grid_size == m.grid_size
+                and torch.equal(pm.points, m.points) and torch.equal(pm.sample_inds, m.sample_inds)):
+            pm = MetaData(points=m.points, sample_inds=m.sample_inds, sample_sizes=m.sample_sizes,
+                          grid_size=m.grid_size, parent=m.parent)
+            m.parent = pm
+        rb = build_full_cover_strided_rulebook(
+            points=pm.points, sample_inds=pm.sample_inds, sample_sizes=pm.sample_sizes, stride=stride,
+            input_grid_size=pm.grid_size, kernel_size=conv_op.kernel_size_3, radius_margin=radius_margin,
+            radius_backend=radius_backend, return_num_neighbors=True)
+        taps = math.prod(conv_op.kernel_size_3)
+        m.points, m.sample_inds, m.sample_sizes = rb.points, rb.sample_inds, rb.sample_sizes
+        m.grid_size = float(stride) * pm.grid_size
+        m.downsample_indices = rb.center_source_indices
+        m.i, m.j, m.k = rb.i, rb.j, rb.k
+        m.seg_offs = kernel_offset_segments(m.k, taps)
+        m.num_neighbors = rb.num_neighbors
+        m.contract = TripletContract(k_sorted=True)
+        pm.i_upsample, pm.j_upsample, pm.k_upsample = rb.i_upsample, rb.j_upsample, rb.k_upsample
+        pm.seg_offs_upsample = kernel_offset_segments(rb.k_upsample, taps)
+        pm.full_cover_point_to_initial_center = rb.point_to_initial_center
+        pm.full_cover_initial_center_indices = rb.initial_center_source_indices
+        pm.full_cover_additional_center_indices = rb.additional_center_source_indices
+        pm.full_cover_coverage_per_input = rb.coverage_per_input
+        pm.full_cover_telemetry = {
+            "radius": rb.radius, "radius_scaler": rb.radius_scaler,
+            "initial_center_count": int(rb.initial_center_source_indices.numel()),
+            "additional_center_count": int(rb.additional_center_source_indices.numel()),
+            "selector_round_count": rb.selector_round_count, "edge_count": int(rb.k.numel())}
     x = conv_op(x, m.i, m.j, m.k, m.num_points(), contract=m.contract, seg_offs=m.seg_offs)
     return x, m

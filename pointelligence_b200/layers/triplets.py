@@ -196,3 +196,204 @@ def handle_stride_and_build_triplets(m: MetaData, stride, kernel_size=_triple(3)
                 sort_by, distance_type, return_num_neighbors)
     m.contract = TripletContract(k_sorted=(sort_by == "k"))
     return m
+
+
+# --------------------------------------------------------------------------
+# Full-cover strided rulebook (mirror of ``layers/triplets.py:36-465``)
+# --------------------------------------------------------------------------
+from dataclasses import dataclass  # noqa: E402
+
+from torch import Tensor  # noqa: E402
+
+from ..internals.grid_sample import grid_sample_filter  # noqa: E402
+
+
+@dataclass(frozen=True)
+class FullCoverStridedRulebook:
+    """Rulebook of an overlapping strided convolution whose output centres are
+    observed input points and whose balls of radius ``radius`` cover every
+    input point (field set of the reference's dataclass)."""
+    points: Tensor
+    sample_inds: Tensor
+    sample_sizes: Tensor
+    center_source_indices: Tensor
+    initial_center_source_indices: Tensor
+    additional_center_source_indices: Tensor
+    point_to_initial_center: Tensor
+    i: Tensor
+    j: Tensor
+    k: Tensor
+    num_neighbors: Optional[Tensor]
+    i_upsample: Tensor
+    j_upsample: Tensor
+    k_upsample: Tensor
+    radius: float
+    radius_scaler: float
+    initial_center_counts: Tensor
+    additional_center_counts: Tensor
+    selector_round_count: int
+    coverage_per_input: Tensor
+
+
+def _strict_taps(offsets, grid_size, K, context):
+    """Tap of every offset without clamping: an offset outside the kernel is an error."""
+    half = K // 2
+    d = torch.round(offsets / float(grid_size)).to(torch.int64)
+    if d.numel():
+        worst = int(d.abs().max().item())
+        if worst > half:
+            raise ValueError(
+                f"{context} kernel_size={K} is insufficient for observed offset {worst} grid steps; "
+                f"need at least K{2 * worst + 1}. Full-cover strided convolution never clamps or "
+                "aliases out-of-range offsets.")
+    return ((d[:, 0] + half) * K + (d[:, 1] + half)) * K + (d[:, 2] + half), d
+
+
+def _edges(points, sample_inds, centers, center_sample, radius, backend):
+    """(centre ordinal, point index, per-centre counts) of all pairs within ``radius``."""
+    nb, counts = radius_search(points=points, query_points=centers, radius=radius, sample_inds=sample_inds,
+                               query_sample_inds=center_sample, backend=backend)
+    owner = torch.repeat_interleave(torch.arange(counts.numel(), device=points.device), counts,
+                                    output_size=int(nb.numel()))
+    return owner, nb.long(), counts
+
+
+def _residual_net(points, sample_inds, c0_points, point_to_c0, uncovered, radius, backend):
+    """Deterministic maximal R-net over the points no initial centre covers.
+
+    Rounds: every still-active point gets a priority (most active neighbours
+    first, then farthest from its cell's initial centre, then lowest index); a
+    point whose priority is the best of its active neighbourhood becomes a
+    centre and retires that neighbourhood."""
+    dev = points.device
+    src = torch.nonzero(uncovered).squeeze(1)
+    if src.numel() == 0:
+        return torch.empty(0, dtype=torch.long, device=dev), 0
+    up, us = points[src], sample_inds[src]
+    q, p, _ = _edges(up, us, up, us, radius, backend)
+    far = torch.sum((up - c0_points[point_to_c0[src]]).square(), dim=1)
+    n = src.numel()
+    active = torch.ones(n, dtype=torch.bool, device=dev)
+    chosen, rounds = [], 0
+    while bool(active.any().item()):
+        live = active[q] & active[p]
+        gain = torch.zeros(n, dtype=torch.long, device=dev)
+        gain.index_add_(0, q[live], torch.ones(int(live.sum().item()), dtype=torch.long, device=dev))
+        order = torch.argsort(src, stable=True)
+        order = order[torch.argsort(-far[order], stable=True)]
+        order = order[torch.argsort(-gain[order], stable=True)]
+        rank = torch.empty_like(order)
+        rank[order] = torch.arange(n, device=dev)
+        nb_rank = torch.where(active[p], rank[p], torch.full_like(p, n + 1))
+        best = torch.full((n,), n + 1, dtype=torch.long, device=dev)
+        best.scatter_reduce_(0, q, nb_rank, reduce="amin", include_self=True)
+        pick = active & (rank == best)
+        if not bool(pick.any().item()):
+            raise RuntimeError("full-cover R-net selector made no progress")
+        chosen.append(src[pick])
+        retire = pick[q] & active[p]
+        active[p[retire]] = False
+        rounds += 1
+    added = torch.cat(chosen)
+    order = torch.argsort(sample_inds[added] * (points.shape[0] + 1) + added, stable=True)
+    return added[order], rounds
+
+
+@torch.compiler.disable
+def build_full_cover_strided_rulebook(points, sample_inds, sample_sizes, *, stride, input_grid_size,
+                                      kernel_size, radius_margin=1e-2, radius_backend="auto",
+                                      return_num_neighbors=True) -> FullCoverStridedRulebook:
+    """Centres = the observed point nearest every occupied stride cell's centre,
+    plus a residual R-net over the points those centres leave uncovered; edges =
+    all (centre, point) pairs within ``R = sqrt(3)/2 * stride * grid * (1 + margin)``;
+    taps by strict (non-clamping) voxelisation; the mirrored rulebook for the
+    matching up-sampling layer comes with it."""
+    with torch.no_grad():
+        if points.dim() != 2 or points.shape[1] != 3:
+            raise ValueError(f"points must have shape (N, 3); got {tuple(points.shape)}")
+        dev = points.device
+        N = points.shape[0]
+        if sample_inds is None:
+            sample_inds = torch.zeros(N, device=dev, dtype=torch.long)
+        sample_inds = sample_inds.to(torch.long)
+        if sample_sizes is None:
+            sample_sizes = torch.bincount(sample_inds)
+        if points.numel() == 0:
+            e = torch.empty(0, device=dev, dtype=torch.long)
+            z = torch.zeros(0, device=dev, dtype=torch.long)
+            return FullCoverStridedRulebook(points, sample_inds, sample_sizes, e, e, e, e, e, e, e,
+                                            z if return_num_neighbors else None, e, e, e, 0.0, 0.0,
+                                            torch.zeros_like(sample_sizes), torch.zeros_like(sample_sizes), 0, z)
+        radius_scaler = full_cover_radius_scaler(stride, radius_margin)
+        radius = float(input_grid_size) * radius_scaler
+        need = minimum_full_cover_kernel_size(radius_scaler)
+        ks = _triple(kernel_size)
+        K = int(ks[0])
+        if not (ks[0] == ks[1] == ks[2]):
+            raise ValueError(f"full-cover strided conv requires a cubic kernel; got {ks}")
+        if K < need:
+            raise ValueError(f"full-cover stride={stride} at grid_size={input_grid_size} "
+                             f"needs kernel_size >= {need}; got {kernel_size}")
+
+        # initial centres: one per occupied stride cell, ordered by (sample, source index)
+        _, _, cell_pick, cell_of_point = grid_sample_filter(
+            points, float(stride) * float(input_grid_size), sample_inds, reduction="center_nearest",
+            return_mapping=True)
+        by_source = torch.argsort(sample_inds[cell_pick] * (N + 1) + cell_pick, stable=True)
+        c0 = cell_pick[by_source]
+        rank_of_cell = torch.empty_like(by_source)
+        rank_of_cell[by_source] = torch.arange(by_source.numel(), device=dev)
+        point_to_c0 = rank_of_cell[cell_of_point]
+
+        c0_owner, c0_nb, c0_counts = _edges(points, sample_inds, points[c0], sample_inds[c0], radius, radius_backend)
+        covered = torch.zeros(N, dtype=torch.bool, device=dev)
+        covered[c0_nb] = True
+        c1, rounds = _residual_net(points, sample_inds, points[c0], point_to_c0, ~covered, radius, radius_backend)
+
+        multi = sample_sizes.numel() > 1
+        if c1.numel() and multi:
+            both = torch.cat([c0, c1])
+            group = torch.cat([torch.zeros_like(c0), torch.ones_like(c1)])
+            order = torch.argsort(sample_inds[both] * (2 * (N + 1)) + group * (N + 1) + both, stable=True)
+            centers = both[order]
+        else:
+            centers = torch.cat([c0, c1]) if c1.numel() else c0
+        slot = torch.empty(N, dtype=torch.long, device=dev)
+        slot[centers] = torch.arange(centers.numel(), device=dev)
+        point_to_center = slot[c0[point_to_c0]]
+
+        center_points = points[centers].contiguous()
+        center_sample = sample_inds[centers].contiguous()
+        i_parts, j_parts = [slot[c0[c0_owner]]], [c0_nb]
+        num_neighbors = torch.zeros(centers.numel(), dtype=c0_counts.dtype, device=dev)
+        num_neighbors[slot[c0]] = c0_counts
+        if c1.numel():
+            c1_owner, c1_nb, c1_counts = _edges(points, sample_inds, points[c1], sample_inds[c1], radius, radius_backend)
+            i_parts.append(slot[c1[c1_owner]])
+            j_parts.append(c1_nb)
+            num_neighbors[slot[c1]] = c1_counts
+        i, j = torch.cat(i_parts), torch.cat(j_parts)
+        k, d = _strict_taps(points[j] - center_points[i], input_grid_size, K, "full-cover patchify")
+        k, order = torch.sort(k, stable=True)
+        i, j, d = i[order], j[order], d[order]
+
+        coverage = torch.bincount(j, minlength=N)
+        if bool((coverage == 0).any().item()):
+            raise RuntimeError("full-cover rulebook construction failed: some input points have zero incident edges")
+        k_up, _ = _strict_taps(-d.to(points.dtype) * float(input_grid_size), input_grid_size, K,
+                               "full-cover unpatchify")
+        k_up, up_order = torch.sort(k_up, stable=True)
+        idt = torch.int32 if max(N, centers.numel()) <= 2147483647 else torch.int64
+        nS = sample_sizes.numel()
+        return FullCoverStridedRulebook(
+            points=center_points, sample_inds=center_sample,
+            sample_sizes=torch.bincount(center_sample, minlength=nS),
+            center_source_indices=centers.to(idt), initial_center_source_indices=c0.to(idt),
+            additional_center_source_indices=c1.to(idt), point_to_initial_center=point_to_center.to(idt),
+            i=i.to(idt), j=j.to(idt), k=k.to(idt),
+            num_neighbors=num_neighbors if return_num_neighbors else None,
+            i_upsample=j[up_order].to(idt), j_upsample=i[up_order].to(idt), k_upsample=k_up.to(idt),
+            radius=radius, radius_scaler=radius_scaler,
+            initial_center_counts=torch.bincount(sample_inds[c0], minlength=nS),
+            additional_center_counts=torch.bincount(sample_inds[c1], minlength=nS),
+            selector_round_count=rounds, coverage_per_input=coverage.to(idt))

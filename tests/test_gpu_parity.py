@@ -37,7 +37,7 @@ def _qm_keys(neighbors, counts, P):
 
 # ------------------------------------------------------------------ geometry
 def test_radius_search_matches_reference_golden(golden):
-    from pointelligence_b200.internals.neighbors import radius_search_sorted_grid8
+    from pointelligence_b200.internals.neighbors import radius_predicate, radius_search_sorted_grid8
 
     z = golden("radius")
     for name in _cases(z):
@@ -45,8 +45,9 @@ def test_radius_search_matches_reference_golden(golden):
         has_s = f"{name}.sample_inds" in z.files
         si = _t(z[f"{name}.sample_inds"]) if has_s else None
         qsi = _t(z[f"{name}.query_sample_inds"]) if has_s else None
-        nb, cnt, dist = radius_search_sorted_grid8(_t(pts), _t(q), float(z[f"{name}.radius"]), si, qsi,
-                                                   return_distances=True)
+        with radius_predicate("ieee"):  # the golden vectors come from Triton's CPU interpreter
+            nb, cnt, dist = radius_search_sorted_grid8(_t(pts), _t(q), float(z[f"{name}.radius"]), si, qsi,
+                                                       return_distances=True)
         nb, cnt, dist = nb.cpu().numpy(), cnt.cpu().numpy(), dist.cpu().numpy()
         assert nb.dtype == np.int64 and cnt.dtype == np.int64
         assert np.array_equal(cnt, z[f"{name}.num_neighbors"]), name
@@ -59,7 +60,7 @@ def test_radius_search_matches_reference_golden(golden):
 
 
 def test_tap_segments_match_reference_golden(golden):
-    from pointelligence_b200.internals.neighbors import radius_search_sorted_grid8_segments
+    from pointelligence_b200.internals.neighbors import radius_predicate, radius_search_sorted_grid8_segments
 
     z = golden("radius")
     for name in _cases(z):
@@ -68,9 +69,10 @@ def test_tap_segments_match_reference_golden(golden):
         si = _t(z[f"{name}.sample_inds"]) if has_s else None
         qsi = _t(z[f"{name}.query_sample_inds"]) if has_s else None
         K = int(z[f"{name}.kernel_size"])
-        i, j, seg, cnt, k = radius_search_sorted_grid8_segments(
-            _t(pts), _t(q), float(z[f"{name}.radius"]), K, float(z[f"{name}.kernel_grid_size"]), si, qsi,
-            return_k=True)
+        with radius_predicate("ieee"):
+            i, j, seg, cnt, k = radius_search_sorted_grid8_segments(
+                _t(pts), _t(q), float(z[f"{name}.radius"]), K, float(z[f"{name}.kernel_grid_size"]), si, qsi,
+                return_k=True)
         assert i.dtype == torch.int32 and j.dtype == torch.int32 and seg.dtype == torch.int64
         i, j, seg, cnt, k = (x.cpu().numpy() for x in (i, j, seg, cnt, k))
         assert np.array_equal(seg, z[f"{name}.seg_offs"]), name
@@ -84,10 +86,19 @@ def test_tap_segments_match_reference_golden(golden):
             assert np.all(np.diff(i[seg[t]:seg[t + 1]]) >= 0)
 
 
+@pytest.mark.parametrize("mode", ["fma", "ieee"])
 @pytest.mark.parametrize("distance_type", ["ball", "chebyshev"])
-def test_radius_search_matches_oracle_random(distance_type):
-    from pointelligence_b200.internals.neighbors import (radius_search_sorted_grid8,
+def test_radius_search_matches_oracle_random(distance_type, mode):
+    from pointelligence_b200.internals.neighbors import (radius_predicate, radius_search_sorted_grid8,
                                                          radius_search_sorted_grid8_segments)
+
+    with radius_predicate(mode):
+        _check_radius_search_against_oracle(distance_type, mode == "fma", radius_search_sorted_grid8,
+                                            radius_search_sorted_grid8_segments)
+
+
+def _check_radius_search_against_oracle(distance_type, fma, radius_search_sorted_grid8,
+                                        radius_search_sorted_grid8_segments):
 
     rng = np.random.default_rng(17)
     pts = ((rng.random((6000, 3)) - 0.5) * 4).astype(np.float32)
@@ -96,14 +107,14 @@ def test_radius_search_matches_oracle_random(distance_type):
     qs = np.sort(rng.integers(0, 3, len(qry)))
     r = 0.19
     nb, cnt = radius_search_sorted_grid8(_t(pts), _t(qry), r, _t(ps), _t(qs), distance_type=distance_type)
-    onb, ocnt = og.radius_search_sorted_grid8(pts, qry, r, ps, qs, distance_type=distance_type)
+    onb, ocnt = og.radius_search_sorted_grid8(pts, qry, r, ps, qs, distance_type=distance_type, fma=fma)
     assert np.array_equal(cnt.cpu().numpy(), ocnt)
     assert np.array_equal(_qm_keys(nb.cpu().numpy(), ocnt, len(pts)), _qm_keys(onb, ocnt, len(pts)))
     for K, g in ((3, 0.1), (5, 0.07)):
         i, j, seg, c2 = radius_search_sorted_grid8_segments(_t(pts), _t(qry), r, K, g, _t(ps), _t(qs),
                                                             distance_type=distance_type)
         oi, oj, oseg, oc = og.radius_search_sorted_grid8_segments(pts, qry, r, K, g, ps, qs,
-                                                                  distance_type=distance_type)
+                                                                  distance_type=distance_type, fma=fma)
         assert np.array_equal(seg.cpu().numpy(), oseg)
         k = np.repeat(np.arange(K ** 3), np.diff(oseg))
         assert np.array_equal(og.canonical_triplet_keys(i.cpu().numpy(), j.cpu().numpy(), k, len(qry), len(pts)),
@@ -345,7 +356,7 @@ def test_pointconv3d_forward_backward_on_scene(dtype):
         else:
             qp, qi, oidx, _ = og.grid_sample_center_nearest(pts, 0.04, inds)
             assert np.array_equal(m.downsample_indices.cpu().numpy(), oidx)
-        oi, oj, oseg, _ = og.radius_search_sorted_grid8_segments(pts, qp, 0.02 * rs, 3, 0.02, inds, qi)
+        oi, oj, oseg, _ = og.radius_search_sorted_grid8_segments(pts, qp, 0.02 * rs, 3, 0.02, inds, qi, fma=True)
         ok = np.repeat(np.arange(27), np.diff(oseg))
         assert np.array_equal(m.seg_offs.cpu().numpy(), oseg)
         assert np.array_equal(
@@ -401,3 +412,91 @@ def test_full_size_properties_150k_scene():
     err = (out.float() - ref).norm() / ref.norm()
     assert float(err) < 2e-2
     assert _cabi.device_status() == 0
+
+
+# ------------------------------------------------------------------ full cover
+def _full_cover_fixture():
+    pts0 = torch.tensor([[0.001, 0.001, 0.001], [0.399, 0.399, 0.399], [0.401, 0.001, 0.001],
+                         [0.799, 0.399, 0.399]], device=_dev())
+    pts = torch.cat([pts0, pts0 + torch.tensor([2.0, 0.0, 0.0], device=_dev())])
+    si = torch.cat([torch.zeros(4, dtype=torch.long, device=_dev()), torch.ones(4, dtype=torch.long, device=_dev())])
+    return pts, si, torch.bincount(si)
+
+
+def test_full_cover_rulebook_fixture():
+    """tests/unittest/test_full_cover_strided.py:52-120 of the reference: K15 is
+    required for stride 8 at grid 0.05, edges are exactly the same-sample pairs
+    within R, the mirrored rulebook is the transpose with mirrored taps."""
+    from pointelligence_b200.layers import build_full_cover_strided_rulebook
+
+    pts, si, sizes = _full_cover_fixture()
+    with pytest.raises(ValueError, match="needs kernel_size >= 15"):
+        build_full_cover_strided_rulebook(pts, si, sizes, stride=8, input_grid_size=0.05, kernel_size=13)
+    rb = build_full_cover_strided_rulebook(pts, si, sizes, stride=8, input_grid_size=0.05, kernel_size=15)
+    rb2 = build_full_cover_strided_rulebook(pts, si, sizes, stride=8, input_grid_size=0.05, kernel_size=15)
+    for f in ("i", "j", "k", "center_source_indices", "i_upsample", "j_upsample", "k_upsample"):
+        assert torch.equal(getattr(rb, f), getattr(rb2, f)), f          # deterministic
+    assert rb.radius == pytest.approx(0.34987426, rel=1e-7)
+    n = pts.shape[0]
+    cpts, cs = rb.points, rb.sample_inds
+    within = (torch.cdist(cpts.double(), pts.double()) <= rb.radius) & (cs[:, None] == si[None, :])
+    bi, bj = torch.nonzero(within, as_tuple=True)
+    assert torch.equal(torch.sort(rb.i.long() * (n + 1) + rb.j.long()).values, torch.sort(bi * (n + 1) + bj).values)
+    assert torch.all(rb.coverage_per_input > 0)
+    assert torch.equal(rb.points, pts[rb.center_source_indices.long()])
+    assert torch.all(rb.k[1:] >= rb.k[:-1]) and torch.all(rb.k_upsample[1:] >= rb.k_upsample[:-1])
+    K = 15
+    kk = rb.k.long()
+    mirrored = ((K - 1 - kk // (K * K)) * K + (K - 1 - (kk // K) % K)) * K + (K - 1 - kk % K)
+    nc = cpts.shape[0]
+    down = torch.sort(mirrored * (n * nc) + rb.j.long() * nc + rb.i.long()).values
+    up = torch.sort(rb.k_upsample.long() * (n * nc) + rb.i_upsample.long() * nc + rb.j_upsample.long()).values
+    assert torch.equal(down, up)
+    assert torch.equal(torch.bincount(rb.i.long(), minlength=nc), rb.num_neighbors)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_conv_with_stride_full_cover_on_scene(dtype):
+    """Stride 2 needs a 5x5x5 kernel (125 taps); centres cover every input and
+    residual centres keep their distance; the convolution matches the fp64 oracle."""
+    from pointelligence_b200.layers import MetaData, PointConv3d, conv_with_stride_full_cover
+    from pointelligence_b200.synthetic import indoor_scene, ragged_batch
+
+    torch.manual_seed(1)
+    pts, inds, sizes = ragged_batch([indoor_scene(5000, 5), indoor_scene(3000, 6)])
+    C, M = 32, 32
+    conv = PointConv3d(C, M, 5, bias=False, device=_dev(), dtype=dtype)
+    with pytest.raises(ValueError, match="needs kernel_size >= 5"):
+        conv_with_stride_full_cover(PointConv3d(C, M, 3, device=_dev(), dtype=dtype),
+                                    torch.zeros(len(pts), C, device=_dev(), dtype=dtype),
+                                    MetaData(points=_t(pts), sample_inds=_t(inds), sample_sizes=_t(sizes),
+                                             grid_size=0.02), 2)
+    x = torch.randn(len(pts), C, device=_dev(), dtype=dtype, requires_grad=True)
+    m = MetaData(points=_t(pts), sample_inds=_t(inds), sample_sizes=_t(sizes), grid_size=0.02)
+    y, m = conv_with_stride_full_cover(conv, x, m, 2)
+    assert m.grid_size == 0.04 and y.shape == (m.num_points(), M)
+    tel = m.parent.full_cover_telemetry
+    assert tel["edge_count"] == m.i.numel() and tel["initial_center_count"] > 0
+    assert torch.all(m.parent.full_cover_coverage_per_input > 0)
+    extra = m.parent.full_cover_additional_center_indices.long()
+    if extra.numel() > 1:    # the residual centres form an R-net: no two of one sample within R
+        ep, es = _t(pts)[extra], _t(inds)[extra]
+        dmat = torch.cdist(ep.double(), ep.double()) + torch.eye(len(extra), device=_dev()) * 10
+        assert torch.all((dmat > tel["radius"]) | (es[:, None] != es[None, :]))
+    # edge set = oracle radius search from the chosen centres
+    centers = m.downsample_indices.long().cpu().numpy()
+    oi, oj, _, _ = og.radius_search_sorted_grid8_segments(pts, pts[centers], tel["radius"], 5, 0.02, inds,
+                                                          inds[centers], fma=True)
+    n = len(pts)
+    assert np.array_equal(np.sort(m.i.cpu().numpy().astype(np.int64) * n + m.j.cpu().numpy()),
+                          np.sort(oi.astype(np.int64) * n + oj))
+    go = torch.randn_like(y)
+    y.backward(go)
+    wn = conv.weight.detach().float().cpu().numpy().astype(np.float64)
+    xn = x.detach().float().cpu().numpy().astype(np.float64)[:, None, :]
+    gn = go.float().cpu().numpy().astype(np.float64)[:, None, :]
+    i_, j_, k_ = (t.cpu().numpy() for t in (m.i, m.j, m.k))
+    assert oso.rel_frobenius(y.detach().float().cpu().numpy(), oso.mvmr_f64(wn, k_, xn, j_, i_, len(centers))[:, 0]) < TOL[dtype]
+    assert oso.rel_frobenius(conv.weight.grad.float().cpu().numpy(), oso.vvor_f64(xn, j_, gn, i_, k_, 125)) < TOL[dtype]
+    assert oso.rel_frobenius(x.grad.float().cpu().numpy(),
+                             oso.mvmr_f64(np.swapaxes(wn, 2, 3), k_, gn, i_, j_, n)[:, 0]) < TOL[dtype]

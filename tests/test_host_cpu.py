@@ -171,3 +171,21 @@ def test_gradient_allreduce_two_ranks_gloo(tmp_path):
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, o
         assert f"rank {r} ok" in o
+
+
+def test_radius_predicate_switch_is_scoped():
+    from pointelligence_b200 import _cabi
+    from pointelligence_b200.internals.neighbors import radius_predicate
+
+    lib = _cabi.lib()
+    default = lib.pcx_get_radius_predicate()
+    assert default in (0, 1, 2)
+    with radius_predicate("ieee"):
+        assert lib.pcx_get_radius_predicate() == 0
+        with radius_predicate("fma"):
+            assert lib.pcx_get_radius_predicate() == 1
+        assert lib.pcx_get_radius_predicate() == 0
+    assert lib.pcx_get_radius_predicate() == default
+    with pytest.raises(ValueError):
+        with radius_predicate("exact"):
+            pass
