@@ -213,6 +213,24 @@ def run_ours(args, rank, local_rank, world):
     i, j, k, seg, _ = build_triplets_segmented(pts, sample, sizes, RADIUS, KERNEL, radius_scaler=RADIUS / TAP_GRID)
     T = int(i.numel())
     K = KERNEL ** 3
+    # geometry stage timings (reported beside the headline, not part of it): wall clock
+    # around the public builders, which end with the host hand-over of the counts
+    from pointelligence_b200.layers.downsample import downsample
+
+    def _wall(fn, reps=5):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / reps * 1e3
+
+    geometry_ms = {
+        "build_triplets_segmented": _wall(lambda: build_triplets_segmented(
+            pts, sample, sizes, RADIUS, KERNEL, radius_scaler=RADIUS / TAP_GRID)),
+        "downsample_stride2": _wall(lambda: downsample(pts, sample, 0.02, 2)),
+    }
     g = torch.Generator(device=dev).manual_seed(rank + 1)
     C = M = args.channels
     bound = 1.0 / np.sqrt(M * K)
@@ -359,7 +377,8 @@ def run_ours(args, rank, local_rank, world):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "points_per_rank": n, "triplets_rank0": T,
                        "triplets_per_point": T / n, "l2": "flushed between steps (256 MiB write)",
-                       "collective": "all-reduce of dW per step" if world > 1 else "none"},
+                       "collective": "all-reduce of dW per step" if world > 1 else "none",
+                       "geometry_ms": geometry_ms},
             "tflops": 6.0 * T_all * C * M / (per_step_ms * 1e-3) / 1e12,
             "roofline": roofline,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
