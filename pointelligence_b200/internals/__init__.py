@@ -1,1 +1,1 @@
-from . import grid_indexing, grid_sample, indexing, neighbors  # noqa: F401
+from . import grid_indexing, grid_sample, indexing, neighbors, triplet_cache  # noqa: F401

@@ -18,6 +18,7 @@ from torch.nn.modules.utils import _triple
 
 from ..internals.indexing import cumsum_exclusive, repeat_interleave_indices
 from ..internals.neighbors import radius_search, radius_search_sorted_grid8_segments
+from ..internals.triplet_cache import cache_get, cache_put, triplet_key
 from ..sparse_engines._seg_offs import kernel_offset_segments
 from .contract import TripletContract
 from .downsample import downsample
@@ -92,6 +93,13 @@ def build_triplets_segmented(points, sample_inds, sample_sizes, neighbor_radius,
     with torch.no_grad():
         query_points, query_sample_inds, query_sample_sizes = _resolve_queries(
             points, sample_inds, sample_sizes, query_points, query_sample_inds, query_sample_sizes)
+        key = triplet_key(points, query_points, neighbor_radius, radius_scaler, "k", return_num_neighbors,
+                          sample_inds, query_sample_inds, partial(voxelize_3d, kernel_size=sizes))
+        if key is not None:
+            key = key + ("segmented",)
+        hit = cache_get(key)
+        if hit is not None:
+            return hit
         i, j, seg_offs, num_neighbors, k = radius_search_sorted_grid8_segments(
             points=points, queries=query_points, radius=neighbor_radius, kernel_size=ks,
             kernel_grid_size=kernel_grid_size, sample_inds=sample_inds,
@@ -99,7 +107,9 @@ def build_triplets_segmented(points, sample_inds, sample_sizes, neighbor_radius,
             distance_type="ball", tap_stripes=tap_stripes, return_k=True)
         if num_neighbors.numel() and bool((num_neighbors == 0).any().item()):
             raise AssertionError(_NO_NEIGHBOR_MSG)
-        return i, j, k, seg_offs, (num_neighbors if return_num_neighbors else None)
+        out = (i, j, k, seg_offs, (num_neighbors if return_num_neighbors else None))
+        cache_put(key, out, points)
+        return out
 
 
 def _triplets_from_pairs(points, query_points, neighbor_indices, num_neighbors, kernel_indexer,
@@ -131,13 +141,20 @@ def build_triplets(points, sample_inds, sample_sizes, neighbor_radius, kernel_in
     with torch.no_grad():
         query_points, query_sample_inds, query_sample_sizes = _resolve_queries(
             points, sample_inds, sample_sizes, query_points, query_sample_inds, query_sample_sizes)
+        key = triplet_key(points, query_points, neighbor_radius, radius_scaler, sort_by, return_num_neighbors,
+                          sample_inds, query_sample_inds, kernel_indexer)
+        hit = cache_get(key)
+        if hit is not None:
+            return hit
         grid_size = neighbor_radius / radius_scaler if radius_scaler is not None else None
         neighbor_indices, num_neighbors = radius_search(
             points=points, query_points=query_points, radius=neighbor_radius, sample_inds=sample_inds,
             sample_sizes=sample_sizes, query_sample_inds=query_sample_inds,
             query_sample_sizes=query_sample_sizes, grid_size=grid_size)
-    return _triplets_from_pairs(points, query_points, neighbor_indices, num_neighbors, kernel_indexer,
-                                neighbor_radius, radius_scaler, sort_by, return_num_neighbors)
+    out = _triplets_from_pairs(points, query_points, neighbor_indices, num_neighbors, kernel_indexer,
+                               neighbor_radius, radius_scaler, sort_by, return_num_neighbors)
+    cache_put(key, out, points)
+    return out
 
 
 def _same_cloud(a: MetaData, b: MetaData):
