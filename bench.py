@@ -241,10 +241,11 @@ def run_ours(args, rank, local_rank, world):
 
     def step_resident():
         out = _cabi.mvmr(w, x, j, i, seg, None, n, False)
-        gx = _cabi.mvmr(w, go, i, j, seg, None, n, True)
         gw = _cabi.vvor(x.view(n, 1, C), j, go.view(n, 1, M), i, seg, None, K)
-        if world > 1:
-            dist.all_reduce(gw)
+        work = dist.all_reduce(gw, async_op=True) if world > 1 else None   # overlaps the input gradient
+        gx = _cabi.mvmr(w, go, i, j, seg, None, n, True)
+        if work is not None:
+            work.wait()
         return out, gx, gw
 
     def barrier():

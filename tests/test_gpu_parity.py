@@ -500,3 +500,61 @@ def test_conv_with_stride_full_cover_on_scene(dtype):
     assert oso.rel_frobenius(conv.weight.grad.float().cpu().numpy(), oso.vvor_f64(xn, j_, gn, i_, k_, 125)) < TOL[dtype]
     assert oso.rel_frobenius(x.grad.float().cpu().numpy(),
                              oso.mvmr_f64(np.swapaxes(wn, 2, 3), k_, gn, i_, j_, n)[:, 0]) < TOL[dtype]
+
+
+# ------------------------------------------------------- upsample, triplet cache
+def test_upsample_fresh_search_and_cached_edges():
+    from pointelligence_b200.layers import MetaData, PointConv3d, Upsample, conv_with_stride
+    from pointelligence_b200.synthetic import indoor_scene, ragged_batch
+
+    torch.manual_seed(3)
+    pts, inds, sizes = ragged_batch([indoor_scene(4000, 7), indoor_scene(2500, 8)])
+    down = PointConv3d(16, 32, 3, bias=False, device=_dev())
+    x = torch.randn(len(pts), 16, device=_dev())
+    m = MetaData(points=_t(pts), sample_inds=_t(inds), sample_sizes=_t(sizes), grid_size=0.02)
+    y, m = conv_with_stride(down, x, m, 2, receptive_field_scaler=2.5)
+    coarse = m.points.cpu().numpy()
+    coarse_s = m.sample_inds.cpu().numpy()
+    yn = y.detach().cpu().numpy().astype(np.float64)[:, None, :]
+
+    fresh = Upsample(32, 16, 3, bias=False, receptive_field_scaler=2.5).to(_dev())
+    out, m_hi = fresh(y, m)
+    assert out.shape == (len(pts), 16) and m_hi.num_points() == len(pts)
+    rs = og.radius_scaler_for_kernel_size(3, 2.5)
+    oi, oj, oseg, _ = og.radius_search_sorted_grid8_segments(coarse, pts, 0.04 * rs, 3, 0.04, coarse_s, inds, fma=True)
+    ok = np.repeat(np.arange(27), np.diff(oseg))
+    assert np.array_equal(m_hi.seg_offs.cpu().numpy(), oseg)
+    assert np.array_equal(
+        og.canonical_triplet_keys(m_hi.i.cpu().numpy(), m_hi.j.cpu().numpy(), m_hi.k.cpu().numpy(), len(pts), len(coarse)),
+        og.canonical_triplet_keys(oi, oj, ok, len(pts), len(coarse)))
+    wn = fresh.conv.weight.detach().cpu().numpy().astype(np.float64)
+    assert oso.rel_frobenius(out.detach().cpu().numpy(), oso.mvmr_f64(wn, ok, yn, oj, oi, len(pts))[:, 0]) < 1e-5
+
+    cached = Upsample(32, 16, 3, bias=False, straight_recover=True).to(_dev())
+    out2, m2 = cached(y, m)
+    assert torch.equal(m2.i, m.j) and torch.equal(m2.j, m.i) and torch.equal(m2.k, m.k)
+    wn = cached.conv.weight.detach().cpu().numpy().astype(np.float64)
+    ref = oso.mvmr_f64(wn, m.k.cpu().numpy(), yn, m.i.cpu().numpy(), m.j.cpu().numpy(), len(pts))[:, 0]
+    assert oso.rel_frobenius(out2.detach().cpu().numpy(), ref) < 1e-5
+    with pytest.raises(ValueError, match="Parent information"):
+        fresh(x[:, :16].repeat(1, 2), MetaData(points=_t(pts), sample_inds=_t(inds), sample_sizes=_t(sizes), grid_size=0.02))
+
+
+def test_triplet_cache_scope_reuses_rulebooks():
+    from pointelligence_b200.internals.triplet_cache import triplet_cache_scope
+    from pointelligence_b200.layers.triplets import build_triplets_segmented
+
+    pts = _t(np.random.default_rng(0).random((3000, 3)).astype(np.float32))
+    s = torch.zeros(3000, dtype=torch.int64, device=_dev())
+    n = torch.tensor([3000], device=_dev())
+    a = build_triplets_segmented(pts, s, n, 0.1, 3, radius_scaler=2.0)
+    b = build_triplets_segmented(pts, s, n, 0.1, 3, radius_scaler=2.0)
+    assert a[0] is not b[0] and torch.equal(a[0], b[0])          # no scope: rebuilt, same result
+    with triplet_cache_scope():
+        c = build_triplets_segmented(pts, s, n, 0.1, 3, radius_scaler=2.0)
+        d = build_triplets_segmented(pts, s, n, 0.1, 3, radius_scaler=2.0)
+        e = build_triplets_segmented(pts, s, n, 0.12, 3, radius_scaler=2.0)
+        assert c[0] is d[0] and c[3] is d[3]
+        assert e[0] is not c[0]
+    f = build_triplets_segmented(pts, s, n, 0.1, 3, radius_scaler=2.0)
+    assert f[0] is not c[0] and torch.equal(f[0], c[0])
