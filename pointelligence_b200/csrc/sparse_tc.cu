@@ -317,6 +317,7 @@ struct MvmrTcParams {
     const int64_t *seg;
     float *acc;
     int K, C, M, transpose, fmt, nbuf, slab;  // slab: columns parked per bulk reduction (32 or 64)
+    int bulk_warps;                           // warps 0..bulk_warps-1 scatter through bulk reductions
     uint32_t ncols;
 };
 
@@ -457,7 +458,7 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
             gather_tile<false>(a_tile0, p.feat, s_gather[b ^ 1], rows_next, inw, tid, 128);
             cp_async_commit();
         }
-        if (alive && warp * 32 < rows) {
+        if (alive && warp * 32 < rows && warp < p.bulk_warps) {
             const int row = warp * 32 + lane;
             const bool row_ok = row < rows;
             float *dst_row = p.acc + (int64_t)(row_ok ? s_scatter[b][row] : 0) * outw;
@@ -477,6 +478,21 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
                 const int cols = min(p.slab, outw - col0);
                 if (row_ok) bulk_reduce_add_f32(dst_row + col0, my_park, (uint32_t)cols * 4);
                 bulk_commit();
+            }
+        } else if (alive && warp * 32 < rows) {
+            // the remaining warps scatter from registers through the load/store pipe, so that
+            // the copy engine and the load/store pipe share the reduction traffic
+            const int32_t *sc = s_scatter[b];
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                if (warp * 32 + half * 16 >= rows) break;
+                const int ra = warp * 32 + half * 16 + (lane >> 2), rb = ra + 8;
+                const int64_t da = ra < rows ? sc[ra] : -1, db = rb < rows ? sc[rb] : -1;
+                for (int col0 = 0; col0 < outw; col0 += 64) {
+                    float v[32];
+                    tmem_ld_16x64(tmem + ((uint32_t)(warp * 32 + half * 16) << 16) + (uint32_t)col0, v);
+                    scatter_block(p.acc, da, db, outw, col0, lane, v);
+                }
             }
         }
         c0 = c1;
@@ -705,7 +721,9 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     p.weight = (const uint16_t *)a.weight, p.feat = (const uint16_t *)a.feat;
     p.gather = a.gather, p.scatter = a.scatter, p.seg = a.seg_offs, p.acc = a.acc;
     p.K = a.K, p.C = a.C, p.M = a.M, p.transpose = a.transpose, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
-    p.ncols = pow2_cols((outw + 31) / 32 * 32);  // the epilogue reads blocks of 32 columns
+    p.ncols = pow2_cols((outw + 63) / 64 * 64);  // the epilogue reads blocks of up to 64 columns
+    p.bulk_warps = 4;
+    if (const char *e = getenv("PCX_BULK_WARPS")) p.bulk_warps = std::max(0, std::min(4, atoi(e)));
     const int kb = (inw + 63) / 64, wb = (a.M + 63) / 64;
     const size_t static_smem = 6656;  // index rings, chunk table, barrier
     // parking area of the scatter: 64 columns per row when it fits, else 32
