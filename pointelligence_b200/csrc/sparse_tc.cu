@@ -317,7 +317,6 @@ struct MvmrTcParams {
     const int64_t *seg;
     float *acc;
     int K, C, M, transpose, fmt, nbuf, slab;  // slab: columns parked per bulk reduction (32 or 64)
-    int bulk_warps;                           // warps 0..bulk_warps-1 scatter through bulk reductions
     uint32_t ncols;
 };
 
@@ -326,6 +325,7 @@ struct MvmrTcParams {
 // into registers.  When two A tiles do not fit next to the weight tile
 // (nbuf == 1) the next gather is issued as soon as the multiply has finished,
 // so it still overlaps the scatter.
+template <bool BULK>
 __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t s_bar;
@@ -458,7 +458,7 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
             gather_tile<false>(a_tile0, p.feat, s_gather[b ^ 1], rows_next, inw, tid, 128);
             cp_async_commit();
         }
-        if (alive && warp * 32 < rows && warp < p.bulk_warps) {
+        if (BULK && alive && warp * 32 < rows) {
             const int row = warp * 32 + lane;
             const bool row_ok = row < rows;
             float *dst_row = p.acc + (int64_t)(row_ok ? s_scatter[b][row] : 0) * outw;
@@ -479,9 +479,9 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
                 if (row_ok) bulk_reduce_add_f32(dst_row + col0, my_park, (uint32_t)cols * 4);
                 bulk_commit();
             }
-        } else if (alive && warp * 32 < rows) {
-            // the remaining warps scatter from registers through the load/store pipe, so that
-            // the copy engine and the load/store pipe share the reduction traffic
+        } else if (!BULK && alive && warp * 32 < rows) {
+            // wide rows: scatter from registers (two-float vector reductions); with several
+            // 64-column blocks per row the single parking area would serialise the bulk reductions
             const int32_t *sc = s_scatter[b];
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
@@ -692,6 +692,17 @@ size_t pad_for_tmem(size_t smem, uint32_t ncols) {
     return smem > floor_bytes ? smem : floor_bytes;
 }
 
+// cudaFuncSetAttribute is a host-side round trip; raise the opt-in shared-memory
+// limit of a kernel only when a launch needs more than any launch before it.
+template <typename Kernel>
+int ensure_dynamic_smem(Kernel kernel, size_t smem, int *granted) {
+    if ((int)smem <= *granted) return PCX_OK;
+    PCX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PCX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    *granted = (int)smem;
+    return PCX_OK;
+}
+
 bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 }  // namespace
@@ -722,14 +733,15 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     p.gather = a.gather, p.scatter = a.scatter, p.seg = a.seg_offs, p.acc = a.acc;
     p.K = a.K, p.C = a.C, p.M = a.M, p.transpose = a.transpose, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
     p.ncols = pow2_cols((outw + 63) / 64 * 64);  // the epilogue reads blocks of up to 64 columns
-    p.bulk_warps = 4;
-    if (const char *e = getenv("PCX_BULK_WARPS")) p.bulk_warps = std::max(0, std::min(4, atoi(e)));
+    // rows of up to 64 floats leave through one bulk reduction each; wider rows from registers
+    bool bulk = outw <= 64;
+    if (const char *e = getenv("PCX_MVMR_SCATTER")) bulk = atoi(e) != 0;
     const int kb = (inw + 63) / 64, wb = (a.M + 63) / 64;
     const size_t static_smem = 6656;  // index rings, chunk table, barrier
     // parking area of the scatter: 64 columns per row when it fits, else 32
     const size_t fixed_part = 1024 + (size_t)wb * a.C * 128 + (size_t)kb * BLK_BYTES;
     p.slab = (outw >= 64 && fixed_part + (size_t)CH * (64 * 4 + 16) + static_smem <= 232448 - 1024) ? 64 : 32;
-    const size_t rest = 1024 + (size_t)wb * a.C * 128 + (size_t)CH * (p.slab * 4 + 16);
+    const size_t rest = 1024 + (size_t)wb * a.C * 128 + (bulk ? (size_t)CH * (p.slab * 4 + 16) : 0);
     // One A tile: it is free again as soon as the multiply has finished, so the
     // next gather still overlaps the scatter, and more CTAs fit on an SM.
     p.nbuf = 1;
@@ -738,13 +750,18 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     size_t smem = rest + (size_t)p.nbuf * kb * BLK_BYTES;
     smem = pad_for_tmem(smem, p.ncols);
     if (smem + static_smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "mvmr tensor kernel does not fit (smem %zu)", smem);
-    PCX_CUDA(cudaFuncSetAttribute(mvmr_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PCX_CUDA(cudaFuncSetAttribute(mvmr_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    static int granted_mvmr[2][64] = {};   // per scatter mode and device
+    int dev = 0;
+    PCX_CUDA(cudaGetDevice(&dev));
+    if (int rc = bulk ? ensure_dynamic_smem(mvmr_tc_kernel<true>, smem, &granted_mvmr[1][dev & 63])
+                      : ensure_dynamic_smem(mvmr_tc_kernel<false>, smem, &granted_mvmr[0][dev & 63]))
+        return rc;
     const int occ = ctas_per_sm(smem + static_smem, p.ncols);
     int64_t upper = a.T / CH + a.K + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
     prof_begin(a.transpose ? "mvmr_tc_kernel(dgrad)" : "mvmr_tc_kernel(fwd)", stream);
-    mvmr_tc_kernel<<<(unsigned)grid, 128, smem, stream>>>(p);
+    if (bulk) mvmr_tc_kernel<true><<<(unsigned)grid, 128, smem, stream>>>(p);
+    else mvmr_tc_kernel<false><<<(unsigned)grid, 128, smem, stream>>>(p);
     prof_end(stream);
     PCX_LAUNCH_CHECK();
     return PCX_OK;
@@ -779,8 +796,10 @@ int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
     size_t smem = fixed + stages * buf;
     smem = pad_for_tmem(smem, p.ncols);
     if (smem + static_smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "vvor tensor kernel does not fit (smem %zu)", smem);
-    PCX_CUDA(cudaFuncSetAttribute(vvor_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PCX_CUDA(cudaFuncSetAttribute(vvor_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    static int granted_vvor[64] = {};   // per device
+    int dev = 0;
+    PCX_CUDA(cudaGetDevice(&dev));
+    if (int rc = ensure_dynamic_smem(vvor_tc_kernel, smem, &granted_vvor[dev & 63])) return rc;
     const int occ = ctas_per_sm(smem + static_smem, p.ncols);
     int64_t upper = a.T / CH + a.n_o + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
