@@ -733,8 +733,11 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     p.gather = a.gather, p.scatter = a.scatter, p.seg = a.seg_offs, p.acc = a.acc;
     p.K = a.K, p.C = a.C, p.M = a.M, p.transpose = a.transpose, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
     p.ncols = pow2_cols((outw + 63) / 64 * 64);  // the epilogue reads blocks of up to 64 columns
-    // rows of up to 64 floats leave through one bulk reduction each; wider rows from registers
-    bool bulk = outw <= 64;
+    // Measured on B200: rows of exactly 64 floats leave fastest through one bulk reduction
+    // each (80 vs 84 us on the 150k-point scene); narrower and wider rows from registers
+    // (C = 32: 50 vs 59 us, C = 128: 160 vs 180 us, C = 256: 435 vs 671 us).  Folding rows
+    // with equal destinations in shared memory first was tried and cost more than it saved.
+    bool bulk = outw == 64;
     if (const char *e = getenv("PCX_MVMR_SCATTER")) bulk = atoi(e) != 0;
     const int kb = (inw + 63) / 64, wb = (a.M + 63) / 64;
     const size_t static_smem = 6656;  // index rings, chunk table, barrier
