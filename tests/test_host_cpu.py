@@ -189,3 +189,16 @@ def test_radius_predicate_switch_is_scoped():
     with pytest.raises(ValueError):
         with radius_predicate("exact"):
             pass
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    import json
+
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "Gtriplets/s" and line["value"] > 0
+    assert line["cpu_baseline"]["cores"] == 1 and line["cpu_baseline"]["kind"] in ("reference", "port")
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["value"] == line["value"]
+    assert line["config"]["workload"].startswith("indoor150k_c64_bf16") and line["vs_baseline"] is None
