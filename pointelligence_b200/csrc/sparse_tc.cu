@@ -317,6 +317,8 @@ struct MvmrTcParams {
     const int64_t *seg;
     float *acc;
     int K, C, M, transpose, fmt, nbuf, slab;  // slab: columns parked per bulk reduction (32 or 64)
+    int prow_log2;                            // a warp parks 2^prow_log2 rows at a time (8, 16 or 32)
+    uint32_t park_bytes;                      // size of the parking area (the chunk table follows it)
     uint32_t ncols;
 };
 
@@ -332,7 +334,6 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     __shared__ uint32_t s_tmem;
     __shared__ __align__(16) int32_t s_scatter[2][CH];
     __shared__ int32_t s_gather[2][CH];
-    __shared__ int32_t s_cum[MAX_TAPS_SMEM + 1];
     __shared__ int32_t s_warp_sums[4];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int inw = p.transpose ? p.M : p.C, outw = p.transpose ? p.C : p.M;
@@ -348,7 +349,11 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     const uint32_t bar = smem_u32(&s_bar);
     // per-warp parking area of the scatter: 32 rows of slab floats, rows padded by 16 bytes
     const uint32_t park_pitch = (uint32_t)p.slab * 4 + 16;
-    const uint32_t park = b_tile + (uint32_t)wb * w_blk + (uint32_t)warp * 32 * park_pitch;
+    const int prow = 1 << p.prow_log2;
+    const uint32_t park0 = b_tile + (uint32_t)wb * w_blk;
+    const uint32_t park = park0 + (uint32_t)(warp * prow) * park_pitch;
+    // chunk table behind the parking area
+    int32_t *s_cum = reinterpret_cast<int32_t *>(smem_raw + (park0 - smem_u32(smem_raw)) + p.park_bytes);
 
     if (tid == 0) {
         mbar_init(bar, 1);
@@ -462,22 +467,31 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
             const int row = warp * 32 + lane;
             const bool row_ok = row < rows;
             float *dst_row = p.acc + (int64_t)(row_ok ? s_scatter[b][row] : 0) * outw;
-            const uint32_t my_park = park + (uint32_t)lane * park_pitch;
-            for (int col0 = 0; col0 < outw; col0 += p.slab) {
-                bulk_wait_read();  // the previous reductions have read this warp's parking area
-                __syncwarp();
-                for (int c32 = 0; c32 < p.slab; c32 += 32) {
-                    float v[32];
-                    tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(col0 + c32), v);
+            // a warp parks `prow` rows at a time (32, or 16 when shared memory is better spent
+            // on one more resident CTA): lanes of the current batch store, the others only
+            // take part in the warp-wide TMEM load
+            const uint32_t my_park = park + (uint32_t)(lane & (prow - 1)) * park_pitch;
+            for (int batch = 0; batch * prow < 32; ++batch) {
+                const bool mine = (lane >> p.prow_log2) == batch;
+                if (warp * 32 + batch * prow >= rows) break;
+                for (int col0 = 0; col0 < outw; col0 += p.slab) {
+                    bulk_wait_read();  // the previous reductions have read this warp's parking area
+                    __syncwarp();
+                    for (int c32 = 0; c32 < p.slab; c32 += 32) {
+                        float v[32];
+                        tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(col0 + c32), v);
+                        if (mine) {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(my_park + (uint32_t)(c32 + 4 * q) * 4),
-                                     "f"(v[4 * q]), "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
+                            for (int q = 0; q < 8; ++q)
+                                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(my_park + (uint32_t)(c32 + 4 * q) * 4),
+                                             "f"(v[4 * q]), "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
+                        }
+                    }
+                    fence_async_smem();
+                    const int cols = min(p.slab, outw - col0);
+                    if (row_ok && mine) bulk_reduce_add_f32(dst_row + col0, my_park, (uint32_t)cols * 4);
+                    bulk_commit();
                 }
-                fence_async_smem();
-                const int cols = min(p.slab, outw - col0);
-                if (row_ok) bulk_reduce_add_f32(dst_row + col0, my_park, (uint32_t)cols * 4);
-                bulk_commit();
             }
         } else if (!BULK && alive && warp * 32 < rows) {
             // wide rows: scatter from registers (two-float vector reductions); with several
@@ -524,8 +538,6 @@ __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t s_bar;
     __shared__ uint32_t s_tmem;
-    __shared__ int32_t s_ia[MAX_STAGES][CH], s_ib[MAX_STAGES][CH];
-    __shared__ int32_t s_cum[MAX_TAPS_SMEM + 1];
     __shared__ int32_t s_warp_sums[4];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -534,6 +546,10 @@ __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
     const int bblk = (p.Cb + 63) >> 6;
     const uint32_t buf_bytes = (uint32_t)(ablk + bblk) * BLK_BYTES;
     const int NS = p.stages;
+    // behind the operand stages: the index rings of both operands, then the chunk table
+    int32_t(*s_ia)[CH] = reinterpret_cast<int32_t(*)[CH]>(smem_raw + (base - smem_u32(smem_raw)) + (size_t)NS * buf_bytes);
+    int32_t(*s_ib)[CH] = s_ia + NS;
+    int32_t *s_cum = reinterpret_cast<int32_t *>(s_ib + NS);
     const uint32_t bar = smem_u32(&s_bar);
 
     if (tid == 0) {
@@ -676,12 +692,24 @@ uint32_t pow2_cols(int n) {
 
 // CTAs per SM: bounded by shared memory (227 KiB usable, 1 KiB reserved per
 // CTA), by TMEM (512 columns) and by registers / warp slots.
-int ctas_per_sm(size_t smem, uint32_t ncols) {
+int ctas_per_sm(size_t smem, uint32_t ncols, int regs_per_thread) {
     int by_smem = (int)((size_t)232448 / (smem + 1024));
     int by_tmem = (int)(512 / ncols);
-    int occ = by_smem < by_tmem ? by_smem : by_tmem;
+    int by_regs = 65536 / (((regs_per_thread * 32 + 255) / 256 * 256) * 4);  // 128-thread CTAs
+    int occ = std::min(by_smem, std::min(by_tmem, by_regs));
     if (occ > 8) occ = 8;
     return occ < 1 ? 1 : occ;
+}
+
+// Registers per thread of a kernel (asked once per kernel; the persistent grids
+// must not exceed what is resident at once, or the surplus CTAs run as a second wave).
+template <typename Kernel>
+int kernel_registers(Kernel kernel, int *cached) {
+    if (*cached == 0) {
+        cudaFuncAttributes attr;
+        *cached = cudaFuncGetAttributes(&attr, kernel) == cudaSuccess ? attr.numRegs : 128;
+    }
+    return *cached;
 }
 
 // Dynamic shared memory padded so that at most 512 / ncols CTAs share an SM
@@ -734,17 +762,22 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     p.K = a.K, p.C = a.C, p.M = a.M, p.transpose = a.transpose, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
     p.ncols = pow2_cols((outw + 63) / 64 * 64);  // the epilogue reads blocks of up to 64 columns
     // Measured on B200: rows of exactly 64 floats leave fastest through one bulk reduction
-    // each (80 vs 84 us on the 150k-point scene); narrower and wider rows from registers
-    // (C = 32: 50 vs 59 us, C = 128: 160 vs 180 us, C = 256: 435 vs 671 us).  Folding rows
+    // each (64 vs 84 us on the 150k-point scene); narrower and wider rows from registers
+    // (C = 32: 50 vs 59 us, C = 128: 160 vs 180 us, C = 256: 390 vs 671 us).  Folding rows
     // with equal destinations in shared memory first was tried and cost more than it saved.
     bool bulk = outw == 64;
     if (const char *e = getenv("PCX_MVMR_SCATTER")) bulk = atoi(e) != 0;
     const int kb = (inw + 63) / 64, wb = (a.M + 63) / 64;
-    const size_t static_smem = 6656;  // index rings, chunk table, barrier
-    // parking area of the scatter: 64 columns per row when it fits, else 32
-    const size_t fixed_part = 1024 + (size_t)wb * a.C * 128 + (size_t)kb * BLK_BYTES;
-    p.slab = (outw >= 64 && fixed_part + (size_t)CH * (64 * 4 + 16) + static_smem <= 232448 - 1024) ? 64 : 32;
-    const size_t rest = 1024 + (size_t)wb * a.C * 128 + (bulk ? (size_t)CH * (p.slab * 4 + 16) : 0);
+    const size_t static_smem = 2176;  // index rings, barrier
+    const size_t table = align_up((size_t)(a.K + 1) * 4, 16);
+    p.slab = outw >= 64 ? 64 : 32;  // columns parked per bulk reduction
+    // Rows a warp parks at a time.  Fewer rows leave shared memory for more resident CTAs,
+    // which hide the gather latency (measured on the 150k-point scene, C = 64: 32 rows /
+    // 3 CTAs per SM 78 us, 16 rows / 5 CTAs 64 us, 8 rows / 6 CTAs 66 us).
+    p.prow_log2 = 4;
+    if (const char *e = getenv("PCX_MVMR_PARK_ROWS")) p.prow_log2 = atoi(e) == 32 ? 5 : atoi(e) == 8 ? 3 : 4;
+    p.park_bytes = bulk ? (uint32_t)(4 << p.prow_log2) * (p.slab * 4 + 16) : 0;
+    const size_t rest = 1024 + (size_t)wb * a.C * 128 + p.park_bytes + table;
     // One A tile: it is free again as soon as the multiply has finished, so the
     // next gather still overlaps the scatter, and more CTAs fit on an SM.
     p.nbuf = 1;
@@ -759,7 +792,10 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     if (int rc = bulk ? ensure_dynamic_smem(mvmr_tc_kernel<true>, smem, &granted_mvmr[1][dev & 63])
                       : ensure_dynamic_smem(mvmr_tc_kernel<false>, smem, &granted_mvmr[0][dev & 63]))
         return rc;
-    const int occ = ctas_per_sm(smem + static_smem, p.ncols);
+    static int regs_mvmr[2] = {0, 0};
+    const int regs = bulk ? kernel_registers(mvmr_tc_kernel<true>, &regs_mvmr[1])
+                          : kernel_registers(mvmr_tc_kernel<false>, &regs_mvmr[0]);
+    const int occ = ctas_per_sm(smem + static_smem, p.ncols, regs);
     int64_t upper = a.T / CH + a.K + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
     prof_begin(a.transpose ? "mvmr_tc_kernel(dgrad)" : "mvmr_tc_kernel(fwd)", stream);
@@ -777,9 +813,10 @@ int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
     p.n_o = (int)a.n_o, p.Ma = a.Ma, p.Cb = a.Cb, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
     const int row_tiles = (a.Ma + 127) / 128;
     p.ncols = pow2_cols((row_tiles - 1) * a.Cb + (a.Cb + 63) / 64 * 64);  // flushed in blocks of 64 columns
-    const size_t buf = (size_t)((a.Ma + 63) / 64 + (a.Cb + 63) / 64) * BLK_BYTES;
-    const size_t fixed = 1024;
-    const size_t static_smem = 10240;  // index rings, chunk table, barrier
+    // one stage = both operand tiles plus their index rows
+    const size_t buf = (size_t)((a.Ma + 63) / 64 + (a.Cb + 63) / 64) * BLK_BYTES + 2 * CH * sizeof(int32_t);
+    const size_t fixed = 1024 + align_up((size_t)(a.n_o + 1) * 4, 16);  // alignment slack, chunk table
+    const size_t static_smem = 128;  // barrier, TMEM address, scan scratch
     // One stage by default: measured on B200, more resident CTAs hide the gather
     // latency better than a deeper ring inside fewer CTAs (PCX_VVOR_STAGES raises it).
     int stages = 1, max_fit = 1;
@@ -803,7 +840,8 @@ int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
     int dev = 0;
     PCX_CUDA(cudaGetDevice(&dev));
     if (int rc = ensure_dynamic_smem(vvor_tc_kernel, smem, &granted_vvor[dev & 63])) return rc;
-    const int occ = ctas_per_sm(smem + static_smem, p.ncols);
+    static int regs_vvor = 0;
+    const int occ = ctas_per_sm(smem + static_smem, p.ncols, kernel_registers(vvor_tc_kernel, &regs_vvor));
     int64_t upper = a.T / CH + a.n_o + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
     prof_begin("vvor_tc_kernel", stream);
