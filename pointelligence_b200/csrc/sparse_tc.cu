@@ -13,15 +13,21 @@
 //          B = W[tap] exactly as stored, (C, M) row-major: read MN-major in the
 //              forward (its rows are the contraction index) and K-major in the
 //              input gradient (its rows are the output channels)
-//          two A tiles alternate: the gather of the next chunk overlaps the
-//          multiply and the scatter of the current one
-//          epilogue: TMEM -> registers -> padded smem -> per-row run-merged
-//          red.global.add.f32 (128 contiguous bytes per warp instruction).
+//          one A tile per CTA; latency is hidden by the other CTAs resident on the
+//          SM (5-6 at C = 64), so shared memory per CTA is kept as small as possible
+//          epilogue, rows of 64 floats: TMEM -> registers -> a parking area in shared
+//          memory (16 rows per warp at a time, aliased with the A tile) -> one bulk
+//          reduction (cp.reduce.async.bulk add.f32) per output row;
+//          other widths: TMEM -> registers -> red.global.add.v2.f32
 //   VVOR   D[Ma x Cb] += X[t x Ma]^T * G[t x Cb], t = triplets of the chunk
 //          both operands MN-major (a gathered row is contiguous along M / N,
 //          the triplet index is the contraction), accumulated in TMEM over all
-//          chunks of a tap and flushed once per (CTA, tap); a ring of 2-4
-//          operand buffers keeps the next gathers in flight.
+//          chunks of a tap and flushed once per (CTA, tap); one operand stage by
+//          default (a ring of up to 4 is available)
+//
+// Measured on B200, both kernels are bound by latency, not by a pipe: at C = 64 the
+// L2 runs at about a third of its throughput and DRAM at a tenth, and every step that
+// put more CTAs on an SM (3 -> 5 -> 6) shortened the kernel (78 -> 64 -> 62 us).
 //
 // One thread issues tcgen05.mma; completion is signalled with tcgen05.commit on
 // an mbarrier.  Every wait is bounded (one second): after the limit the kernel raises a flag
@@ -319,6 +325,7 @@ struct MvmrTcParams {
     int K, C, M, transpose, fmt, nbuf, slab;  // slab: columns parked per bulk reduction (32 or 64)
     int prow_log2;                            // a warp parks 2^prow_log2 rows at a time (8, 16 or 32)
     uint32_t park_bytes;                      // size of the parking area (the chunk table follows it)
+    int alias;                                // parking area shares the feature tile's memory
     uint32_t ncols;
 };
 
@@ -340,8 +347,10 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int kb = (inw + 63) >> 6;
     const uint32_t a_bytes = (uint32_t)kb * BLK_BYTES;
-    const uint32_t a_tile0 = base;
-    const uint32_t b_tile = a_tile0 + (uint32_t)p.nbuf * a_bytes;
+    // layout: weight tile | feature tile(s) | parking area | chunk table; when the parking area
+    // aliases the feature tile (p.alias) it starts where the feature tile starts
+    const uint32_t b_tile = base;
+    const uint32_t a_tile0 = b_tile + (uint32_t)((p.M + 63) >> 6) * (uint32_t)p.C * 128;
     const bool two = p.nbuf == 2;
     // the weight tile is W[tap] as stored: C rows of M channels, 64-channel blocks
     const int wb = (p.M + 63) >> 6;
@@ -350,10 +359,11 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
     // per-warp parking area of the scatter: 32 rows of slab floats, rows padded by 16 bytes
     const uint32_t park_pitch = (uint32_t)p.slab * 4 + 16;
     const int prow = 1 << p.prow_log2;
-    const uint32_t park0 = b_tile + (uint32_t)wb * w_blk;
+    const uint32_t a_all = (uint32_t)p.nbuf * a_bytes;
+    const uint32_t park0 = p.alias ? a_tile0 : a_tile0 + a_all;
     const uint32_t park = park0 + (uint32_t)(warp * prow) * park_pitch;
-    // chunk table behind the parking area
-    int32_t *s_cum = reinterpret_cast<int32_t *>(smem_raw + (park0 - smem_u32(smem_raw)) + p.park_bytes);
+    const uint32_t table_off = p.alias ? max(a_all, p.park_bytes) : a_all + p.park_bytes;
+    int32_t *s_cum = reinterpret_cast<int32_t *>(smem_raw + (a_tile0 - smem_u32(smem_raw)) + table_off);
 
     if (tid == 0) {
         mbar_init(bar, 1);
@@ -459,7 +469,7 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
             loaded_tap = c1.tap;
             cp_async_commit();
         }
-        if (have_next && !two) {  // single A tile: it is free as well
+        if (have_next && !two && !p.alias) {  // single A tile: it is free as well
             gather_tile<false>(a_tile0, p.feat, s_gather[b ^ 1], rows_next, inw, tid, 128);
             cp_async_commit();
         }
@@ -507,6 +517,16 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
                     tmem_ld_16x64(tmem + ((uint32_t)(warp * 32 + half * 16) << 16) + (uint32_t)col0, v);
                     scatter_block(p.acc, da, db, outw, col0, lane, v);
                 }
+            }
+        }
+        if (p.alias) {
+            // the parking area lies in the feature tile: gather the next chunk only after the
+            // reductions have read it (other resident CTAs cover the latency)
+            bulk_wait_read();
+            __syncthreads();
+            if (have_next) {
+                gather_tile<false>(a_tile0, p.feat, s_gather[b ^ 1], rows_next, inw, tid, 128);
+                cp_async_commit();
             }
         }
         c0 = c1;
@@ -777,13 +797,18 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     p.prow_log2 = 4;
     if (const char *e = getenv("PCX_MVMR_PARK_ROWS")) p.prow_log2 = atoi(e) == 32 ? 5 : atoi(e) == 8 ? 3 : 4;
     p.park_bytes = bulk ? (uint32_t)(4 << p.prow_log2) * (p.slab * 4 + 16) : 0;
-    const size_t rest = 1024 + (size_t)wb * a.C * 128 + p.park_bytes + table;
+    // The parking area shares the feature tile's memory: the next gather then waits for the
+    // reductions to drain, but one more CTA fits per SM (measured: 62 vs 65 us).
+    p.alias = bulk ? 1 : 0;
+    if (const char *e = getenv("PCX_MVMR_ALIAS")) p.alias = bulk && atoi(e) != 0;
+    const size_t rest = 1024 + (size_t)wb * a.C * 128 + (p.alias ? 0 : p.park_bytes) + table;
     // One A tile: it is free again as soon as the multiply has finished, so the
     // next gather still overlaps the scatter, and more CTAs fit on an SM.
     p.nbuf = 1;
     if (const char *e = getenv("PCX_MVMR_NBUF"))
         if (atoi(e) == 2 && rest + 2 * (size_t)kb * BLK_BYTES + static_smem <= 232448 - 1024) p.nbuf = 2;
-    size_t smem = rest + (size_t)p.nbuf * kb * BLK_BYTES;
+    if (p.alias) p.nbuf = 1;
+    size_t smem = rest + std::max((size_t)p.nbuf * kb * BLK_BYTES, p.alias ? (size_t)p.park_bytes : (size_t)0);
     smem = pad_for_tmem(smem, p.ncols);
     if (smem + static_smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "mvmr tensor kernel does not fit (smem %zu)", smem);
     static int granted_mvmr[2][64] = {};   // per scatter mode and device
