@@ -140,6 +140,47 @@ int pcx_vvor_static_scratch(const void *d_a, const int32_t *d_a_idx, const void 
                             void *stream);
 
 /* ------------------------------------------------------------------------
+ * Segment reductions (op: 0 sum, 1 mean, 2 max, 3 min; fp32 accumulation,
+ * inputs, outputs and gradients all in `dtype`).
+ *
+ * pcx_segment_reduce: out[s] = reduce of the rows of segment s, segments being
+ * consecutive runs of d_lengths[s] rows of x (N, C).  Replaces
+ * large_segment_reduce (sparse_engines/large_segment_reduce_triton.py:25-77,
+ * :180-188): empty segments give 0 (sum, mean) or -inf / +inf (max / min),
+ * fp16 results are clamped to +-65504.  _backward replaces :94-166: the
+ * gradient is broadcast (divided by max(len,1) for mean) or, for max / min,
+ * given to every element equal to the reduced value; d_x and d_out are only
+ * read for max / min.
+ *
+ * pcx_indexed_segment_reduce: y[k] = reduce over the d_lengths[k] consecutive
+ * entries e of list k of x[d_indices[e]].  Replaces indexed_segment_reduce
+ * (sparse_engines/indexed_segment_reduce_triton.py:25-63, :147-173): an empty
+ * list gives 0 (sum), NaN (mean) or -inf / +inf.  _backward replaces :84-140
+ * (scatter-add of the gradient; value match for max / min).
+ */
+size_t pcx_segment_reduce_workspace_bytes(int64_t S, int C);
+int pcx_segment_reduce(const void *d_x, const int64_t *d_lengths, void *d_out,
+                       int64_t N, int64_t S, int C, int op, int dtype,
+                       void *d_ws, size_t ws_bytes, void *stream);
+int pcx_segment_reduce_backward(const void *d_grad_out, const void *d_x,
+                                const void *d_out, const int64_t *d_lengths,
+                                void *d_grad_x, int64_t N, int64_t S, int C,
+                                int op, int dtype, void *d_ws, size_t ws_bytes,
+                                void *stream);
+size_t pcx_indexed_segment_reduce_workspace_bytes(int64_t K, int64_t n_x, int C,
+                                                  int dtype, int backward);
+int pcx_indexed_segment_reduce(const void *d_x, const int32_t *d_indices,
+                               const int64_t *d_lengths, void *d_y, int64_t n_x,
+                               int64_t E, int64_t K, int C, int op, int dtype,
+                               void *d_ws, size_t ws_bytes, void *stream);
+int pcx_indexed_segment_reduce_backward(const void *d_grad_y, const void *d_x,
+                                        const void *d_y, const int32_t *d_indices,
+                                        const int64_t *d_lengths, void *d_grad_x,
+                                        int64_t n_x, int64_t E, int64_t K, int C,
+                                        int op, int dtype, void *d_ws,
+                                        size_t ws_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
  * Tap bookkeeping.
  * pcx_seg_offs: seg[k] = first position with value >= k in a sorted int32
  *   array (sparse_engines/_seg_offs.py:21-44, kernel_offset_segments).

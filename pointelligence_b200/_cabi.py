@@ -48,6 +48,16 @@ SIGNATURES = {
     "pcx_vvor": (c_int, [c_void_p] * 7 + [c_int64] * 4 + [c_int] * 5 + [c_void_p, c_size_t, c_void_p]),
     "pcx_vvor_static_scratch_max_elements": (c_size_t, []),
     "pcx_vvor_static_scratch": (c_int, [c_void_p] * 6 + [c_int64] * 4 + [c_int] * 4 + [c_void_p]),
+    "pcx_segment_reduce_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "pcx_segment_reduce": (c_int, [c_void_p] * 3 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_size_t,
+                                                   c_void_p]),
+    "pcx_segment_reduce_backward": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
+                                                            c_size_t, c_void_p]),
+    "pcx_indexed_segment_reduce_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int, c_int]),
+    "pcx_indexed_segment_reduce": (c_int, [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 3 + [c_void_p, c_size_t,
+                                                                                         c_void_p]),
+    "pcx_indexed_segment_reduce_backward": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int] * 3
+                                            + [c_void_p, c_size_t, c_void_p]),
     "pcx_seg_offs": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "pcx_expand_taps": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "pcx_set_radius_predicate": (c_int, [c_int]),
@@ -220,6 +230,74 @@ def vvor_static_scratch(a, a_idx, b, b_idx, seg_offs, out):
                                             a_idx.numel(), a.shape[0], b.shape[0], n_o, G, Ma, Cb, code,
                                             stream_ptr()))
     return out
+
+
+REDUCE_OPS = {"sum": 0, "mean": 1, "max": 2, "min": 3}
+
+
+def segment_reduce(x, lengths, op):
+    """``out[s] = op`` over the ``lengths[s]`` consecutive rows of segment s; x (N, C) -> (S, C)."""
+    require_cuda(x, lengths)
+    x = x.contiguous()
+    lengths = lengths.to(torch.int64).contiguous()
+    N, C = x.shape
+    S = lengths.numel()
+    out = torch.empty((S, C), dtype=x.dtype, device=x.device)
+    L = lib()
+    with torch.cuda.device(x.device):
+        ws = workspace(L.pcx_segment_reduce_workspace_bytes(S, C), x.device)
+        check(L.pcx_segment_reduce(ptr(x), ptr(lengths), ptr(out), N, S, C, op, dtype_code(x.dtype), ptr(ws),
+                                   ws.numel(), stream_ptr()))
+    return out
+
+
+def segment_reduce_backward(grad_out, x, out, lengths, op, n_rows):
+    require_cuda(grad_out, lengths)
+    grad_out = grad_out.contiguous()
+    lengths = lengths.to(torch.int64).contiguous()
+    S, C = grad_out.shape
+    grad_x = torch.empty((n_rows, C), dtype=grad_out.dtype, device=grad_out.device)
+    L = lib()
+    with torch.cuda.device(grad_out.device):
+        ws = workspace(L.pcx_segment_reduce_workspace_bytes(S, 1), grad_out.device)
+        check(L.pcx_segment_reduce_backward(ptr(grad_out), ptr(x), ptr(out), ptr(lengths), ptr(grad_x), n_rows, S, C,
+                                            op, dtype_code(grad_out.dtype), ptr(ws), ws.numel(), stream_ptr()))
+    return grad_x
+
+
+def indexed_segment_reduce(x, indices, lengths, op):
+    """``y[k] = op`` over ``x[indices[e]]`` for the ``lengths[k]`` consecutive entries of list k."""
+    require_cuda(x, indices, lengths)
+    x = x.contiguous()
+    indices = as_i32(indices)
+    lengths = lengths.to(torch.int64).contiguous()
+    n_x, C = x.shape
+    K = lengths.numel()
+    y = torch.empty((K, C), dtype=x.dtype, device=x.device)
+    L = lib()
+    code = dtype_code(x.dtype)
+    with torch.cuda.device(x.device):
+        ws = workspace(L.pcx_indexed_segment_reduce_workspace_bytes(K, n_x, C, code, 0), x.device)
+        check(L.pcx_indexed_segment_reduce(ptr(x), ptr(indices), ptr(lengths), ptr(y), n_x, indices.numel(), K, C, op,
+                                           code, ptr(ws), ws.numel(), stream_ptr()))
+    return y
+
+
+def indexed_segment_reduce_backward(grad_y, x, y, indices, lengths, op, n_x):
+    require_cuda(grad_y, indices, lengths)
+    grad_y = grad_y.contiguous()
+    indices = as_i32(indices)
+    lengths = lengths.to(torch.int64).contiguous()
+    K, C = grad_y.shape
+    grad_x = torch.empty((n_x, C), dtype=grad_y.dtype, device=grad_y.device)
+    L = lib()
+    code = dtype_code(grad_y.dtype)
+    with torch.cuda.device(grad_y.device):
+        ws = workspace(L.pcx_indexed_segment_reduce_workspace_bytes(K, n_x, C, code, 1), grad_y.device)
+        check(L.pcx_indexed_segment_reduce_backward(ptr(grad_y), ptr(x), ptr(y), ptr(indices), ptr(lengths),
+                                                    ptr(grad_x), n_x, indices.numel(), K, C, op, code, ptr(ws),
+                                                    ws.numel(), stream_ptr()))
+    return grad_x
 
 
 def seg_offs_from_sorted(idx_sorted, K):

@@ -22,6 +22,10 @@ What runs, per file:
 ``voxelize.npz``     ``layers.triplets.voxelize_3d`` and the scalar formulas.
 ``sparse.npz``       the reference's CPU MVMR / VVOR operators compiled from
     its C++ sources (oracle/build_ref.py).
+``segment.npz``      ``sparse_engines.ops.large_segment_reduce`` and
+    ``indexed_segment_reduce`` (Triton kernels under the interpreter, forward
+    and autograd backward) and ``layers.norm.Ragged{Layer,Instance,Group}Norm``
+    (plain torch on CPU).
 
 Inputs are stored next to the outputs so that no random-number generator has
 to agree between machines.
@@ -232,6 +236,67 @@ def gen_sparse(torch, out):
         out[f"{name}.vvor"] = sparse_ops.vvor_ref(b, bi, go, oi, ai, K)
 
 
+def gen_segment(torch, out):
+    """Segment reductions (Triton kernels under the interpreter, forward and
+    autograd backward) and the ragged norm layers (plain torch on CPU)."""
+    # interpreted kernels are plain callables: torch's wrapper (which only accepts compiled
+    # kernels) is bypassed before the reference modules import it
+    import torch.library
+
+    torch.library.wrap_triton = lambda kernel: kernel
+    from layers.norm import RaggedGroupNorm, RaggedInstanceNorm, RaggedLayerNorm
+    from sparse_engines.ops import indexed_segment_reduce, large_segment_reduce
+    import sparse_engines.indexed_segment_reduce_triton as isr
+
+    # the forward kernel is wrapped in an autotuner (launch parameters only), which wants
+    # a GPU to time its candidates: run the kernel it wraps
+    isr.indexed_segment_reduce_fwd_kernel = isr.indexed_segment_reduce_fwd_kernel.fn
+
+    rng = np.random.default_rng(11)
+    with torch.enable_grad():
+        for name, (lengths, C) in {
+            "ragged": ([70, 0, 5, 130, 1, 64], 20),      # boundaries inside and at block edges, an empty segment
+            "single": ([200], 33),
+            "wide": ([3, 90, 40], 96),
+        }.items():
+            n = int(sum(lengths))
+            x = np.round(rng.standard_normal((n, C)) * 4).astype(np.float32) / 4   # ties for max / min
+            go = rng.standard_normal((len(lengths), C)).astype(np.float32)
+            out[f"large.{name}.x"], out[f"large.{name}.lengths"], out[f"large.{name}.go"] = x, np.asarray(lengths), go
+            for op in ("sum", "mean", "max", "min"):
+                xt = torch.from_numpy(x).requires_grad_(True)
+                y = large_segment_reduce(xt, op, lengths=torch.tensor(lengths))
+                y.backward(torch.from_numpy(go))
+                out[f"large.{name}.{op}"] = y.detach().numpy()
+                out[f"large.{name}.{op}.grad"] = xt.grad.numpy()
+        for name, (lengths, n_x, C) in {
+            "pool": ([3, 1, 4, 2, 0, 7, 1], 12, 16),
+            "wide": ([5, 5, 9, 1], 30, 70),
+        }.items():
+            E = int(sum(lengths))
+            x = np.round(rng.standard_normal((n_x, C)) * 4).astype(np.float32) / 4
+            idx = rng.integers(0, n_x, E).astype(np.int64)
+            go = rng.standard_normal((len(lengths), C)).astype(np.float32)
+            out[f"indexed.{name}.x"], out[f"indexed.{name}.indices"] = x, idx
+            out[f"indexed.{name}.lengths"], out[f"indexed.{name}.go"] = np.asarray(lengths), go
+            for op in ("sum", "mean", "max", "min"):
+                xt = torch.from_numpy(x).requires_grad_(True)
+                y = indexed_segment_reduce(xt, op, torch.from_numpy(idx), lengths=torch.tensor(lengths))
+                y.backward(torch.from_numpy(go))
+                out[f"indexed.{name}.{op}"] = y.detach().numpy()
+                out[f"indexed.{name}.{op}.grad"] = xt.grad.numpy()
+    lengths = [40, 7, 90]
+    x = rng.standard_normal((sum(lengths), 24)).astype(np.float32)
+    w = rng.standard_normal(24).astype(np.float32)
+    b = rng.standard_normal(24).astype(np.float32)
+    out["norm.x"], out["norm.lengths"], out["norm.weight"], out["norm.bias"] = x, np.asarray(lengths), w, b
+    for kind, layer in (("layer", RaggedLayerNorm(24)), ("instance", RaggedInstanceNorm(24, affine=True)),
+                        ("group", RaggedGroupNorm(4, 24))):
+        layer.weight.data = torch.from_numpy(w)
+        layer.bias.data = torch.from_numpy(b)
+        out[f"norm.{kind}"] = layer(torch.from_numpy(x), torch.tensor(lengths)).detach().numpy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("POINTELLIGENCE_REFERENCE", "/root/reference"))
@@ -242,7 +307,7 @@ def main():
 
     _patch_libdevice()
     gens = dict(downsample=gen_downsample, radius=gen_radius, voxelize=gen_voxelize,
-                sparse=gen_sparse)
+                sparse=gen_sparse, segment=gen_segment)
     for name, fn in gens.items():
         if args.only and name not in args.only.split(","):
             continue

@@ -144,3 +144,43 @@ def test_reference_cpu_ops_when_built(golden):
     out = os_.mvmr_ref(z[f"{name}.a"], z[f"{name}.a_idx"], z[f"{name}.b"],
                        z[f"{name}.b_idx"], z[f"{name}.o_idx"], int(z[f"{name}.n_o"]))
     assert np.array_equal(out, z[f"{name}.mvmr"])
+
+
+def _segment_cases(z, prefix):
+    return sorted({k.split(".")[1] for k in z.files if k.startswith(prefix + ".")})
+
+
+def test_segment_reduce_oracle_matches_reference_golden(golden):
+    """oracle/segment_ops.py against the reference's Triton kernels (run under the
+    interpreter): forward values and autograd gradients of both reductions."""
+    from oracle import segment_ops as seg
+
+    z = golden("segment")
+    for name in _segment_cases(z, "large"):
+        x, lengths, go = z[f"large.{name}.x"], z[f"large.{name}.lengths"], z[f"large.{name}.go"]
+        for op in ("sum", "mean", "max", "min"):
+            want = z[f"large.{name}.{op}"]
+            got = seg.large_segment_reduce(x, lengths, op)
+            np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5, err_msg=f"{name} {op}")
+            grad = seg.large_segment_reduce_grad(go, x, want, lengths, op)
+            np.testing.assert_allclose(grad, z[f"large.{name}.{op}.grad"], rtol=1e-5, atol=1e-6, err_msg=f"{name} {op}")
+    for name in _segment_cases(z, "indexed"):
+        x, idx = z[f"indexed.{name}.x"], z[f"indexed.{name}.indices"]
+        lengths, go = z[f"indexed.{name}.lengths"], z[f"indexed.{name}.go"]
+        for op in ("sum", "mean", "max", "min"):
+            want = z[f"indexed.{name}.{op}"]
+            got = seg.indexed_segment_reduce(x, idx, lengths, op)
+            np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5, equal_nan=True, err_msg=f"{name} {op}")
+            grad = seg.indexed_segment_reduce_grad(go, x, want, idx, lengths, op, len(x))
+            np.testing.assert_allclose(grad, z[f"indexed.{name}.{op}.grad"], rtol=1e-5, atol=1e-6,
+                                       err_msg=f"{name} {op}")
+
+
+def test_ragged_norm_oracle_matches_reference_golden(golden):
+    from oracle import segment_ops as seg
+
+    z = golden("segment")
+    for kind in ("layer", "instance", "group"):
+        got = seg.ragged_norm(z["norm.x"], z["norm.lengths"], kind, num_groups=4, weight=z["norm.weight"],
+                              bias=z["norm.bias"])
+        np.testing.assert_allclose(got, z[f"norm.{kind}"], rtol=1e-4, atol=1e-5, err_msg=kind)
