@@ -181,6 +181,34 @@ int pcx_indexed_segment_reduce_backward(const void *d_grad_y, const void *d_x,
                                         size_t ws_bytes, void *stream);
 
 /* ------------------------------------------------------------------------
+ * Fused layer normalisation over a ragged batch (samples = consecutive runs of
+ * d_lengths[s] rows), with the residual add and the ReLU of a residual block:
+ *   y = relu?((x - mean_s) * rstd_s * weight + bias (+ residual))
+ * mean_s / rstd_s over all rows x channels of sample s, two-pass, as
+ * RaggedLayerNorm composes them (layers/norm.py:59-83, :118-130 of the
+ * reference, which runs it as a chain of torch reductions and elementwise
+ * launches).  d_weight / d_bias (fp32, C) may both be null (no affine);
+ * d_residual may be null.  d_mean / d_rstd (fp32, S) are outputs kept for the
+ * backward.  _backward: d_y is read only when relu != 0; d_grad_weight /
+ * d_grad_bias (fp32, C) and d_grad_residual may be null.
+ */
+size_t pcx_ragged_layer_norm_workspace_bytes(int64_t S);
+int pcx_ragged_layer_norm(const void *d_x, const int64_t *d_lengths,
+                          const float *d_weight, const float *d_bias,
+                          const void *d_residual, void *d_y, float *d_mean,
+                          float *d_rstd, int64_t N, int64_t S, int C, double eps,
+                          int relu, int dtype, void *d_ws, size_t ws_bytes,
+                          void *stream);
+int pcx_ragged_layer_norm_backward(const void *d_grad_y, const void *d_x,
+                                   const void *d_y, const int64_t *d_lengths,
+                                   const float *d_weight, const float *d_mean,
+                                   const float *d_rstd, void *d_grad_x,
+                                   float *d_grad_weight, float *d_grad_bias,
+                                   void *d_grad_residual, int64_t N, int64_t S,
+                                   int C, int relu, int dtype, void *d_ws,
+                                   size_t ws_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
  * Tap bookkeeping.
  * pcx_seg_offs: seg[k] = first position with value >= k in a sorted int32
  *   array (sparse_engines/_seg_offs.py:21-44, kernel_offset_segments).

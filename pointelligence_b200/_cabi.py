@@ -58,6 +58,11 @@ SIGNATURES = {
                                                                                          c_void_p]),
     "pcx_indexed_segment_reduce_backward": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int] * 3
                                             + [c_void_p, c_size_t, c_void_p]),
+    "pcx_ragged_layer_norm_workspace_bytes": (c_size_t, [c_int64]),
+    "pcx_ragged_layer_norm": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_double, c_int, c_int, c_void_p,
+                                                      c_size_t, c_void_p]),
+    "pcx_ragged_layer_norm_backward": (c_int, [c_void_p] * 11 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
+                                                                c_size_t, c_void_p]),
     "pcx_seg_offs": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "pcx_expand_taps": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "pcx_set_radius_predicate": (c_int, [c_int]),
@@ -298,6 +303,53 @@ def indexed_segment_reduce_backward(grad_y, x, y, indices, lengths, op, n_x):
                                                     ptr(grad_x), n_x, indices.numel(), K, C, op, code, ptr(ws),
                                                     ws.numel(), stream_ptr()))
     return grad_x
+
+
+def _f32_or_none(t):
+    return None if t is None else t.detach().to(torch.float32).contiguous()
+
+
+def ragged_layer_norm(x, lengths, weight, bias, residual, eps, relu):
+    """Fused ``relu?(layer_norm_per_sample(x) * weight + bias (+ residual))``; returns ``(y, mean, rstd)``."""
+    require_cuda(x, lengths, weight, bias, residual)
+    x = x.contiguous()
+    lengths = lengths.to(torch.int64).contiguous()
+    weight, bias = _f32_or_none(weight), _f32_or_none(bias)
+    residual = None if residual is None else residual.to(x.dtype).contiguous()
+    N, C = x.shape
+    S = lengths.numel()
+    y = torch.empty_like(x)
+    mean = torch.empty(S, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(S, dtype=torch.float32, device=x.device)
+    L = lib()
+    with torch.cuda.device(x.device):
+        ws = workspace(L.pcx_ragged_layer_norm_workspace_bytes(S), x.device)
+        check(L.pcx_ragged_layer_norm(ptr(x), ptr(lengths), ptr(weight), ptr(bias), ptr(residual), ptr(y), ptr(mean),
+                                      ptr(rstd), N, S, C, float(eps), int(bool(relu)), dtype_code(x.dtype), ptr(ws),
+                                      ws.numel(), stream_ptr()))
+    return y, mean, rstd
+
+
+def ragged_layer_norm_backward(grad_y, x, y, lengths, weight, mean, rstd, relu, want_affine, want_residual):
+    """Returns ``(grad_x, grad_weight|None, grad_bias|None, grad_residual|None)`` (affine gradients in fp32)."""
+    require_cuda(grad_y, x, lengths)
+    grad_y, x = grad_y.contiguous(), x.contiguous()
+    lengths = lengths.to(torch.int64).contiguous()
+    weight = _f32_or_none(weight)
+    N, C = x.shape
+    S = lengths.numel()
+    grad_x = torch.empty_like(x)
+    gw = torch.empty(C, dtype=torch.float32, device=x.device) if want_affine else None
+    gb = torch.empty(C, dtype=torch.float32, device=x.device) if want_affine else None
+    gres = torch.empty_like(x) if want_residual else None
+    L = lib()
+    with torch.cuda.device(x.device):
+        ws = workspace(L.pcx_ragged_layer_norm_workspace_bytes(S), x.device)
+        check(L.pcx_ragged_layer_norm_backward(ptr(grad_y), ptr(x), ptr(y), ptr(lengths), ptr(weight), ptr(mean),
+                                               ptr(rstd), ptr(grad_x), ptr(gw), ptr(gb), ptr(gres), N, S, C,
+                                               int(bool(relu)), dtype_code(x.dtype), ptr(ws), ws.numel(),
+                                               stream_ptr()))
+    return grad_x, gw, gb, gres
 
 
 def seg_offs_from_sorted(idx_sorted, K):

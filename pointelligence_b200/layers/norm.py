@@ -14,9 +14,46 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
+from .. import _cabi
 from ..sparse_engines.segment_reduce import large_segment_reduce
 
-__all__ = ["RaggedNorm", "RaggedBatchNorm", "RaggedInstanceNorm", "RaggedLayerNorm", "RaggedGroupNorm"]
+__all__ = ["RaggedNorm", "RaggedBatchNorm", "RaggedInstanceNorm", "RaggedLayerNorm", "RaggedGroupNorm",
+           "fused_layer_norm"]
+
+
+class _FusedLayerNorm(torch.autograd.Function):
+    """One autograd node over the library's fused kernels (``pcx_ragged_layer_norm`` and its
+    backward): statistics, affine, optional residual add and ReLU."""
+
+    @staticmethod
+    def forward(ctx, x, lengths, weight, bias, residual, eps, relu):
+        y, mean, rstd = _cabi.ragged_layer_norm(x, lengths, weight, bias, residual, eps, relu)
+        ctx.save_for_backward(x, y, lengths, weight, mean, rstd)
+        ctx.relu, ctx.has_residual = bool(relu), residual is not None
+        ctx.param_dtypes = (None if weight is None else weight.dtype, None if bias is None else bias.dtype)
+        ctx.residual_dtype = None if residual is None else residual.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, y, lengths, weight, mean, rstd = ctx.saved_tensors
+        want_affine = weight is not None and (ctx.needs_input_grad[2] or ctx.needs_input_grad[3])
+        want_res = ctx.has_residual and ctx.needs_input_grad[4]
+        gx, gw, gb, gres = _cabi.ragged_layer_norm_backward(grad_y, x, y, lengths, weight, mean, rstd, ctx.relu,
+                                                            want_affine, want_res)
+        if gw is not None:
+            gw, gb = gw.to(ctx.param_dtypes[0]), gb.to(ctx.param_dtypes[1])
+        if gres is not None:
+            gres = gres.to(ctx.residual_dtype)
+        return gx, None, gw, gb, gres, None, None
+
+
+def fused_layer_norm(x, lengths, weight=None, bias=None, eps=1e-5, residual=None, relu=False):
+    """``relu?(RaggedLayerNorm(x) (+ residual))`` in one pass over the data (CUDA tensors only).
+
+    Same arithmetic as ``RaggedLayerNorm`` (layers/norm.py:59-83,118-130 of the reference) followed by
+    the ``out += identity; relu(out)`` tail of its residual blocks (models/resnet.py:129-130)."""
+    return _FusedLayerNorm.apply(x, lengths, weight, bias, residual, eps, relu)
 
 
 class RaggedNorm(nn.Module):
@@ -47,6 +84,8 @@ class RaggedNorm(nn.Module):
             return self.bn(x.float()).to(input_dtype)
         if lengths is None:
             raise ValueError(f"lengths argument is required for {self.norm_type} norm")
+        if self.norm_type == "layer" and self.reduce_fn is None and x.is_cuda:
+            return fused_layer_norm(x, lengths, self.weight, self.bias, self.eps)
         x = x.float()
         if self.norm_type == "instance":
             x_norm = self._instance_norm(x, lengths)

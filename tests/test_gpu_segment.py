@@ -165,3 +165,40 @@ def test_segment_reduce_rejects_bad_arguments_and_handles_empty():
         large_segment_reduce(torch.zeros((4, 8)), "sum", lengths=torch.tensor([4]))
     with pytest.raises(ValueError):
         _cabi.segment_reduce(torch.ones((4, 8), device="cuda:0"), torch.tensor([4], device="cuda:0"), 7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_layer_norm_residual_relu_matches_composition(dtype):
+    """The fused kernel (statistics + affine + residual + ReLU, forward and backward)
+    against the layer composed from torch operators, on samples that span many blocks
+    and on boundaries inside a block."""
+    from pointelligence_b200.layers import RaggedLayerNorm
+    from pointelligence_b200.layers.norm import fused_layer_norm
+
+    def torch_reduce(v, reduce, lengths):
+        return torch.segment_reduce(v, reduce=reduce, lengths=lengths, axis=0)
+
+    rng = np.random.default_rng(5)
+    lengths = _t(np.array([3000, 1, 5000, 300]))
+    C = 48
+    x0 = _t(rng.standard_normal((8301, C)) * 2 + 0.5, dtype)
+    r0 = _t(rng.standard_normal((8301, C)), dtype)
+    composed = RaggedLayerNorm(C, reduce_fn=torch_reduce).to("cuda:0")
+    composed.weight.data = _t(rng.standard_normal(C).astype(np.float32))
+    composed.bias.data = _t(rng.standard_normal(C).astype(np.float32))
+    go = _t(rng.standard_normal((8301, C)), dtype)
+    results = []
+    for fused in (True, False):
+        x, r = x0.clone().requires_grad_(True), r0.clone().requires_grad_(True)
+        composed.zero_grad()
+        if fused:
+            y = fused_layer_norm(x, lengths, composed.weight, composed.bias, composed.eps, residual=r, relu=True)
+        else:
+            y = torch.relu(composed(x.float(), lengths) + r.float()).to(dtype)
+        y.backward(go)
+        results.append([t.detach().float().cpu().numpy() for t in
+                        (y, x.grad, r.grad, composed.weight.grad, composed.bias.grad)])
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    for name, a, b in zip(("y", "dx", "dresidual", "dweight", "dbias"), *results):
+        scale = max(1.0, np.abs(b).max())
+        assert np.abs(a - b).max() <= tol * scale, (name, np.abs(a - b).max(), scale)
