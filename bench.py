@@ -442,6 +442,76 @@ def run_ours(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_block_ops(args, local_rank):
+    """Secondary workload: the non-convolution passes of a residual block on the same scene
+    (fused ragged layer norm forward / backward, global mean pool, strided max pool).  One JSON
+    line: per-kernel milliseconds (CUDA events, L2 flushed before every timed call) and the
+    algorithmic bytes of each pass over its time, against the measured HBM copy bandwidth."""
+    import torch
+
+    from pointelligence_b200.layers import GlobalPool, MetaData, max_pool3d
+    from pointelligence_b200.layers.norm import fused_layer_norm
+    from pointelligence_b200.synthetic import indoor_scene
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    pts = torch.from_numpy(indoor_scene(args.points, 0)).to(dev)
+    n, C, e = pts.shape[0], args.channels, 2
+    sizes = torch.tensor([n], device=dev)
+    sample = torch.zeros(n, dtype=torch.int64, device=dev)
+    g = torch.Generator(device=dev).manual_seed(1)
+    x = torch.randn(n, C, device=dev, generator=g).bfloat16()
+    res = torch.randn(n, C, device=dev, generator=g).bfloat16()
+    go = torch.randn(n, C, device=dev, generator=g).bfloat16()
+    w = torch.rand(C, device=dev, generator=g) + 0.5
+    b = torch.randn(C, device=dev, generator=g)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    m = MetaData(points=pts, sample_inds=sample, sample_sizes=sizes, grid_size=0.02)
+    _, m2 = max_pool3d(x, m, kernel_size=3, stride=2)
+    E, n_out = int(m2.j.numel()), int(m2.points.shape[0])
+    from pointelligence_b200.sparse_engines.ops import indexed_segment_reduce
+
+    xr = x.clone().requires_grad_(True)
+    rr = res.clone().requires_grad_(True)
+    y_ln = fused_layer_norm(xr, sizes, w, b, 1e-5, residual=rr, relu=True)
+    y_mp = indexed_segment_reduce(xr, "max", m2.j, lengths=m2.num_neighbors)
+    go_mp = torch.randn(n_out, C, device=dev, generator=g).bfloat16()
+    passes = {
+        "layer_norm_residual_relu_fwd": (lambda: fused_layer_norm(x, sizes, w, b, 1e-5, residual=res, relu=True),
+                                         3 * n * C * e),
+        "layer_norm_residual_relu_bwd": (lambda: torch.autograd.grad(y_ln, (xr, rr), go, retain_graph=True),
+                                         5 * n * C * e),
+        "global_mean_pool": (lambda: GlobalPool("mean")(x, sizes), n * C * e),
+        "max_pool3d_stride2_fwd": (lambda: indexed_segment_reduce(x, "max", m2.j, lengths=m2.num_neighbors),
+                                   E * (C * e + 4) + n_out * (C * e + 8)),
+        "max_pool3d_stride2_bwd": (lambda: torch.autograd.grad(y_mp, xr, go_mp, retain_graph=True),
+                                   E * (2 * C * e + 4) + n_out * 2 * C * e + n * C * e),
+    }
+    hbm, peak_kind = _peaks()
+    out = {}
+    for name, (fn, nbytes) in passes.items():
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        ms = []
+        for _ in range(args.steps):
+            flush.fill_(1)
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            z.record()
+            torch.cuda.synchronize()
+            ms.append(a.elapsed_time(z))
+        t = statistics.median(ms)
+        out[name] = {"ms": t, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (t * 1e-3) / 1e9,
+                     "frac_of_hbm_peak": nbytes / (t * 1e-3) / 1e9 / hbm}
+    print(json.dumps({"metric": "residual_block_passes", "unit": "ms", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"indoor{n}_c{C}_bf16 block passes", "points": n, "channels": C,
+                                 "pool_edges": E, "pool_outputs": n_out,
+                                 "l2": "flushed before every timed call (256 MiB write)"},
+                      "peak": hbm, "peak_source": peak_kind, "passes": out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -453,6 +523,8 @@ def main():
     ap.add_argument("--overlap-grads", action="store_true",
                     help="run the weight gradient on a second stream beside the input gradient "
                          "(kernel timings then include the contention)")
+    ap.add_argument("--workload", default="conv", choices=["conv", "block_ops"],
+                    help="conv: the headline convolution step; block_ops: norm / pooling passes of a residual block")
     ap.add_argument("--resident-only", action="store_true",
                     help="skip the host-buffer and CPU legs (for profiler captures of the kernels)")
     args = ap.parse_args()
@@ -461,6 +533,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "block_ops":
+        if rank == 0:
+            run_block_ops(args, local_rank)
         return
     run_ours(args, rank, local_rank, world)
 

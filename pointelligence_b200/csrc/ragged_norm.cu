@@ -17,22 +17,14 @@
 //   dresidual = g'.
 #include <cub/cub.cuh>
 
+#include "rowwise.cuh"
 #include "sparse_kernels.cuh"
 
 namespace pcx {
 namespace {
 
-constexpr int LN_ROWS = 256;      // rows per block
+constexpr int LN_ROWS = 512;      // rows per block
 constexpr int LN_THREADS = 256;
-
-__device__ __forceinline__ int64_t sample_of(const int64_t *__restrict__ offsets, int64_t S, int64_t row) {
-    int64_t lo = 0, hi = S;
-    while (lo < hi) {
-        int64_t mid = (lo + hi) >> 1;
-        if (offsets[mid + 1] <= row) lo = mid + 1; else hi = mid;
-    }
-    return lo;
-}
 
 __device__ __forceinline__ float block_sum(float v, float *scratch) {
 #pragma unroll
@@ -50,38 +42,56 @@ __global__ void ln_tail_kernel(int64_t *offsets, int64_t S, int64_t total) {
     if (threadIdx.x == 0 && blockIdx.x == 0) offsets[S] = total;
 }
 
-// sums[s] += sum of x (mean == null) or of (x - mean_s)^2 over the block's rows.
-// A block that lies inside one sample reduces in shared memory and issues one
-// atomic; the few blocks that straddle a boundary add per thread.
-template <typename T>
+// The kernels below share one shape: a block owns LN_ROWS consecutive rows, a thread
+// keeps one vector column (VN channels, one 16-byte access when VN > 1) and walks the
+// rows of its row lane.  `uniform` blocks lie inside one sample (all but S - 1 of them).
+struct BlockRows {
+    int64_t row0, row1, s_first;
+    bool uniform;
+    __device__ __forceinline__ BlockRows(const int64_t *__restrict__ offsets, int64_t N, int64_t S) {
+        row0 = (int64_t)blockIdx.x * LN_ROWS;
+        row1 = min(N, row0 + LN_ROWS);
+        s_first = segment_of_row(offsets, S, row0);
+        uniform = s_first == segment_of_row(offsets, S, row1 - 1);
+    }
+};
+
+// sums[s] += sum of x (mean == null) or of (x - mean_s)^2 over the block's rows: one
+// atomic per uniform block, per-thread atomics in the blocks that straddle a boundary.
+template <typename T, int VN>
 __global__ void ln_sum_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets,
                               const float *__restrict__ mean, float *sums, int64_t N, int64_t S, int C) {
     __shared__ float scratch[LN_THREADS / 32];
-    const int64_t row0 = (int64_t)blockIdx.x * LN_ROWS, row1 = min(N, row0 + LN_ROWS);
-    const int64_t s_first = sample_of(offsets, S, row0), s_last = sample_of(offsets, S, row1 - 1);
-    const int64_t e0 = row0 * C, e1 = row1 * C;
-    if (s_first == s_last) {
-        const float mu = mean ? mean[s_first] : 0.f;
-        float v = 0.f;
-        for (int64_t e = e0 + threadIdx.x; e < e1; e += LN_THREADS) {
-            const float d = to_f32<T>(x[e]) - mu;
-            v += mean ? d * d : d;
-        }
-        v = block_sum(v, scratch);
-        if (threadIdx.x == 0) atomicAdd(sums + s_first, v);
-        return;
-    }
-    for (int64_t r = row0 + threadIdx.x / 32; r < row1; r += LN_THREADS / 32) {
-        const int64_t s = sample_of(offsets, S, r);
-        const float mu = mean ? mean[s] : 0.f;
-        float v = 0.f;
-        for (int c = threadIdx.x & 31; c < C; c += 32) {
-            const float d = to_f32<T>(x[r * C + c]) - mu;
-            v += mean ? d * d : d;
-        }
+    const BlockRows B(offsets, N, S);
+    const RowLayout L(C, VN);
+    float acc = 0.f;
+    int64_t cur = B.s_first;
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        if (vcol >= L.vc_total || L.lane >= L.lanes) continue;
+#pragma unroll 4
+        for (int64_t r = B.row0 + L.lane; r < B.row1; r += L.lanes) {
+            const int64_t s = B.uniform ? B.s_first : segment_of_row(offsets, S, r);
+            if (s != cur) {
+                atomicAdd(sums + cur, acc);
+                acc = 0.f;
+                cur = s;
+            }
+            const float mu = mean ? mean[s] : 0.f;
+            float v[VN];
+            load_vec<T, VN>(x + r * C + (int64_t)vcol * VN, v);
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if ((threadIdx.x & 31) == 0) atomicAdd(sums + s, v);
+            for (int i = 0; i < VN; ++i) {
+                const float d = v[i] - mu;
+                acc += mean ? d * d : d;
+            }
+        }
+    }
+    if (B.uniform) {
+        acc = block_sum(acc, scratch);
+        if (threadIdx.x == 0) atomicAdd(sums + B.s_first, acc);
+    } else {
+        atomicAdd(sums + cur, acc);
     }
 }
 
@@ -96,85 +106,121 @@ __global__ void ln_stats_kernel(const float *__restrict__ sums, const int64_t *_
     else rstd[s] = 1.f / sqrtf(sums[s] / n + eps);
 }
 
-template <typename T>
+template <typename T, int VN>
 __global__ void ln_apply_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets,
                                 const float *__restrict__ mean, const float *__restrict__ rstd,
                                 const float *__restrict__ weight, const float *__restrict__ bias,
                                 const T *__restrict__ residual, T *y, int64_t N, int64_t S, int C, int relu) {
-    const int64_t row0 = (int64_t)blockIdx.x * LN_ROWS, row1 = min(N, row0 + LN_ROWS);
-    for (int64_t r = row0 + threadIdx.x / 32; r < row1; r += LN_THREADS / 32) {
-        const int64_t s = sample_of(offsets, S, r);
-        const float mu = mean[s], rs = rstd[s];
-        for (int c = threadIdx.x & 31; c < C; c += 32) {
-            float v = (to_f32<T>(x[r * C + c]) - mu) * rs;
-            if (weight) v = v * weight[c] + bias[c];
-            if (residual) v += to_f32<T>(residual[r * C + c]);
-            if (relu) v = fmaxf(v, 0.f);
-            y[r * C + c] = from_f32<T>(v);
+    const BlockRows B(offsets, N, S);
+    const RowLayout L(C, VN);
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        if (vcol >= L.vc_total || L.lane >= L.lanes) continue;
+        float w[VN], b[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) {
+            w[i] = weight ? weight[vcol * VN + i] : 1.f;
+            b[i] = weight ? bias[vcol * VN + i] : 0.f;
+        }
+#pragma unroll 4
+        for (int64_t r = B.row0 + L.lane; r < B.row1; r += L.lanes) {
+            const int64_t s = B.uniform ? B.s_first : segment_of_row(offsets, S, r);
+            const float mu = mean[s], rs = rstd[s];
+            const int64_t at = r * C + (int64_t)vcol * VN;
+            float v[VN], res[VN];
+            load_vec<T, VN>(x + at, v);
+            if (residual) load_vec<T, VN>(residual + at, res);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                float o = (v[i] - mu) * rs * w[i] + b[i];
+                if (residual) o += res[i];
+                v[i] = relu ? fmaxf(o, 0.f) : o;
+            }
+            store_vec<T, VN>(y + at, v);
         }
     }
 }
 
 // Per-sample sums of gh and gh * xh, per-channel sums of g' * xh and g', and
-// (optionally) the masked gradient for the residual branch.  Partial sums stay in
-// registers while a thread's rows belong to one sample; a block inside one sample
-// reduces in shared memory and issues one atomic per sum, and one per channel.
-template <typename T>
+// (optionally) the masked gradient for the residual branch.  Per-sample partial sums
+// stay in registers while a thread's rows belong to one sample; the per-channel sums of
+// the row lanes are folded in shared memory, one atomic per channel and block.
+template <typename T, int VN>
 __global__ void ln_bwd_sums_kernel(const T *__restrict__ g, const T *__restrict__ x, const T *__restrict__ y,
                                    const int64_t *__restrict__ offsets, const float *__restrict__ mean,
                                    const float *__restrict__ rstd, const float *__restrict__ weight, float *s1,
                                    float *s2, float *dweight, float *dbias, T *dresidual, int64_t N, int64_t S,
                                    int C, int relu) {
     __shared__ float scratch[LN_THREADS / 32];
-    __shared__ float col_w[LN_THREADS / 32][32], col_b[LN_THREADS / 32][32];
-    const int64_t row0 = (int64_t)blockIdx.x * LN_ROWS, row1 = min(N, row0 + LN_ROWS);
-    const int lane = threadIdx.x & 31, rl = threadIdx.x / 32;
-    const int64_t s_first = sample_of(offsets, S, row0), s_last = sample_of(offsets, S, row1 - 1);
-    const bool uniform = s_first == s_last;
+    __shared__ float col_w[LN_THREADS * VN], col_b[LN_THREADS * VN];
+    const BlockRows B(offsets, N, S);
+    const RowLayout L(C, VN);
     float a = 0.f, b = 0.f;     // running sums of gh and gh * xh for sample `cur`
-    int64_t cur = s_first;
-    for (int c0 = 0; c0 < C; c0 += 32) {
-        const int c = c0 + lane;
-        const float w = (weight && c < C) ? weight[c] : 1.f;
-        float dw = 0.f, db = 0.f;
-        for (int64_t r = row0 + rl; r < row1; r += LN_THREADS / 32) {
-            const int64_t s = uniform ? s_first : sample_of(offsets, S, r);
-            if (s != cur) {
-                atomicAdd(s1 + cur, a);
-                atomicAdd(s2 + cur, b);
-                a = b = 0.f;
-                cur = s;
-            }
-            if (c < C) {
-                float gv = to_f32<T>(g[r * C + c]);
-                if (relu && !(to_f32<T>(y[r * C + c]) > 0.f)) gv = 0.f;
-                if (dresidual) dresidual[r * C + c] = from_f32<T>(gv);
-                const float xh = (to_f32<T>(x[r * C + c]) - mean[s]) * rstd[s];
-                a += gv * w;
-                b += gv * w * xh;
-                dw += gv * xh;
-                db += gv;
+    int64_t cur = B.s_first;
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        const bool active = vcol < L.vc_total && L.lane < L.lanes;
+        float w[VN], dw[VN], db[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) {
+            w[i] = (weight && active) ? weight[vcol * VN + i] : 1.f;
+            dw[i] = db[i] = 0.f;
+        }
+        if (active) {
+#pragma unroll 2
+            for (int64_t r = B.row0 + L.lane; r < B.row1; r += L.lanes) {
+                const int64_t s = B.uniform ? B.s_first : segment_of_row(offsets, S, r);
+                if (s != cur) {
+                    atomicAdd(s1 + cur, a);
+                    atomicAdd(s2 + cur, b);
+                    a = b = 0.f;
+                    cur = s;
+                }
+                const float mu = mean[s], rs = rstd[s];
+                const int64_t at = r * C + (int64_t)vcol * VN;
+                float gv[VN], xv[VN], yv[VN];
+                load_vec<T, VN>(g + at, gv);
+                load_vec<T, VN>(x + at, xv);
+                if (relu) load_vec<T, VN>(y + at, yv);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) {
+                    if (relu && !(yv[i] > 0.f)) gv[i] = 0.f;
+                    const float xh = (xv[i] - mu) * rs;
+                    a += gv[i] * w[i];
+                    b += gv[i] * w[i] * xh;
+                    dw[i] += gv[i] * xh;
+                    db[i] += gv[i];
+                }
+                if (dresidual) store_vec<T, VN>(dresidual + at, gv);
             }
         }
         if (dweight) {
-            col_w[rl][lane] = dw;
-            col_b[rl][lane] = db;
+            // col_*[lane][column of the pass]: fold the row lanes, then one atomic per channel
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                col_w[(L.lane * L.vcb + L.vc) * VN + i] = dw[i];
+                col_b[(L.lane * L.vcb + L.vc) * VN + i] = db[i];
+            }
             __syncthreads();
-            if (rl == 0 && c < C) {
-                float tw = 0.f, tb = 0.f;
-                for (int q = 0; q < LN_THREADS / 32; ++q) tw += col_w[q][lane], tb += col_b[q][lane];
-                atomicAdd(dweight + c, tw);
-                atomicAdd(dbias + c, tb);
+            const int cols = L.vcb * VN;
+            for (int t = threadIdx.x; t < cols; t += LN_THREADS) {
+                const int c = cp * cols + t;
+                if (c < C) {
+                    float tw = 0.f, tb = 0.f;
+                    for (int q = 0; q < L.lanes; ++q) tw += col_w[q * cols + t], tb += col_b[q * cols + t];
+                    atomicAdd(dweight + c, tw);
+                    atomicAdd(dbias + c, tb);
+                }
             }
             __syncthreads();
         }
     }
-    if (uniform) {
+    if (B.uniform) {
         a = block_sum(a, scratch);
         b = block_sum(b, scratch);
         if (threadIdx.x == 0) {
-            atomicAdd(s1 + s_first, a);
-            atomicAdd(s2 + s_first, b);
+            atomicAdd(s1 + B.s_first, a);
+            atomicAdd(s2 + B.s_first, b);
         }
     } else {
         atomicAdd(s1 + cur, a);
@@ -182,24 +228,38 @@ __global__ void ln_bwd_sums_kernel(const T *__restrict__ g, const T *__restrict_
     }
 }
 
-template <typename T>
+template <typename T, int VN>
 __global__ void ln_bwd_apply_kernel(const T *__restrict__ g, const T *__restrict__ x, const T *__restrict__ y,
                                     const int64_t *__restrict__ offsets, const float *__restrict__ mean,
                                     const float *__restrict__ rstd, const float *__restrict__ weight,
                                     const float *__restrict__ s1, const float *__restrict__ s2, T *dx, int64_t N,
                                     int64_t S, int C, int relu) {
-    const int64_t row0 = (int64_t)blockIdx.x * LN_ROWS, row1 = min(N, row0 + LN_ROWS);
-    for (int64_t r = row0 + threadIdx.x / 32; r < row1; r += LN_THREADS / 32) {
-        const int64_t s = sample_of(offsets, S, r);
-        const float mu = mean[s], rs = rstd[s];
-        const float inv_n = 1.f / ((float)(offsets[s + 1] - offsets[s]) * (float)C);
-        const float m1 = s1[s] * inv_n, m2 = s2[s] * inv_n;
-        for (int c = threadIdx.x & 31; c < C; c += 32) {
-            float gv = to_f32<T>(g[r * C + c]);
-            if (relu && !(to_f32<T>(y[r * C + c]) > 0.f)) gv = 0.f;
-            const float gh = weight ? gv * weight[c] : gv;
-            const float xh = (to_f32<T>(x[r * C + c]) - mu) * rs;
-            dx[r * C + c] = from_f32<T>(rs * (gh - m1 - xh * m2));
+    const BlockRows B(offsets, N, S);
+    const RowLayout L(C, VN);
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        if (vcol >= L.vc_total || L.lane >= L.lanes) continue;
+        float w[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) w[i] = weight ? weight[vcol * VN + i] : 1.f;
+#pragma unroll 2
+        for (int64_t r = B.row0 + L.lane; r < B.row1; r += L.lanes) {
+            const int64_t s = B.uniform ? B.s_first : segment_of_row(offsets, S, r);
+            const float mu = mean[s], rs = rstd[s];
+            const float inv_n = 1.f / ((float)(offsets[s + 1] - offsets[s]) * (float)C);
+            const float m1 = s1[s] * inv_n, m2 = s2[s] * inv_n;
+            const int64_t at = r * C + (int64_t)vcol * VN;
+            float gv[VN], xv[VN], yv[VN];
+            load_vec<T, VN>(g + at, gv);
+            load_vec<T, VN>(x + at, xv);
+            if (relu) load_vec<T, VN>(y + at, yv);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                if (relu && !(yv[i] > 0.f)) gv[i] = 0.f;
+                const float xh = (xv[i] - mu) * rs;
+                gv[i] = rs * (gv[i] * w[i] - m1 - xh * m2);
+            }
+            store_vec<T, VN>(dx + at, gv);
         }
     }
 }
@@ -236,11 +296,12 @@ bool ln_sizes_ok(int64_t N, int64_t S, int C, int dtype) {
     return N >= 0 && S > 0 && S <= INT32_MAX && C > 0 && (dtype == PCX_F32 || dtype == PCX_F16 || dtype == PCX_BF16);
 }
 
-#define PCX_LN_BY_DTYPE(dtype, CALL)                              \
-    do {                                                          \
-        if ((dtype) == PCX_F32) { using T = float; CALL; }        \
-        else if ((dtype) == PCX_F16) { using T = __half; CALL; }  \
-        else { using T = __nv_bfloat16; CALL; }                   \
+// CALL sees T (element type) and VN (channels per access: 16 bytes' worth when `vec`, else 1)
+#define PCX_LN_DISPATCH(dtype, vec, CALL)                                                        \
+    do {                                                                                         \
+        if ((dtype) == PCX_F32) { using T = float; if (vec) { constexpr int VN = 4; CALL; } else { constexpr int VN = 1; CALL; } }           \
+        else if ((dtype) == PCX_F16) { using T = __half; if (vec) { constexpr int VN = 8; CALL; } else { constexpr int VN = 1; CALL; } }      \
+        else { using T = __nv_bfloat16; if (vec) { constexpr int VN = 8; CALL; } else { constexpr int VN = 1; CALL; } }                       \
     } while (0)
 
 }  // namespace
@@ -266,21 +327,22 @@ int pcx_ragged_layer_norm(const void *d_x, const int64_t *d_lengths, const float
     if (int rc = ln_offsets(d_lengths, S, N, w, stream)) return rc;
     PCX_CUDA(cudaMemsetAsync(w.sums, 0, (size_t)2 * S * sizeof(float), stream));
     const unsigned grid = (unsigned)((N + LN_ROWS - 1) / LN_ROWS), sgrid = (unsigned)((S + 127) / 128);
+    const bool vec = vec_ok(C, dtype, {d_x, d_y, d_residual});
     if (N > 0) {
-        PCX_LN_BY_DTYPE(dtype, (ln_sum_kernel<T><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, nullptr, w.sums, N, S, C)));
+        PCX_LN_DISPATCH(dtype, vec, (ln_sum_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, nullptr, w.sums, N, S, C)));
         PCX_LAUNCH_CHECK();
     }
     ln_stats_kernel<<<sgrid, 128, 0, stream>>>(w.sums, w.offsets, d_mean, d_rstd, S, C, (float)eps, 0);
     PCX_LAUNCH_CHECK();
     if (N > 0) {
-        PCX_LN_BY_DTYPE(dtype, (ln_sum_kernel<T><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, d_mean, w.sums + S, N, S, C)));
+        PCX_LN_DISPATCH(dtype, vec, (ln_sum_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, d_mean, w.sums + S, N, S, C)));
         PCX_LAUNCH_CHECK();
     }
     ln_stats_kernel<<<sgrid, 128, 0, stream>>>(w.sums + S, w.offsets, d_mean, d_rstd, S, C, (float)eps, 1);
     PCX_LAUNCH_CHECK();
     if (N > 0) {
         prof_begin("ln_apply_kernel", stream);
-        PCX_LN_BY_DTYPE(dtype, (ln_apply_kernel<T><<<grid, LN_THREADS, 0, stream>>>(
+        PCX_LN_DISPATCH(dtype, vec, (ln_apply_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>(
                                    (const T *)d_x, w.offsets, d_mean, d_rstd, d_weight, d_bias, (const T *)d_residual,
                                    (T *)d_y, N, S, C, relu)));
         prof_end(stream);
@@ -310,11 +372,12 @@ int pcx_ragged_layer_norm_backward(const void *d_grad_y, const void *d_x, const 
     }
     if (N == 0) return PCX_OK;
     const unsigned grid = (unsigned)((N + LN_ROWS - 1) / LN_ROWS);
-    PCX_LN_BY_DTYPE(dtype, (ln_bwd_sums_kernel<T><<<grid, LN_THREADS, 0, stream>>>(
+    const bool vec = vec_ok(C, dtype, {d_grad_y, d_x, d_y, d_grad_x, d_grad_residual});
+    PCX_LN_DISPATCH(dtype, vec, (ln_bwd_sums_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>(
                                (const T *)d_grad_y, (const T *)d_x, (const T *)d_y, w.offsets, d_mean, d_rstd, d_weight,
                                w.sums, w.sums + S, d_grad_weight, d_grad_bias, (T *)d_grad_residual, N, S, C, relu)));
     PCX_LAUNCH_CHECK();
-    PCX_LN_BY_DTYPE(dtype, (ln_bwd_apply_kernel<T><<<grid, LN_THREADS, 0, stream>>>(
+    PCX_LN_DISPATCH(dtype, vec, (ln_bwd_apply_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>(
                                (const T *)d_grad_y, (const T *)d_x, (const T *)d_y, w.offsets, d_mean, d_rstd, d_weight,
                                w.sums, w.sums + S, (T *)d_grad_x, N, S, C, relu)));
     PCX_LAUNCH_CHECK();

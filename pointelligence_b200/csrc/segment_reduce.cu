@@ -17,13 +17,13 @@
 // reduced value; fp16 results of the contiguous reduction are clamped to +-65504.
 #include <cub/cub.cuh>
 
+#include "rowwise.cuh"
 #include "sparse_kernels.cuh"
 
 namespace pcx {
 namespace {
 
 enum { OP_SUM = 0, OP_MEAN = 1, OP_MAX = 2, OP_MIN = 3 };
-constexpr int ROWS_PER_BLOCK = 128;
 
 __device__ __forceinline__ float neutral_of(int op) {
     return op == OP_MAX ? -INFINITY : op == OP_MIN ? INFINITY : 0.f;
@@ -56,39 +56,64 @@ __global__ void fill_kernel(float *p, int64_t n, float v) {
     if (i < n) p[i] = v;
 }
 
-// first segment s with offsets[s + 1] > row
-__device__ __forceinline__ int64_t segment_of(const int64_t *__restrict__ offsets, int64_t S, int64_t row) {
-    int64_t lo = 0, hi = S;
-    while (lo < hi) {
-        int64_t mid = (lo + hi) >> 1;
-        if (offsets[mid + 1] <= row) lo = mid + 1; else hi = mid;
-    }
-    return lo;
-}
+// A block owns SEG_ROWS consecutive rows; a thread keeps one vector column (VN channels,
+// one 16-byte access when VN > 1) and walks the rows of its row lane.  A block inside one
+// segment folds its row lanes in shared memory and issues one atomic per channel; blocks
+// that straddle a boundary flush per thread whenever the segment changes.
+constexpr int SEG_ROWS = 1024;
+constexpr int SEG_THREADS = 256;
 
-// A block owns ROWS_PER_BLOCK consecutive rows; threads are laid out
-// (channel lane, row lane), walk their rows in order and flush the running
-// value into the fp32 accumulator whenever the segment changes.
-template <typename T>
+template <typename T, int VN>
 __global__ void seg_reduce_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets, float *acc,
-                                  int64_t N, int64_t S, int C, int cw, int op) {
-    const int cx = threadIdx.x % cw, ry = threadIdx.x / cw, rl = blockDim.x / cw;
-    const int64_t row0 = (int64_t)blockIdx.x * ROWS_PER_BLOCK;
-    const int64_t row1 = min(N, row0 + ROWS_PER_BLOCK);
-    if (row0 + ry >= row1) return;
-    const int64_t s0 = segment_of(offsets, S, row0 + ry);
-    for (int c = cx; c < C; c += cw) {
-        int64_t s = s0, end = offsets[s + 1];
-        float v = neutral_of(op);
-        for (int64_t r = row0 + ry; r < row1; r += rl) {
-            if (r >= end) {
-                atomic_combine(acc + s * C + c, v, op);
-                v = neutral_of(op);
-                while (r >= end) end = offsets[++s + 1];
+                                  int64_t N, int64_t S, int C, int op) {
+    __shared__ float fold[SEG_THREADS * VN];
+    const int64_t row0 = (int64_t)blockIdx.x * SEG_ROWS, row1 = min(N, row0 + SEG_ROWS);
+    const int64_t s_first = segment_of_row(offsets, S, row0);
+    const bool uniform = s_first == segment_of_row(offsets, S, row1 - 1);
+    const RowLayout L(C, VN);
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        const bool active = vcol < L.vc_total && L.lane < L.lanes;
+        float v[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) v[i] = neutral_of(op);
+        int64_t cur = s_first;
+        if (active) {
+#pragma unroll 4
+            for (int64_t r = row0 + L.lane; r < row1; r += L.lanes) {
+                const int64_t s = uniform ? s_first : segment_of_row(offsets, S, r);
+                if (s != cur) {
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) {
+                        atomic_combine(acc + cur * C + vcol * VN + i, v[i], op);
+                        v[i] = neutral_of(op);
+                    }
+                    cur = s;
+                }
+                float in[VN];
+                load_vec<T, VN>(x + r * C + (int64_t)vcol * VN, in);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) v[i] = combine(v[i], in[i], op);
             }
-            v = combine(v, to_f32<T>(x[r * C + c]), op);
         }
-        atomic_combine(acc + s * C + c, v, op);
+        if (uniform) {
+#pragma unroll
+            for (int i = 0; i < VN; ++i) fold[(L.lane * L.vcb + L.vc) * VN + i] = v[i];
+            __syncthreads();
+            const int cols = L.vcb * VN;
+            for (int t = threadIdx.x; t < cols; t += SEG_THREADS) {
+                const int c = cp * cols + t;
+                if (c < C) {
+                    float f = neutral_of(op);
+                    for (int q = 0; q < L.lanes; ++q) f = combine(f, fold[q * cols + t], op);
+                    atomic_combine(acc + s_first * C + c, f, op);
+                }
+            }
+            __syncthreads();
+        } else if (active) {
+#pragma unroll
+            for (int i = 0; i < VN; ++i) atomic_combine(acc + cur * C + vcol * VN + i, v[i], op);
+        }
     }
 }
 
@@ -106,61 +131,117 @@ __global__ void seg_finalize_kernel(const float *__restrict__ acc, const int64_t
     out[e] = from_f32<T>(v);
 }
 
-template <typename T>
+template <typename T, int VN>
 __global__ void seg_reduce_bwd_kernel(const T *__restrict__ gout, const T *__restrict__ x, const T *__restrict__ outv,
                                       const int64_t *__restrict__ offsets, T *gin, int64_t N, int64_t S, int C,
-                                      int cw, int op) {
-    const int cx = threadIdx.x % cw, ry = threadIdx.x / cw, rl = blockDim.x / cw;
-    const int64_t row0 = (int64_t)blockIdx.x * ROWS_PER_BLOCK;
-    const int64_t row1 = min(N, row0 + ROWS_PER_BLOCK);
-    if (row0 + ry >= row1) return;
-    int64_t s = segment_of(offsets, S, row0 + ry), end = offsets[s + 1];
-    for (int64_t r = row0 + ry; r < row1; r += rl) {
-        while (r >= end) end = offsets[++s + 1];
-        const float inv = op == OP_MEAN ? 1.f / (float)max((int64_t)1, end - offsets[s]) : 1.f;
-        for (int c = cx; c < C; c += cw) {
-            float g = to_f32<T>(gout[s * C + c]);
-            if (op == OP_MEAN) g *= inv;
-            if (op >= OP_MAX && !(to_f32<T>(x[r * C + c]) == to_f32<T>(outv[s * C + c]))) g = 0.f;
-            gin[r * C + c] = from_f32<T>(g);
+                                      int op) {
+    const int64_t row0 = (int64_t)blockIdx.x * SEG_ROWS, row1 = min(N, row0 + SEG_ROWS);
+    const int64_t s_first = segment_of_row(offsets, S, row0);
+    const bool uniform = s_first == segment_of_row(offsets, S, row1 - 1);
+    const RowLayout L(C, VN);
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        if (vcol >= L.vc_total || L.lane >= L.lanes) continue;
+#pragma unroll 2
+        for (int64_t r = row0 + L.lane; r < row1; r += L.lanes) {
+            const int64_t s = uniform ? s_first : segment_of_row(offsets, S, r);
+            const float inv = op == OP_MEAN ? 1.f / (float)max((int64_t)1, offsets[s + 1] - offsets[s]) : 1.f;
+            float gv[VN], xv[VN], ov[VN];
+            load_vec<T, VN>(gout + s * C + (int64_t)vcol * VN, gv);
+            if (op >= OP_MAX) {
+                load_vec<T, VN>(x + r * C + (int64_t)vcol * VN, xv);
+                load_vec<T, VN>(outv + s * C + (int64_t)vcol * VN, ov);
+            }
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                gv[i] *= inv;
+                if (op >= OP_MAX && !(xv[i] == ov[i])) gv[i] = 0.f;
+            }
+            store_vec<T, VN>(gin + r * C + (int64_t)vcol * VN, gv);
         }
     }
 }
 
-// One warp per output row; lanes stride the channels.
-template <typename T>
+// Output rows side by side in a block: a thread keeps one vector column of one output row
+// and walks that row's list (C = 64 bf16: 8 threads per output row, 32 rows per block).
+constexpr int IDX_THREADS = 256;
+
+template <typename T, int VN>
 __global__ void idx_reduce_kernel(const T *__restrict__ x, const int32_t *__restrict__ indices,
                                   const int64_t *__restrict__ offsets, T *y, int64_t K, int C, int op) {
-    const int64_t k = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (k >= K) return;
+    const RowLayout L(C, VN);
+    const int64_t k = (int64_t)blockIdx.x * L.lanes + L.lane;
+    if (L.lane >= L.lanes || k >= K) return;
     const int64_t lo = offsets[k], hi = offsets[k + 1];
-    for (int c = lane; c < C; c += 32) {
-        float v = neutral_of(op);
-        for (int64_t e = lo; e < hi; ++e) v = combine(v, to_f32<T>(x[(int64_t)indices[e] * C + c]), op);
-        if (op == OP_MEAN) v = v / (float)(hi - lo);
-        y[k * C + c] = from_f32<T>(v);
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        if (vcol >= L.vc_total) continue;
+        float v[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) v[i] = neutral_of(op);
+#pragma unroll 4
+        for (int64_t e = lo; e < hi; ++e) {
+            float in[VN];
+            load_vec<T, VN>(x + (int64_t)indices[e] * C + (int64_t)vcol * VN, in);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) v[i] = combine(v[i], in[i], op);
+        }
+        if (op == OP_MEAN) {
+#pragma unroll
+            for (int i = 0; i < VN; ++i) v[i] = v[i] / (float)(hi - lo);
+        }
+        store_vec<T, VN>(y + k * C + (int64_t)vcol * VN, v);
     }
 }
 
-template <typename T>
+template <typename T, int VN>
 __global__ void idx_reduce_bwd_kernel(const T *__restrict__ gy, const T *__restrict__ x, const T *__restrict__ y,
                                       const int32_t *__restrict__ indices, const int64_t *__restrict__ offsets,
                                       float *acc, int64_t K, int C, int op) {
-    const int64_t k = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (k >= K) return;
+    const RowLayout L(C, VN);
+    const int64_t k = (int64_t)blockIdx.x * L.lanes + L.lane;
+    if (L.lane >= L.lanes || k >= K) return;
     const int64_t lo = offsets[k], hi = offsets[k + 1];
-    for (int c = lane; c < C; c += 32) {
-        float g = to_f32<T>(gy[k * C + c]);
-        if (op == OP_MEAN) g = g / (float)(hi - lo);
-        const float target = op >= OP_MAX ? to_f32<T>(y[k * C + c]) : 0.f;
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        if (vcol >= L.vc_total) continue;
+        float g[VN], target[VN];
+        load_vec<T, VN>(gy + k * C + (int64_t)vcol * VN, g);
+        if (op >= OP_MAX) load_vec<T, VN>(y + k * C + (int64_t)vcol * VN, target);
+        if (op == OP_MEAN) {
+#pragma unroll
+            for (int i = 0; i < VN; ++i) g[i] = g[i] / (float)(hi - lo);
+        }
         for (int64_t e = lo; e < hi; ++e) {
-            const int64_t row = indices[e];
-            if (op >= OP_MAX && !(to_f32<T>(x[row * C + c]) == target)) continue;
-            atomicAdd(acc + row * C + c, g);
+            const int64_t at = (int64_t)indices[e] * C + (int64_t)vcol * VN;
+            float add[VN];
+#pragma unroll
+            for (int i = 0; i < VN; ++i) add[i] = g[i];
+            if (op >= OP_MAX) {
+                float in[VN];
+                load_vec<T, VN>(x + at, in);
+#pragma unroll
+                for (int i = 0; i < VN; ++i)
+                    if (!(in[i] == target[i])) add[i] = 0.f;
+            }
+            if constexpr (VN % 4 == 0) {
+#pragma unroll
+                for (int i = 0; i < VN; i += 4)
+                    atomicAdd(reinterpret_cast<float4 *>(acc + at + i), make_float4(add[i], add[i + 1], add[i + 2], add[i + 3]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < VN; ++i)
+                    if (add[i] != 0.f || op < OP_MAX) atomicAdd(acc + at + i, add[i]);
+            }
         }
     }
+}
+
+static inline unsigned idx_grid(int64_t K, int C, int vn) {
+    const int vc_total = C / vn;
+    const int vcb = vc_total < IDX_THREADS ? vc_total : IDX_THREADS;
+    const int lanes = IDX_THREADS / vcb;
+    return (unsigned)((K + lanes - 1) / lanes);
 }
 
 struct OffsWs {
@@ -193,12 +274,18 @@ int scan_lengths(const int64_t *d_lengths, int64_t S, int64_t total, const OffsW
     return PCX_OK;
 }
 
-int channel_lanes(int C) { return C <= 32 ? 32 : C <= 64 ? 64 : 128; }
-
 bool sizes_ok(int64_t rows, int64_t S, int C, int op, int dtype) {
     return rows >= 0 && S >= 0 && S <= INT32_MAX && C > 0 && op >= 0 && op <= 3 &&
            (dtype == PCX_F32 || dtype == PCX_F16 || dtype == PCX_BF16);
 }
+
+// CALL sees T and VN (channels per access: 16 bytes' worth when `vec`, else 1)
+#define PCX_BY_DTYPE_VEC(dtype, vec, CALL)                                                                       \
+    do {                                                                                                         \
+        if ((dtype) == PCX_F32) { using T = float; if (vec) { constexpr int VN = 4; CALL; } else { constexpr int VN = 1; CALL; } }       \
+        else if ((dtype) == PCX_F16) { using T = __half; if (vec) { constexpr int VN = 8; CALL; } else { constexpr int VN = 1; CALL; } }  \
+        else { using T = __nv_bfloat16; if (vec) { constexpr int VN = 8; CALL; } else { constexpr int VN = 1; CALL; } }                   \
+    } while (0)
 
 #define PCX_BY_DTYPE(dtype, CALL)                    \
     do {                                             \
@@ -235,10 +322,10 @@ int pcx_segment_reduce(const void *d_x, const int64_t *d_lengths, void *d_out, i
     fill_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, stream>>>(w.acc, elems, init);
     PCX_LAUNCH_CHECK();
     if (N > 0) {
-        const int cw = channel_lanes(C);
-        const unsigned grid = (unsigned)((N + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
+        const unsigned grid = (unsigned)((N + SEG_ROWS - 1) / SEG_ROWS);
+        const bool vec = vec_ok(C, dtype, {d_x});
         prof_begin("seg_reduce_kernel", stream);
-        PCX_BY_DTYPE(dtype, (seg_reduce_kernel<T><<<grid, 128, 0, stream>>>((const T *)d_x, w.offsets, w.acc, N, S, C, cw, op)));
+        PCX_BY_DTYPE_VEC(dtype, vec, (seg_reduce_kernel<T, VN><<<grid, SEG_THREADS, 0, stream>>>((const T *)d_x, w.offsets, w.acc, N, S, C, op)));
         prof_end(stream);
         PCX_LAUNCH_CHECK();
     }
@@ -261,11 +348,11 @@ int pcx_segment_reduce_backward(const void *d_grad_out, const void *d_x, const v
     size_t need = carve_offsets(d_ws, S, 0, &w);
     if (ws_bytes < need) PCX_FAIL(PCX_E_CAPACITY, "pcx_segment_reduce_backward: workspace %zu < %zu bytes", ws_bytes, need);
     if (int rc = scan_lengths(d_lengths, S, N, w, stream)) return rc;
-    const int cw = channel_lanes(C);
-    const unsigned grid = (unsigned)((N + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
-    PCX_BY_DTYPE(dtype, (seg_reduce_bwd_kernel<T><<<grid, 128, 0, stream>>>((const T *)d_grad_out, (const T *)d_x,
-                                                                            (const T *)d_out, w.offsets, (T *)d_grad_x,
-                                                                            N, S, C, cw, op)));
+    const unsigned grid = (unsigned)((N + SEG_ROWS - 1) / SEG_ROWS);
+    const bool vec = vec_ok(C, dtype, {d_grad_out, op >= OP_MAX ? d_x : nullptr, op >= OP_MAX ? d_out : nullptr, d_grad_x});
+    PCX_BY_DTYPE_VEC(dtype, vec, (seg_reduce_bwd_kernel<T, VN><<<grid, SEG_THREADS, 0, stream>>>(
+                                     (const T *)d_grad_out, (const T *)d_x, (const T *)d_out, w.offsets, (T *)d_grad_x,
+                                     N, S, C, op)));
     PCX_LAUNCH_CHECK();
     return PCX_OK;
 }
@@ -288,10 +375,10 @@ int pcx_indexed_segment_reduce(const void *d_x, const int32_t *d_indices, const 
     size_t need = carve_offsets(d_ws, K, 0, &w);
     if (ws_bytes < need) PCX_FAIL(PCX_E_CAPACITY, "pcx_indexed_segment_reduce: workspace %zu < %zu bytes", ws_bytes, need);
     if (int rc = scan_lengths(d_lengths, K, E, w, stream)) return rc;
-    const unsigned grid = (unsigned)((K * 32 + 255) / 256);
+    const bool vec = vec_ok(C, dtype, {d_x, d_y});
     prof_begin("idx_reduce_kernel", stream);
-    PCX_BY_DTYPE(dtype, (idx_reduce_kernel<T><<<grid, 256, 0, stream>>>((const T *)d_x, d_indices, w.offsets, (T *)d_y, K,
-                                                                        C, op)));
+    PCX_BY_DTYPE_VEC(dtype, vec, (idx_reduce_kernel<T, VN><<<idx_grid(K, C, VN), IDX_THREADS, 0, stream>>>(
+                                     (const T *)d_x, d_indices, w.offsets, (T *)d_y, K, C, op)));
     prof_end(stream);
     PCX_LAUNCH_CHECK();
     return PCX_OK;
@@ -318,10 +405,10 @@ int pcx_indexed_segment_reduce_backward(const void *d_grad_y, const void *d_x, c
     float *acc = dtype == PCX_F32 ? (float *)d_grad_x : w.acc;
     PCX_CUDA(cudaMemsetAsync(acc, 0, (size_t)n_x * C * sizeof(float), stream));
     if (K > 0 && E > 0) {
-        const unsigned grid = (unsigned)((K * 32 + 255) / 256);
-        PCX_BY_DTYPE(dtype, (idx_reduce_bwd_kernel<T><<<grid, 256, 0, stream>>>((const T *)d_grad_y, (const T *)d_x,
-                                                                                (const T *)d_y, d_indices, w.offsets,
-                                                                                acc, K, C, op)));
+        const bool vec = vec_ok(C, dtype, {d_grad_y, op >= OP_MAX ? d_x : nullptr, op >= OP_MAX ? d_y : nullptr, acc});
+        PCX_BY_DTYPE_VEC(dtype, vec, (idx_reduce_bwd_kernel<T, VN><<<idx_grid(K, C, VN), IDX_THREADS, 0, stream>>>(
+                                         (const T *)d_grad_y, (const T *)d_x, (const T *)d_y, d_indices, w.offsets, acc,
+                                         K, C, op)));
         PCX_LAUNCH_CHECK();
     }
     if (dtype != PCX_F32) return round_accumulator(acc, d_grad_x, n_x * C, dtype, stream);
