@@ -402,8 +402,13 @@ def run_ours(args, rank, local_rank, world):
         dominant = max(avg, key=avg.get)
         dom_pass = label_to_pass[dominant]
         achieved = balg[dom_pass] / (avg[dominant] * 1e-3) / 1e9
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised
+        # in profiles/mvmr_tc_kernel_indoor150k_c64.md (headline workload only)
+        traffic = None
+        if dominant.startswith("mvmr_tc_kernel") and (args.points, C) == (N_POINTS, CHANNELS):
+            traffic = 65.4e6
         roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm, "unit": "GB/s",
-                    "frac": achieved / hbm, "peak_source": peak_kind, "traffic": None,
+                    "frac": achieved / hbm, "peak_source": peak_kind, "traffic": traffic,
                     "algorithmic_bytes": balg[dom_pass], "kernel_ms": avg[dominant],
                     "all_kernels_ms": avg,
                     "all_passes_frac": {label_to_pass[kname]: balg[label_to_pass[kname]] / (ms * 1e-3) / 1e9 / hbm
@@ -512,6 +517,91 @@ def run_block_ops(args, local_rank):
                       "peak": hbm, "peak_source": peak_kind, "passes": out}), flush=True)
 
 
+def run_backbone(args, rank, local_rank, world):
+    """Secondary workload (configs 4 / 5 of the survey): one training step of the residual U-Net
+    backbone -- geometry, forward, cross-entropy, backward, all-reduce of the parameter gradients
+    (optimizer excluded) -- on 8 synthetic indoor scenes per rank (weak scaling).  One JSON line."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from pointelligence_b200 import _cabi
+    from pointelligence_b200.backbone import ResUNet
+    from pointelligence_b200.dist import allreduce_gradients
+    from pointelligence_b200.synthetic import indoor_scene, ragged_batch
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sizes = np.random.default_rng(1000 + rank).integers(args.scene_min, args.scene_max + 1, args.scenes)
+    clouds = [indoor_scene(int(n), rank * args.scenes + s) for s, n in enumerate(sizes)]
+    pts_np, inds_np, sizes_np = ragged_batch(clouds)
+    pts, inds, lens = (torch.from_numpy(a).to(dev) for a in (pts_np, inds_np, sizes_np))
+    n = pts.shape[0]
+    g = torch.Generator(device=dev).manual_seed(rank + 1)
+    feat = torch.randn(n, 3, device=dev, generator=g)
+    labels = torch.randint(0, 20, (n,), device=dev, generator=g)
+    torch.manual_seed(0)                     # identical initial weights on every rank
+    model = ResUNet(in_channels=3, num_classes=20).to(dev)
+    params = [p for p in model.parameters()]
+
+    def step():
+        for p in params:
+            p.grad = None
+        logits = model(feat, pts, inds, lens, 0.02)
+        loss = F.cross_entropy(logits.float(), labels)
+        loss.backward()
+        if world > 1:
+            allreduce_gradients(params)
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        loss = step()
+    barrier()
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    _cabi.launch_count(reset=True)
+    a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    a.record()
+    for _ in range(args.steps):
+        loss = step()
+    z.record()
+    barrier()
+    clock_info = clocks.stop()
+    launches = _cabi.launch_count()
+    stats = torch.tensor([a.elapsed_time(z), float(n)], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx, sm = stats.clone(), stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, n_all = float(mx[0]), float(sm[1])
+    else:
+        total_ms, n_all = float(stats[0]), float(n)
+    if rank == 0:
+        ms = total_ms / args.steps
+        print(json.dumps({
+            "metric": "resunet_train_step_throughput", "value": n_all / (ms * 1e-3) / 1e6, "unit": "Mpoints/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"ResUNet 32/64/128/256, BasicBlock x2 per stage, {args.scenes} indoor scenes of "
+                                   f"{args.scene_min}-{args.scene_max} points per rank, 2 cm grid, "
+                                   "fwd + CE + bwd + gradient all-reduce, geometry rebuilt every step",
+                       "points_rank0": n, "parameters": int(sum(p.numel() for p in params)),
+                       "l2": "working set of a step (GBs of activations) exceeds the L2",
+                       "collective": "bucketed all-reduce of parameter gradients" if world > 1 else "none"},
+            "loss": float(loss.detach()), "gpu_launches": int(launches), "clocks": clock_info}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -523,8 +613,12 @@ def main():
     ap.add_argument("--overlap-grads", action="store_true",
                     help="run the weight gradient on a second stream beside the input gradient "
                          "(kernel timings then include the contention)")
-    ap.add_argument("--workload", default="conv", choices=["conv", "block_ops"],
-                    help="conv: the headline convolution step; block_ops: norm / pooling passes of a residual block")
+    ap.add_argument("--workload", default="conv", choices=["conv", "block_ops", "backbone"],
+                    help="conv: the headline convolution step; block_ops: norm / pooling passes of a residual "
+                         "block; backbone: one training step of the residual U-Net (weak scaling over ranks)")
+    ap.add_argument("--scenes", type=int, default=8, help="backbone workload: scenes per rank")
+    ap.add_argument("--scene-min", type=int, default=80000, help="backbone workload: smallest scene")
+    ap.add_argument("--scene-max", type=int, default=200000, help="backbone workload: largest scene")
     ap.add_argument("--resident-only", action="store_true",
                     help="skip the host-buffer and CPU legs (for profiler captures of the kernels)")
     args = ap.parse_args()
@@ -533,6 +627,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "backbone":
+        run_backbone(args, rank, local_rank, world)
         return
     if args.workload == "block_ops":
         if rank == 0:

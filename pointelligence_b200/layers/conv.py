@@ -103,11 +103,22 @@ class GeneralConv(Module):
                                uniform_seg_len=contract.uniform_seg_len,
                                exact_cover_out=contract.exact_cover_out,
                                exact_cover_in=contract.exact_cover_in)
-            output = tig_mvmr(weight, x3.view(n_in, -1), idx,
-                              input_precision=resolve_input_precision(x3.dtype))
+            cin = weight.shape[2]
+            if self.groups == 1 and cin > 256 and cin % 32 == 0 and x3.dtype in (torch.float16, torch.bfloat16):
+                # wider than the tensor-core engine's 256-channel contraction: split the input
+                # channels into two halves (two tensor-core passes, partial outputs added in fp32)
+                half = cin // 2
+                flat = x3.view(n_in, -1)
+                parts = [tig_mvmr(weight[:, :, lo:lo + half].contiguous(), flat[:, lo:lo + half].contiguous(), idx,
+                                  input_precision=resolve_input_precision(x3.dtype)).float()
+                         for lo in (0, half)]
+                output = (parts[0] + parts[1]).to(x3.dtype)
+            else:
+                output = tig_mvmr(weight, x3.view(n_in, -1), idx,
+                                  input_precision=resolve_input_precision(x3.dtype))
         else:
             output = sparse_matrix_vector_multiplication_reduction(weight, k, x3, j, i, n)
-        output = output.reshape(-1, self.out_channels)
+        output = output.reshape(-1, weight.shape[1] * weight.shape[3])
         if bias is not None:
             output = output + bias
         return output
