@@ -252,10 +252,14 @@ def run_ours(args, rank, local_rank, world):
         ev_fwd.record(main)
         if not args.overlap_grads:
             gw = _cabi.vvor(x.view(n, 1, C), j, go.view(n, 1, M), i, seg, None, K)
-            work = dist.all_reduce(gw, async_op=True) if world > 1 else None   # overlaps the input gradient
+            work = None
+            if world > 1 and args.allreduce == "overlap":
+                work = dist.all_reduce(gw, async_op=True)   # runs beside the input gradient
             gx = _cabi.mvmr(w, go, i, j, seg, None, n, True)
             if work is not None:
                 work.wait()
+            elif world > 1:
+                dist.all_reduce(gw)                         # after the input gradient, on the same stream
             return out, gx, gw
         with torch.cuda.stream(side):
             side.wait_event(ev_fwd)
@@ -619,6 +623,8 @@ def main():
     ap.add_argument("--scenes", type=int, default=8, help="backbone workload: scenes per rank")
     ap.add_argument("--scene-min", type=int, default=80000, help="backbone workload: smallest scene")
     ap.add_argument("--scene-max", type=int, default=200000, help="backbone workload: largest scene")
+    ap.add_argument("--allreduce", default="overlap", choices=["serial", "overlap"],
+                    help="N > 1: all-reduce of dW after the input gradient (serial) or beside it (overlap)")
     ap.add_argument("--resident-only", action="store_true",
                     help="skip the host-buffer and CPU legs (for profiler captures of the kernels)")
     args = ap.parse_args()
