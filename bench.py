@@ -81,12 +81,16 @@ class ClockSampler:
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index):
+    def __init__(self, gpu_index, enabled=True):
+        # one sampler per job (rank 0's GPU): several concurrent nvidia-smi loops contend in the driver
         self.gpu = gpu_index
+        self.enabled = enabled
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.proc = None
 
     def start(self):
+        if not self.enabled:
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -282,7 +286,7 @@ def run_ours(args, rank, local_rank, world):
     barrier()
 
     # ---- timed region: K steps, one event pair per step, L2 flushed between steps
-    clocks = ClockSampler(local_rank)
+    clocks = ClockSampler(local_rank, enabled=(rank == 0))
     clocks.start()
     _cabi.launch_count(reset=True)
     _cabi.profile_enable(True)
@@ -568,7 +572,7 @@ def run_backbone(args, rank, local_rank, world):
     for _ in range(max(args.warmup, 3)):
         loss = step()
     barrier()
-    clocks = ClockSampler(local_rank)
+    clocks = ClockSampler(local_rank, enabled=(rank == 0))
     clocks.start()
     _cabi.launch_count(reset=True)
     a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
