@@ -41,6 +41,10 @@ struct RadiusWs {
     int64_t *offsets;    // Q+1 exclusive scan, offsets[Q] = total
     uint32_t *tap_hist;  // K^3
     int64_t *seg;        // K^3+1 tap segment offsets (copy kept for the fill call)
+    unsigned long long *max_key;  // largest cell key (bounds the radix sort's bit range)
+    int64_t *cell_keys;  // open-addressing table: cell key -> (start,end) in the sorted order
+    int2 *cell_ranges;
+    int64_t cell_cap;    // table slots (power of two, at least 2 P)
     void *cub_tmp;
     size_t cub_bytes;
 };
@@ -69,6 +73,11 @@ size_t carve_radius(void *ws, int64_t P, int64_t Q, int kernel_size, RadiusWs *o
     w.offsets = c.take<int64_t>(Q + 1);
     w.tap_hist = c.take<uint32_t>(k3 > 0 ? k3 : 1);
     w.seg = c.take<int64_t>(k3 + 1);
+    w.max_key = c.take<unsigned long long>(1);
+    w.cell_cap = 1024;
+    while (w.cell_cap < 2 * P) w.cell_cap <<= 1;
+    w.cell_keys = c.take<int64_t>(w.cell_cap);
+    w.cell_ranges = c.take<int2>(w.cell_cap);
     w.cub_bytes = radius_cub_bytes(P, Q);
     w.cub_tmp = c.take<char>(w.cub_bytes);
     if (out) *out = w;
@@ -127,13 +136,64 @@ __device__ __forceinline__ int64_t cell_key(int b, int cx, int cy, int cz, const
 
 __global__ void radius_key_kernel(const float *__restrict__ pts, const int32_t *__restrict__ sample,
                                   int64_t P, float inv, const int32_t *__restrict__ ext,
-                                  int64_t *keys, int32_t *vals) {
+                                  int64_t *keys, int32_t *vals, unsigned long long *max_key) {
+    int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    unsigned long long key = 0;
+    if (p < P) {
+        int b = sample ? sample[p] : 0;
+        key = (unsigned long long)cell_key(b, cell_of(pts[3 * p], inv), cell_of(pts[3 * p + 1], inv),
+                                           cell_of(pts[3 * p + 2], inv), ext);
+        keys[p] = (int64_t)key;
+        vals[p] = (int32_t)p;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) key = max(key, __shfl_xor_sync(0xffffffffu, key, o));
+    if ((threadIdx.x & 31) == 0 && key) atomicMax(max_key, key);
+}
+
+// Cell table: key -> [start, end) of the cell's points in the sorted order.  Heads of
+// runs insert (key, start); tails look their slot up and add the end.  Keys are >= 0.
+constexpr int64_t CELL_EMPTY = -1;
+__device__ __forceinline__ uint64_t mix64(uint64_t x) {
+    x ^= x >> 33;
+    x *= 0xff51afd7ed558ccdULL;
+    x ^= x >> 33;
+    x *= 0xc4ceb9fe1a85ec53ULL;
+    x ^= x >> 33;
+    return x;
+}
+__global__ void cell_table_heads_kernel(const int64_t *__restrict__ keys, int64_t P, int64_t *tkeys, int2 *tranges,
+                                        uint64_t mask) {
     int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (p >= P) return;
-    int b = sample ? sample[p] : 0;
-    keys[p] = cell_key(b, cell_of(pts[3 * p], inv), cell_of(pts[3 * p + 1], inv),
-                       cell_of(pts[3 * p + 2], inv), ext);
-    vals[p] = (int32_t)p;
+    const int64_t key = keys[p];
+    if (p > 0 && keys[p - 1] == key) return;
+    uint64_t slot = mix64((uint64_t)key) & mask;
+    for (;;) {   // the table is at most half full: an empty slot always turns up
+        const long long prev = (long long)atomicCAS((unsigned long long *)&tkeys[slot], (unsigned long long)CELL_EMPTY,
+                                                    (unsigned long long)key);
+        if (prev == CELL_EMPTY) break;
+        slot = (slot + 1) & mask;
+    }
+    tranges[slot].x = (int)p;
+}
+__device__ __forceinline__ int64_t cell_slot(const int64_t *__restrict__ tkeys, uint64_t mask, int64_t key) {
+    uint64_t slot = mix64((uint64_t)key) & mask;
+    for (;;) {
+        const int64_t k = tkeys[slot];
+        if (k == key) return (int64_t)slot;
+        if (k == CELL_EMPTY) return -1;
+        slot = (slot + 1) & mask;
+    }
+}
+__global__ void cell_table_tails_kernel(const int64_t *__restrict__ keys, int64_t P, const int64_t *__restrict__ tkeys,
+                                        int2 *tranges, uint64_t mask) {
+    int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (p >= P) return;
+    const int64_t key = keys[p];
+    if (p + 1 < P && keys[p + 1] == key) return;
+    const int64_t slot = cell_slot(tkeys, mask, key);
+    if (slot >= 0) tranges[slot].y = (int)(p + 1);
 }
 
 __global__ void radius_gather_kernel(const float *__restrict__ pts, const int32_t *__restrict__ perm,
@@ -143,15 +203,6 @@ __global__ void radius_gather_kernel(const float *__restrict__ pts, const int32_
     int32_t p = perm[s];
     sorted_pts[s] = make_float4(pts[3 * (int64_t)p], pts[3 * (int64_t)p + 1], pts[3 * (int64_t)p + 2],
                                 __int_as_float(p));
-}
-
-__device__ __forceinline__ int64_t lower_bound_i64(const int64_t *__restrict__ a, int64_t n, int64_t key) {
-    int64_t lo = 0, hi = n;
-    while (lo < hi) {
-        int64_t mid = (lo + hi) >> 1;
-        if (a[mid] < key) lo = mid + 1; else hi = mid;
-    }
-    return lo;
 }
 
 // Radius predicate  sqrt(dx*dx + dy*dy + dz*dz) <= R  in fp32.
@@ -199,7 +250,9 @@ struct ScanArgs {
     const float *queries;
     const int32_t *query_sample;
     const float4 *sorted_pts;
-    const int64_t *sorted_keys;
+    const int64_t *cell_keys;   // cell table (see cell_table_heads_kernel)
+    const int2 *cell_ranges;
+    uint64_t cell_mask;
     const int32_t *ext;
     int2 *ranges;
     int64_t P, Q;
@@ -238,9 +291,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) radius_scan_kernel(ScanAr
                 int cx = corner_of(qx, a.r32, a.inv) + ((lane >> 2) & 1);
                 int cy = corner_of(qy, a.r32, a.inv) + ((lane >> 1) & 1);
                 int cz = corner_of(qz, a.r32, a.inv) + (lane & 1);
-                int64_t key = cell_key(b, cx, cy, cz, a.ext);
-                start = (int)lower_bound_i64(a.sorted_keys, a.P, key);
-                end = (int)lower_bound_i64(a.sorted_keys, a.P, key + 1);
+                const int64_t slot = cell_slot(a.cell_keys, a.cell_mask, cell_key(b, cx, cy, cz, a.ext));
+                if (slot >= 0) {
+                    const int2 r = a.cell_ranges[slot];
+                    start = r.x, end = r.y;
+                }
                 a.ranges[q * 8 + lane] = make_int2(start, end);
             }
         } else if (lane < 8) {
@@ -556,17 +611,32 @@ int pcx_radius_count(const float *d_points, const float *d_queries, const int32_
     int blocks = (int)std::min<int64_t>((P + Q + 255) / 256, 8 * num_sms());
     radius_extent_kernel<<<blocks, 256, 0, stream>>>(d_points, d_queries, P, Q, inv, r32, w.ext);
     PCX_LAUNCH_CHECK();
-    radius_key_kernel<<<(unsigned)((P + 255) / 256), 256, 0, stream>>>(d_points, d_point_sample, P, inv, w.ext, w.keys_a, w.vals_a);
+    PCX_CUDA(cudaMemsetAsync(w.max_key, 0, sizeof(unsigned long long), stream));
+    PCX_CUDA(cudaMemsetAsync(w.cell_keys, 0xff, (size_t)w.cell_cap * sizeof(int64_t), stream));
+    radius_key_kernel<<<(unsigned)((P + 255) / 256), 256, 0, stream>>>(d_points, d_point_sample, P, inv, w.ext, w.keys_a, w.vals_a, w.max_key);
     PCX_LAUNCH_CHECK();
+    // the sort only has to look at the bits the largest key uses (a hand-over of 8 bytes;
+    // the call ends with one for the total anyway)
+    unsigned long long h_max_key = 0;
+    PCX_CUDA(cudaMemcpyAsync(&h_max_key, w.max_key, sizeof(h_max_key), cudaMemcpyDeviceToHost, stream));
+    PCX_CUDA(cudaStreamSynchronize(stream));
+    int key_bits = 1;
+    while (key_bits < 64 && (h_max_key >> key_bits)) ++key_bits;
     size_t tmp = w.cub_bytes;
-    PCX_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, tmp, w.keys_a, w.keys_b, w.vals_a, w.vals_b, P, 0, 64, stream));
+    PCX_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, tmp, w.keys_a, w.keys_b, w.vals_a, w.vals_b, P, 0, key_bits, stream));
     radius_gather_kernel<<<(unsigned)((P + 255) / 256), 256, 0, stream>>>(d_points, w.vals_b, P, w.sorted_pts);
+    PCX_LAUNCH_CHECK();
+    const uint64_t cell_mask = (uint64_t)w.cell_cap - 1;
+    cell_table_heads_kernel<<<(unsigned)((P + 255) / 256), 256, 0, stream>>>(w.keys_b, P, w.cell_keys, w.cell_ranges, cell_mask);
+    PCX_LAUNCH_CHECK();
+    cell_table_tails_kernel<<<(unsigned)((P + 255) / 256), 256, 0, stream>>>(w.keys_b, P, w.cell_keys, w.cell_ranges, cell_mask);
     PCX_LAUNCH_CHECK();
     if (k3 > 0) PCX_CUDA(cudaMemsetAsync(w.tap_hist, 0, (size_t)k3 * sizeof(uint32_t), stream));
 
     ScanArgs a = {};
     a.queries = d_queries, a.query_sample = d_query_sample, a.sorted_pts = w.sorted_pts;
-    a.sorted_keys = w.keys_b, a.ext = w.ext, a.ranges = w.ranges, a.P = P, a.Q = Q;
+    a.cell_keys = w.cell_keys, a.cell_ranges = w.cell_ranges, a.cell_mask = cell_mask;
+    a.ext = w.ext, a.ranges = w.ranges, a.P = P, a.Q = Q;
     a.r32 = r32, a.inv = inv, a.g32 = (float)kernel_grid_size;
     a.distance_type = distance_type, a.variant = radius_variant(), a.K = kernel_size;
     a.counts = w.counts, a.num_neighbors = d_num_neighbors, a.tap_hist = w.tap_hist;
@@ -607,7 +677,7 @@ int pcx_radius_fill(const float *d_points, const float *d_queries, int64_t P, in
     const int k3 = kernel_size * kernel_size * kernel_size;
 
     ScanArgs a = {};
-    a.queries = d_queries, a.sorted_pts = w.sorted_pts, a.sorted_keys = w.keys_b, a.ext = w.ext;
+    a.queries = d_queries, a.sorted_pts = w.sorted_pts, a.ext = w.ext;
     a.ranges = w.ranges, a.P = P, a.Q = Q;
     a.r32 = (float)radius, a.inv = (float)(1.0 / (2.0 * radius)), a.g32 = (float)kernel_grid_size;
     a.distance_type = distance_type, a.variant = radius_variant(), a.K = kernel_size;

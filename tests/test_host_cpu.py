@@ -202,3 +202,36 @@ def test_bench_reference_arm_prints_the_contract_line():
     assert line["cpu_baseline"]["cores"] == 1 and line["cpu_baseline"]["kind"] in ("reference", "port")
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["value"] == line["value"]
     assert line["config"]["workload"].startswith("indoor150k_c64_bf16") and line["vs_baseline"] is None
+
+
+def test_block_layers_construct_on_cpu_and_fail_loudly_without_cuda():
+    """The norm / pooling layers and the benchmark backbone are host code over the CUDA
+    library: they construct anywhere, keep the reference's parameter layout, and raise
+    instead of computing on the CPU."""
+    import torch
+
+    from pointelligence_b200.backbone import ResUNet
+    from pointelligence_b200.layers import (GlobalPool, RaggedBatchNorm, RaggedGroupNorm, RaggedInstanceNorm,
+                                            RaggedLayerNorm)
+    from pointelligence_b200.sparse_engines.ops import indexed_segment_reduce, large_segment_reduce
+
+    ln = RaggedLayerNorm(24)
+    assert ln.weight.shape == (24,) and ln.bias.shape == (24,) and ln.eps == 1e-5
+    assert RaggedInstanceNorm(8).weight is None              # affine=False by default, as in the reference
+    assert RaggedGroupNorm(4, 24).num_groups == 4
+    with pytest.raises(ValueError):
+        RaggedGroupNorm(5, 24)
+    x, lengths = torch.randn(10, 24), torch.tensor([4, 6])
+    with pytest.raises(ValueError):
+        ln(x)                                                 # lengths are required
+    for call in (lambda: ln(x, lengths), lambda: large_segment_reduce(x, "mean", lengths=lengths),
+                 lambda: indexed_segment_reduce(x, "max", torch.tensor([0, 1, 2]), lengths=torch.tensor([1, 2])),
+                 lambda: GlobalPool("max")(x, lengths)):
+        with pytest.raises(RuntimeError, match="CUDA"):
+            call()
+    with pytest.raises(ValueError):
+        large_segment_reduce(x, "median", lengths=lengths)
+    assert RaggedBatchNorm(24)(x).shape == x.shape            # nn.BatchNorm1d, as in the reference
+    net = ResUNet(in_channels=3, num_classes=20)
+    assert sum(p.numel() for p in net.parameters()) == 22_834_100
+    assert net.conv1.weight.shape == (125, 1, 3, 32) and net.final_conv.weight.shape == (1, 1, 96, 20)
