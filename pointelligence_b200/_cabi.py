@@ -168,21 +168,92 @@ def profile_records():
 
 
 # ---------------------------------------------------------------- sparse ----
+# Dense-tap schedule for dense neighbourhoods.  With T triplets over n_feat feature rows and K
+# taps, the scatter engines multiply T rows and add T rows of fp32 into the accumulator.  Once
+# T > K * n_feat / (a few), it is cheaper to multiply EVERY feature row with EVERY tap once
+# (one plain GEMM, (n_feat, inw) x (inw, K*outw), the single library GEMM of this package) and
+# then sum, per output row, the rows of that product its triplets name (the library's indexed
+# segment sum: fp32 accumulation, one rounding, no atomics).  The reference always takes the
+# scatter schedule (sparse_engines/tig.py:1090-1206); results agree within the bf16 bound (the
+# per-tap products are rounded to the feature type before the sum).
+_DENSE_TAPS_RATIO = float(os.environ.get("PCX_DENSE_TAPS_RATIO", "12"))     # T / n_feat from which on
+_DENSE_TAPS_MAX_BYTES = int(os.environ.get("PCX_DENSE_TAPS_MAX_BYTES", str(12 << 30)))
+_LISTS_CACHE = {}
+_LISTS_CACHE_MAX = 64
+
+
+def output_lists(scatter, gather, seg_offs, K, n_out):
+    """Triplets regrouped by output row: ``(src int32 (T,), lengths int64 (n_out,))`` with
+    ``src = gather * K + tap`` in the order of ascending scatter row (stable)."""
+    T = scatter.numel()
+    taps = expand_taps(seg_offs, K, T)
+    order = torch.sort(scatter, stable=True).indices
+    src = (gather.to(torch.int64) * K + taps)[order].to(torch.int32)
+    offs = seg_offs_from_sorted(scatter[order], n_out)
+    return src, offs[1:] - offs[:-1]
+
+
+def cached_output_lists(scatter, gather, seg_offs, K, n_out):
+    import weakref
+
+    key = (scatter.data_ptr(), gather.data_ptr(), seg_offs.data_ptr(), scatter.numel(), int(K), int(n_out))
+    stamp = (scatter._version, gather._version, seg_offs._version)
+    hit = _LISTS_CACHE.get(key)
+    if hit is not None:
+        refs, old_stamp, value = hit
+        if old_stamp == stamp and all(r() is t for r, t in zip(refs, (scatter, gather, seg_offs))):
+            return value
+    value = output_lists(scatter, gather, seg_offs, K, n_out)
+    if len(_LISTS_CACHE) >= _LISTS_CACHE_MAX:
+        dead = [k for k, (refs, _, _) in _LISTS_CACHE.items() if any(r() is None for r in refs)]
+        for k in dead or list(_LISTS_CACHE)[: _LISTS_CACHE_MAX // 2]:
+            _LISTS_CACHE.pop(k, None)
+    _LISTS_CACHE[key] = (tuple(weakref.ref(t) for t in (scatter, gather, seg_offs)), stamp, value)
+    return value
+
+
+def dense_taps_applies(weight, feat, gather, scatter, seg_offs, n_out):
+    K, G, C, M = weight.shape
+    if _DENSE_TAPS_RATIO <= 0 or G != 1 or seg_offs is None or feat.dtype not in (torch.float16, torch.bfloat16):
+        return False
+    n_feat, T = feat.shape[0], gather.numel()
+    if T < _DENSE_TAPS_RATIO * n_feat or n_out <= 0 or n_feat * K >= 2 ** 31:
+        return False
+    if gather.dtype != torch.int32 or scatter.dtype != torch.int32 or C % 8 or M % 8:
+        return False
+    return n_feat * K * max(C, M) * feat.element_size() <= _DENSE_TAPS_MAX_BYTES
+
+
+def mvmr_dense_taps(weight, feat, gather, scatter, seg_offs, n_out, transpose):
+    """MVMR by the dense-tap schedule (see above); same arguments and result as ``mvmr``."""
+    K, G, C, M = weight.shape
+    inw, outw = (M, C) if transpose else (C, M)
+    src, lengths = cached_output_lists(scatter, gather, seg_offs, K, n_out)
+    w3 = weight[:, 0]
+    wcat = (w3.permute(2, 0, 1) if transpose else w3.permute(1, 0, 2)).reshape(inw, K * outw)
+    product = feat @ wcat                                   # (n_feat, K * outw): every row with every tap
+    return indexed_segment_reduce(product.view(feat.shape[0] * K, outw), src, lengths, REDUCE_OPS["sum"])
+
+
 def mvmr(weight, feat, gather, scatter, seg_offs, tap_idx, n_out, transpose, engine=ENGINE_AUTO):
     """``out[scatter[t]] += feat[gather[t]] @ W[tap(t)]`` (``transpose``: use W^T).
 
-    weight (K,G,C,M); feat (n_feat, G*inw); returns (n_out, G*outw) in feat.dtype.
+    weight (K,G,C,M); feat (n_feat, G*inw); returns (n_out, G*outw) in feat.dtype.  With the
+    automatic engine, dense neighbourhoods (many triplets per feature row) take the dense-tap
+    schedule, everything else the scatter engines of ``pcx_mvmr``.
     """
     require_cuda(weight, feat, gather, scatter, seg_offs, tap_idx)
     K, G, C, M = weight.shape
     code = dtype_code(feat.dtype)
     assert weight.dtype == feat.dtype, (weight.dtype, feat.dtype)
     weight, feat = weight.contiguous(), feat.contiguous()
+    n_out = int(n_out)
+    if engine == ENGINE_AUTO and dense_taps_applies(weight, feat, gather, scatter, seg_offs, n_out):
+        return mvmr_dense_taps(weight, feat, gather, scatter, seg_offs, n_out, transpose)
     gather, scatter, tap_idx = as_i32(gather), as_i32(scatter), as_i32(tap_idx)
     if seg_offs is not None:
         seg_offs = seg_offs.to(torch.int64).contiguous()
     outw = C if transpose else M
-    n_out = int(n_out)
     out = torch.empty((n_out, G * outw), dtype=feat.dtype, device=feat.device)
     L = lib()
     with torch.cuda.device(feat.device):
