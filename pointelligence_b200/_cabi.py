@@ -177,7 +177,7 @@ def profile_records():
 # scatter schedule (sparse_engines/tig.py:1090-1206); results agree within the bf16 bound (the
 # per-tap products are rounded to the feature type before the sum).
 _DENSE_TAPS_RATIO = float(os.environ.get("PCX_DENSE_TAPS_RATIO", "12"))     # T / n_feat from which on
-_DENSE_TAPS_MAX_BYTES = int(os.environ.get("PCX_DENSE_TAPS_MAX_BYTES", str(12 << 30)))
+_DENSE_TAPS_MAX_BYTES = int(os.environ.get("PCX_DENSE_TAPS_MAX_BYTES", str(32 << 30)))
 _LISTS_CACHE = {}
 _LISTS_CACHE_MAX = 64
 
