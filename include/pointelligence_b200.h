@@ -140,6 +140,24 @@ int pcx_vvor_static_scratch(const void *d_a, const int32_t *d_a_idx, const void 
                             void *stream);
 
 /* ------------------------------------------------------------------------
+ * Per-output lists for the dense-tap schedule.
+ *
+ * For scenes with more triplets per feature row than taps it is cheaper to
+ * multiply every feature row with every tap once (a plain GEMM,
+ * (n_feat, C_in) x (C_in, K*C_out), left to the caller) and to sum, per output
+ * row, the rows of that product its triplets name -- pcx_indexed_segment_reduce
+ * with op = 0 over the lists built here: d_src[e] = gather * K + tap in the
+ * order of ascending scatter row (stable), d_lengths[r] = triplets of output
+ * row r.  n_feat * K must fit int32.  The reference never leaves the scatter
+ * schedule (sparse_engines/tig.py:1090-1206); there is no counterpart.
+ */
+size_t pcx_output_lists_workspace_bytes(int64_t T, int64_t n_out);
+int pcx_output_lists(const int32_t *d_scatter, const int32_t *d_gather,
+                     const int64_t *d_seg_offs, int64_t T, int K, int64_t n_feat,
+                     int64_t n_out, int32_t *d_src, int64_t *d_lengths, void *d_ws,
+                     size_t ws_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
  * Segment reductions (op: 0 sum, 1 mean, 2 max, 3 min; fp32 accumulation,
  * inputs, outputs and gradients all in `dtype`).
  *

@@ -48,6 +48,9 @@ SIGNATURES = {
     "pcx_vvor": (c_int, [c_void_p] * 7 + [c_int64] * 4 + [c_int] * 5 + [c_void_p, c_size_t, c_void_p]),
     "pcx_vvor_static_scratch_max_elements": (c_size_t, []),
     "pcx_vvor_static_scratch": (c_int, [c_void_p] * 6 + [c_int64] * 4 + [c_int] * 4 + [c_void_p]),
+    "pcx_output_lists_workspace_bytes": (c_size_t, [c_int64, c_int64]),
+    "pcx_output_lists": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 2
+                         + [c_void_p, c_size_t, c_void_p]),
     "pcx_segment_reduce_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "pcx_segment_reduce": (c_int, [c_void_p] * 3 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_size_t,
                                                    c_void_p]),
@@ -182,18 +185,24 @@ _LISTS_CACHE = {}
 _LISTS_CACHE_MAX = 64
 
 
-def output_lists(scatter, gather, seg_offs, K, n_out):
+def output_lists(scatter, gather, seg_offs, K, n_out, n_feat):
     """Triplets regrouped by output row: ``(src int32 (T,), lengths int64 (n_out,))`` with
     ``src = gather * K + tap`` in the order of ascending scatter row (stable)."""
-    T = scatter.numel()
-    taps = expand_taps(seg_offs, K, T)
-    order = torch.sort(scatter, stable=True).indices
-    src = (gather.to(torch.int64) * K + taps)[order].to(torch.int32)
-    offs = seg_offs_from_sorted(scatter[order], n_out)
-    return src, offs[1:] - offs[:-1]
+    require_cuda(scatter, gather, seg_offs)
+    scatter, gather = as_i32(scatter), as_i32(gather)
+    seg_offs = seg_offs.to(torch.int64).contiguous()
+    dev, T = scatter.device, scatter.numel()
+    src = torch.empty(T, dtype=torch.int32, device=dev)
+    lengths = torch.empty(int(n_out), dtype=torch.int64, device=dev)
+    L = lib()
+    with torch.cuda.device(dev):
+        ws = workspace(L.pcx_output_lists_workspace_bytes(T, int(n_out)), dev)
+        check(L.pcx_output_lists(ptr(scatter), ptr(gather), ptr(seg_offs), T, int(K), int(n_feat), int(n_out),
+                                 ptr(src), ptr(lengths), ptr(ws), ws.numel(), stream_ptr()))
+    return src, lengths
 
 
-def cached_output_lists(scatter, gather, seg_offs, K, n_out):
+def cached_output_lists(scatter, gather, seg_offs, K, n_out, n_feat):
     import weakref
 
     key = (scatter.data_ptr(), gather.data_ptr(), seg_offs.data_ptr(), scatter.numel(), int(K), int(n_out))
@@ -203,7 +212,7 @@ def cached_output_lists(scatter, gather, seg_offs, K, n_out):
         refs, old_stamp, value = hit
         if old_stamp == stamp and all(r() is t for r, t in zip(refs, (scatter, gather, seg_offs))):
             return value
-    value = output_lists(scatter, gather, seg_offs, K, n_out)
+    value = output_lists(scatter, gather, seg_offs, K, n_out, n_feat)
     if len(_LISTS_CACHE) >= _LISTS_CACHE_MAX:
         dead = [k for k, (refs, _, _) in _LISTS_CACHE.items() if any(r() is None for r in refs)]
         for k in dead or list(_LISTS_CACHE)[: _LISTS_CACHE_MAX // 2]:
@@ -228,7 +237,7 @@ def mvmr_dense_taps(weight, feat, gather, scatter, seg_offs, n_out, transpose):
     """MVMR by the dense-tap schedule (see above); same arguments and result as ``mvmr``."""
     K, G, C, M = weight.shape
     inw, outw = (M, C) if transpose else (C, M)
-    src, lengths = cached_output_lists(scatter, gather, seg_offs, K, n_out)
+    src, lengths = cached_output_lists(scatter, gather, seg_offs, K, n_out, feat.shape[0])
     w3 = weight[:, 0]
     wcat = (w3.permute(2, 0, 1) if transpose else w3.permute(1, 0, 2)).reshape(inw, K * outw)
     product = feat @ wcat                                   # (n_feat, K * outw): every row with every tap

@@ -35,7 +35,7 @@ def test_output_lists_regroup_the_triplets_by_output_row():
     K, n_in, n_out = 27, 300, 250
     i, j, k = _triplets(rng, K, n_in, n_out, 9000)
     seg = _cabi.seg_offs_from_sorted(_t(k), K)
-    src, lengths = _cabi.output_lists(_t(i), _t(j), seg, K, n_out)
+    src, lengths = _cabi.output_lists(_t(i), _t(j), seg, K, n_out, n_in)
     order = np.argsort(i, kind="stable")
     assert np.array_equal(src.cpu().numpy(), (j.astype(np.int64) * K + k)[order])
     assert np.array_equal(lengths.cpu().numpy(), np.bincount(i, minlength=n_out))
