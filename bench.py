@@ -546,8 +546,24 @@ def run_backbone(args, rank, local_rank, world):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    sizes = np.random.default_rng(1000 + rank).integers(args.scene_min, args.scene_max + 1, args.scenes)
-    clouds = [indoor_scene(int(n), rank * args.scenes + s) for s, n in enumerate(sizes)]
+    if args.scene == "lidar":
+        # config 5 stand-in: a global batch of 16 spinning-LiDAR sweeps split over the ranks,
+        # de-duplicated on the 5 cm grid the model runs on
+        from pointelligence_b200.synthetic import lidar_sweep
+
+        grid, per_rank = 0.05, max(1, 16 // world)
+        clouds = []
+        for s in range(per_rank):
+            p = lidar_sweep(100 + rank * per_rank + s)
+            _, first = np.unique(np.floor(p / grid).astype(np.int64), axis=0, return_index=True)
+            clouds.append(p[np.sort(first)])
+        scene_desc = f"{per_rank} synthetic 64-beam LiDAR sweeps per rank (global batch {per_rank * world}), 5 cm grid"
+    else:
+        grid = 0.02
+        sizes = np.random.default_rng(1000 + rank).integers(args.scene_min, args.scene_max + 1, args.scenes)
+        clouds = [indoor_scene(int(n), rank * args.scenes + s) for s, n in enumerate(sizes)]
+        scene_desc = (f"{args.scenes} indoor scenes of {args.scene_min}-{args.scene_max} points per rank, "
+                      "2 cm grid")
     pts_np, inds_np, sizes_np = ragged_batch(clouds)
     pts, inds, lens = (torch.from_numpy(a).to(dev) for a in (pts_np, inds_np, sizes_np))
     n = pts.shape[0]
@@ -561,7 +577,7 @@ def run_backbone(args, rank, local_rank, world):
     def step():
         for p in params:
             p.grad = None
-        logits = model(feat, pts, inds, lens, 0.02)
+        logits = model(feat, pts, inds, lens, grid)
         loss = F.cross_entropy(logits.float(), labels)
         loss.backward()
         if world > 1:
@@ -602,8 +618,7 @@ def run_backbone(args, rank, local_rank, world):
             "metric": "resunet_train_step_throughput", "value": n_all / (ms * 1e-3) / 1e6, "unit": "Mpoints/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"ResUNet 32/64/128/256, BasicBlock x2 per stage, {args.scenes} indoor scenes of "
-                                   f"{args.scene_min}-{args.scene_max} points per rank, 2 cm grid, "
+            "config": {"workload": f"ResUNet 32/64/128/256, BasicBlock x2 per stage, {scene_desc}, "
                                    "fwd + CE + bwd + gradient all-reduce, geometry rebuilt every step",
                        "points_rank0": n, "parameters": int(sum(p.numel() for p in params)),
                        "l2": "working set of a step (GBs of activations) exceeds the L2",
@@ -628,6 +643,8 @@ def main():
     ap.add_argument("--workload", default="conv", choices=["conv", "block_ops", "backbone"],
                     help="conv: the headline convolution step; block_ops: norm / pooling passes of a residual "
                          "block; backbone: one training step of the residual U-Net (weak scaling over ranks)")
+    ap.add_argument("--scene", default="indoor", choices=["indoor", "lidar"],
+                    help="backbone workload: indoor scenes (config 4) or LiDAR sweeps (config 5)")
     ap.add_argument("--scenes", type=int, default=8, help="backbone workload: scenes per rank")
     ap.add_argument("--scene-min", type=int, default=80000, help="backbone workload: smallest scene")
     ap.add_argument("--scene-max", type=int, default=200000, help="backbone workload: largest scene")
