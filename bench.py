@@ -237,6 +237,12 @@ def run_ours(args, rank, local_rank, world):
             pts, sample, sizes, RADIUS, KERNEL, radius_scaler=RADIUS / TAP_GRID)),
         "downsample_stride2": _wall(lambda: downsample(pts, sample, 0.02, 2)),
     }
+    if args.resident_only:
+        # config 3's overlapping strided convolution: stride 2 needs kernel size 5 (125 taps)
+        from pointelligence_b200.layers.triplets import build_full_cover_strided_rulebook
+
+        geometry_ms["full_cover_rulebook_stride2_k5"] = _wall(lambda: build_full_cover_strided_rulebook(
+            pts, sample, sizes, stride=2, input_grid_size=0.02, kernel_size=5), reps=3)
     g = torch.Generator(device=dev).manual_seed(rank + 1)
     C = M = args.channels
     bound = 1.0 / np.sqrt(M * K)
