@@ -26,7 +26,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 ORACLE_SO = os.path.join(OUT, "liboracle_sparse.so")
 REF_SO = os.path.join(OUT, "libsparse_engines_ref_cpu.so")
-DEFAULT_REFERENCE = os.environ.get("POINTELLIGENCE_REFERENCE", "/root/reference")
+# the reference checkout: POINTELLIGENCE_REFERENCE, else a directory "reference" beside this repository
+DEFAULT_REFERENCE = os.environ.get("POINTELLIGENCE_REFERENCE",
+                                   os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 _REF_SOURCES = ("definitions.cpp", "spare_mvmr.cpp", "sparse_vvor.cpp", "common.cpp")
 
 

@@ -299,7 +299,8 @@ def gen_segment(torch, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("POINTELLIGENCE_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("POINTELLIGENCE_REFERENCE",
+                                                           os.path.join(os.path.dirname(ROOT), "reference")))
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
