@@ -163,6 +163,44 @@ def cpu_reference_step(d):
     return time.perf_counter() - t0, kind
 
 
+def cpu_torch_step(d):
+    """The same step as a multi-threaded CPU yardstick: fp32 gather -> matmul per tap -> index_add_
+    (the formulation the reference's tests use as their oracle, tests/unittest/test_tig_forward.py:27-38)."""
+    import torch
+
+    x, go = torch.from_numpy(d["x"][:, 0]), torch.from_numpy(d["go"][:, 0])
+    w = torch.from_numpy(d["w"][:, 0])
+    i, j, k = (torch.from_numpy(np.asarray(d[name]).astype(np.int64)) for name in ("i", "j", "k"))
+    seg = np.searchsorted(d["k"], np.arange(KERNEL ** 3 + 1))
+    t0 = time.perf_counter()
+    out, gx, gw = torch.zeros_like(go), torch.zeros_like(x), torch.zeros_like(w)
+    for tap in range(KERNEL ** 3):
+        lo, hi = int(seg[tap]), int(seg[tap + 1])
+        if lo == hi:
+            continue
+        xs, gs = x[j[lo:hi]], go[i[lo:hi]]
+        out.index_add_(0, i[lo:hi], xs @ w[tap])
+        gx.index_add_(0, j[lo:hi], gs @ w[tap].t())
+        gw[tap] = xs.t() @ gs
+    return time.perf_counter() - t0, torch.get_num_threads()
+
+
+def cpu_geometry_ms(seed, crop_points):
+    """CPU restatement of the geometry stage (numpy) on the same crop: tap-segmented radius search
+    and stride-2 centre-nearest down-sampling, milliseconds each."""
+    from oracle import geometry as og
+    from pointelligence_b200.synthetic import indoor_scene
+
+    pts = _crop(indoor_scene(N_POINTS, seed), crop_points)
+    t0 = time.perf_counter()
+    og.radius_search_sorted_grid8_segments(pts, pts, RADIUS, KERNEL, TAP_GRID)
+    t1 = time.perf_counter()
+    og.grid_sample_center_nearest(pts, 0.04, np.zeros(len(pts), np.int64))
+    t2 = time.perf_counter()
+    return {"radius_search_segments_restatement": (t1 - t0) * 1e3, "downsample_stride2_restatement": (t2 - t1) * 1e3,
+            "points": len(pts)}
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -459,6 +497,11 @@ def run_ours(args, rank, local_rank, world):
                 "sample": f"spatial crop of {d['n']} points / {len(d['i'])} triplets of the same scene, "
                           "fp32 operands, fwd+dgrad+wgrad, best of 2",
                 "host_cpus": os.cpu_count()}
+            dt_torch, threads = cpu_torch_step(d)
+            dt_torch = min(dt_torch, cpu_torch_step(d)[0])
+            line["cpu_baseline"]["torch_all_cores"] = {"value": len(d["i"]) / dt_torch / 1e9, "unit": UNIT,
+                                                       "threads": threads, "kind": "fp32 gather-matmul-index_add"}
+            line["cpu_baseline"]["geometry_cpu_ms"] = cpu_geometry_ms(0, 40000)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
