@@ -213,9 +213,12 @@ def cached_output_lists(scatter, gather, seg_offs, K, n_out, n_feat):
         if old_stamp == stamp and all(r() is t for r, t in zip(refs, (scatter, gather, seg_offs))):
             return value
     value = output_lists(scatter, gather, seg_offs, K, n_out, n_feat)
+    # lists of rulebooks whose index tensors are gone are dropped at once (a training loop
+    # builds new rulebooks every step); live ones are bounded by the cache size
+    for k in [k for k, (refs, _, _) in _LISTS_CACHE.items() if any(r() is None for r in refs)]:
+        _LISTS_CACHE.pop(k, None)
     if len(_LISTS_CACHE) >= _LISTS_CACHE_MAX:
-        dead = [k for k, (refs, _, _) in _LISTS_CACHE.items() if any(r() is None for r in refs)]
-        for k in dead or list(_LISTS_CACHE)[: _LISTS_CACHE_MAX // 2]:
+        for k in list(_LISTS_CACHE)[: _LISTS_CACHE_MAX // 2]:
             _LISTS_CACHE.pop(k, None)
     _LISTS_CACHE[key] = (tuple(weakref.ref(t) for t in (scatter, gather, seg_offs)), stamp, value)
     return value
