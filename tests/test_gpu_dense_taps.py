@@ -79,3 +79,47 @@ def test_automatic_route_keeps_sparse_neighbourhoods_on_the_scatter_engine():
     seg = _cabi.seg_offs_from_sorted(_t(k), K)
     assert not _cabi.dense_taps_applies(w, x, _t(j), _t(i), seg, n)
     assert not _cabi.dense_taps_applies(w.float(), x.float(), _t(j), _t(i), seg, n)
+
+
+def test_pointconv3d_on_a_dense_cloud_takes_the_dense_tap_schedule_and_matches_the_oracle():
+    """End to end through the layer API: a cloud with about 30 neighbours per point (more than
+    the 27 taps) runs forward and input gradient on the dense-tap schedule, the weight gradient
+    on the tensor kernel, and all three agree with the float64 oracle on the reference's
+    triplets (bf16 bound 2e-2)."""
+    from oracle import geometry as og
+    from pointelligence_b200 import _cabi
+    from pointelligence_b200.layers import MetaData, PointConv3d, conv_with_stride
+
+    rng = np.random.default_rng(21)
+    pts = (rng.random((6000, 3)) * 0.5).astype(np.float32)          # 6000 points in a 0.5 m cube
+    n, C, M = len(pts), 64, 32
+    dev = "cuda:0"
+    conv = PointConv3d(C, M, 3, bias=False, device=dev, dtype=torch.bfloat16)
+    x = torch.randn(n, C, device=dev).bfloat16().requires_grad_(True)
+    m = MetaData(points=_t(pts), sample_inds=torch.zeros(n, dtype=torch.int64, device=dev),
+                 sample_sizes=torch.tensor([n], device=dev), grid_size=0.02)
+    _cabi.profile_enable(True)
+    y, m = conv_with_stride(conv, x, m, 1, receptive_field_scaler=2.5)
+    go = torch.randn_like(y)
+    y.backward(go)
+    torch.cuda.synchronize()
+    names = [name for name, _ in _cabi.profile_records()]
+    _cabi.profile_enable(False)
+    T = int(m.i.numel())
+    assert T >= 12 * n, (T, n)
+    assert names.count("idx_reduce_kernel") == 2 and "vvor_tc_kernel" in names, names
+    assert not any(name.startswith("mvmr_tc_kernel") for name in names), names
+    rs = og.radius_scaler_for_kernel_size(3, 2.5)
+    oi, oj, oseg, _ = og.radius_search_sorted_grid8_segments(pts, pts, 0.02 * rs, 3, 0.02, fma=True)
+    ok = np.repeat(np.arange(27), np.diff(oseg)).astype(np.int32)
+    assert np.array_equal(og.canonical_triplet_keys(m.i.cpu().numpy(), m.j.cpu().numpy(), m.k.cpu().numpy(), n, n),
+                          og.canonical_triplet_keys(oi, oj, ok, n, n))
+    wn = conv.weight.detach().float().cpu().numpy().astype(np.float64)
+    xn = x.detach().float().cpu().numpy().astype(np.float64)
+    gn = go.float().cpu().numpy().astype(np.float64)
+    ref = oso.mvmr_f64(wn, ok, xn[:, None, :], oj, oi, n)[:, 0]
+    assert oso.rel_frobenius(y.detach().float().cpu().numpy(), ref) < 2e-2
+    ref_gx = oso.mvmr_f64(np.swapaxes(wn, 2, 3), ok, gn[:, None, :], oi, oj, n)[:, 0]
+    assert oso.rel_frobenius(x.grad.float().cpu().numpy(), ref_gx) < 2e-2
+    ref_gw = oso.vvor_f64(xn[:, None, :], oj, gn[:, None, :], oi, ok, 27)
+    assert oso.rel_frobenius(conv.weight.grad.float().cpu().numpy(), ref_gw) < 2e-2
