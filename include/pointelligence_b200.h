@@ -55,7 +55,8 @@ int pcx_version(void);
 const char *pcx_last_error_string(void);
 
 /* Device-side status word: kernels that give up on a bounded wait set a bit
- * (1 = MVMR tensor kernel, 2 = VVOR tensor kernel).  Synchronises `stream`,
+ * (1 = MVMR tensor kernel, 2 = VVOR tensor kernel, 4 = output-stationary MVMR
+ * kernel, 8 = pcx_debug_wait_runs_out).  Synchronises `stream`,
  * copies the word to *h_status and clears it when `clear` is non-zero.
  * No counterpart in the reference (its kernels have no device-side waits). */
 int pcx_device_status(unsigned int *h_status, int clear, void *stream);
@@ -98,6 +99,58 @@ int pcx_mvmr(const void *d_weight, const void *d_feat, const int32_t *d_gather,
              const int32_t *d_tap_idx, void *d_out, int64_t T, int64_t n_feat,
              int64_t n_out, int K, int G, int C, int M, int transpose,
              int dtype, int engine, void *d_ws, size_t ws_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Output-stationary MVMR: same result as pcx_mvmr (fp16 / bf16, one group,
+ * tap-sorted triplets), computed from a "plan" of the rulebook.
+ *
+ * Replaces the same reference code as pcx_mvmr and, for the regrouping of the
+ * rulebook by output row with its (row, tap) buckets summed before the
+ * contraction, sparse_engines/fused_point_conv.py:344-423 (kernel) and
+ * :785-870 (rulebook preparation).
+ *
+ * pcx_mvmr_plan_build regroups the triplets (scatter, gather, tap) by blocks
+ * of 128 output rows, the rows ordered by the set of taps that touch them.  A
+ * plan depends on the index arrays only: build it once per rulebook and
+ * direction (forward: scatter = output index, gather = input index; input
+ * gradient: the two swapped) and use it for every layer and step that shares
+ * the rulebook.  pcx_mvmr_planned then keeps the fp32 sums of every block in
+ * tensor memory across all taps and writes each output row once: no
+ * workspace, no zero-fill, no atomics, bit-reproducible.  Rows that no
+ * triplet touches are written as zero.
+ *
+ *   group_blocks  blocks that share the weight tiles they stream;
+ *                 pcx_mvmr_plan_group_blocks(out_width) gives the value to use
+ *                 for an output row of out_width channels.  The same value
+ *                 must be passed to both calls (a plan built for one value is
+ *                 not valid for another).
+ *   d_plan        caller-owned, 256-byte aligned, pcx_mvmr_plan_bytes();
+ *                 pcx_mvmr_planned updates a work counter inside it, so two
+ *                 launches that use the same plan must not overlap on the GPU
+ *   limits        K <= 512, channel counts multiples of 16, out_width <= 256,
+ *                 T < 2^31, ceil(n_out / 128) * K * 128 <= 2^32
+ * Several triplets of one (row, tap) bucket are summed in the feature type
+ * before they are multiplied (one extra rounding per added row).
+ */
+int pcx_mvmr_plan_group_blocks(int out_width);
+size_t pcx_mvmr_plan_bytes(int64_t T, int64_t n_out, int K, int group_blocks);
+size_t pcx_mvmr_plan_workspace_bytes(int64_t T, int64_t n_out, int K,
+                                     int group_blocks);
+int pcx_mvmr_plan_build(const int32_t *d_scatter, const int32_t *d_gather,
+                        const int64_t *d_seg_offs, int64_t T, int K,
+                        int64_t n_out, int group_blocks, void *d_plan,
+                        size_t plan_bytes, void *d_ws, size_t ws_bytes,
+                        void *stream);
+int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan,
+                     size_t plan_bytes, void *d_out, int64_t T, int64_t n_feat,
+                     int64_t n_out, int K, int C, int M, int transpose,
+                     int dtype, int group_blocks, void *stream);
+
+/* Launches one thread that waits on a barrier nothing arrives at: the bounded
+ * wait gives up after limit_ns (at most 100 ms), sets bit 8 of the device
+ * status word and the kernel returns.  For tests of the status path; no
+ * counterpart in the reference. */
+int pcx_debug_wait_runs_out(unsigned long long limit_ns, void *stream);
 
 /* ------------------------------------------------------------------------
  * VVOR:  out[o[t], g, m, c] += a[ai[t], g, m] * b[bi[t], g, c]

@@ -91,6 +91,55 @@ def vvor_f64(a, a_idx, b, b_idx, o_idx, n_o):
     return o
 
 
+def mvmr_f64_taps(a, seg_offs, b, b_idx, o_idx, n_o, rows=None):
+    """MVMR in fp64 for TAP-SORTED triplets (``seg_offs`` = K+1 segment offsets), one group:
+    per tap one dense product of the gathered rows with ``a[k]`` and a sparse-matrix sum into
+    the output rows.  Same result as ``mvmr_f64`` (it is the same sum in another order) but
+    affordable at benchmark sizes.  With ``rows`` (sorted unique output rows) only those rows
+    are computed and returned, in that order.  a (K,1,C,M) or (K,C,M); b (Nb,C) -> (n_o, M).
+    """
+    import scipy.sparse as sp
+
+    a = np.asarray(a, np.float64)
+    a = a.reshape(a.shape[0], a.shape[-2], a.shape[-1])
+    b = np.asarray(b, np.float64).reshape(len(b), -1)
+    b_idx, o_idx, seg = np.asarray(b_idx), np.asarray(o_idx), np.asarray(seg_offs)
+    if rows is not None:
+        rows = np.asarray(rows)
+        keep = np.isin(o_idx, rows)
+        slot = np.searchsorted(rows, o_idx)
+        n_res = len(rows)
+    else:
+        keep, slot, n_res = None, o_idx, n_o
+    out = np.zeros((n_res, a.shape[2]), np.float64)
+    for k in range(a.shape[0]):
+        lo, hi = int(seg[k]), int(seg[k + 1])
+        if hi <= lo:
+            continue
+        sel = np.arange(lo, hi) if keep is None else lo + np.flatnonzero(keep[lo:hi])
+        if len(sel) == 0:
+            continue
+        prod = b[b_idx[sel]] @ a[k]
+        scatter = sp.csr_matrix((np.ones(len(sel)), (slot[sel], np.arange(len(sel)))), shape=(n_res, len(sel)))
+        out += scatter @ prod
+    return out
+
+
+def vvor_f64_taps(a, a_idx, b, b_idx, seg_offs, taps=None):
+    """VVOR in fp64 for TAP-SORTED triplets, one group: ``out[k] = a[a_idx[seg k]]^T @ b[b_idx[seg k]]``.
+    With ``taps`` only those taps are computed (result (len(taps), Ma, Cb))."""
+    a = np.asarray(a, np.float64).reshape(len(a), -1)
+    b = np.asarray(b, np.float64).reshape(len(b), -1)
+    a_idx, b_idx, seg = np.asarray(a_idx), np.asarray(b_idx), np.asarray(seg_offs)
+    taps = range(len(seg) - 1) if taps is None else taps
+    out = np.zeros((len(taps), a.shape[1], b.shape[1]), np.float64)
+    for n, k in enumerate(taps):
+        lo, hi = int(seg[k]), int(seg[k + 1])
+        if hi > lo:
+            out[n] = a[a_idx[lo:hi]].T @ b[b_idx[lo:hi]]
+    return out
+
+
 def mvmr_c(a, a_idx, b, b_idx, o_idx, n_o):
     a, b = _f32(a), _f32(b)
     ai, bi, oi = _i32(a_idx), _i32(b_idx), _i32(o_idx)

@@ -44,6 +44,13 @@ SIGNATURES = {
     "pcx_profile_get": (c_int, [c_int, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_float)]),
     "pcx_mvmr_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int]),
     "pcx_mvmr": (c_int, [c_void_p] * 7 + [c_int64] * 3 + [c_int] * 7 + [c_void_p, c_size_t, c_void_p]),
+    "pcx_mvmr_plan_group_blocks": (c_int, [c_int]),
+    "pcx_mvmr_plan_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int]),
+    "pcx_mvmr_plan_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int]),
+    "pcx_mvmr_plan_build": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p,
+                                    c_size_t, c_void_p]),
+    "pcx_mvmr_planned": (c_int, [c_void_p] * 3 + [c_size_t, c_void_p] + [c_int64] * 3 + [c_int] * 6 + [c_void_p]),
+    "pcx_debug_wait_runs_out": (c_int, [ctypes.c_ulonglong, c_void_p]),
     "pcx_vvor_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
     "pcx_vvor": (c_int, [c_void_p] * 7 + [c_int64] * 4 + [c_int] * 5 + [c_void_p, c_size_t, c_void_p]),
     "pcx_vvor_static_scratch_max_elements": (c_size_t, []),
@@ -245,6 +252,124 @@ def mvmr_dense_taps(weight, feat, gather, scatter, seg_offs, n_out, transpose):
     wcat = (w3.permute(2, 0, 1) if transpose else w3.permute(1, 0, 2)).reshape(inw, K * outw)
     product = feat @ wcat                                   # (n_feat, K * outw): every row with every tap
     return indexed_segment_reduce(product.view(feat.shape[0] * K, outw), src, lengths, REDUCE_OPS["sum"])
+
+
+class MvmrPlan:
+    """A rulebook regrouped for the output-stationary MVMR kernel (``pcx_mvmr_plan_build``).
+
+    Holds the device buffer and the sizes it was built for.  A plan belongs to one rulebook,
+    one direction (which index is scattered) and one ``group_blocks`` value.
+    """
+
+    __slots__ = ("buffer", "T", "K", "n_out", "group_blocks", "__weakref__")
+
+    def __init__(self, buffer, T, K, n_out, group_blocks):
+        self.buffer, self.T, self.K, self.n_out, self.group_blocks = buffer, T, K, n_out, group_blocks
+
+    def views(self):
+        """The plan's arrays as tensors (for tests): perm, tile_offs, entries (T, 2), group_order."""
+        nblocks = (self.n_out + 127) // 128
+        ngroups = (nblocks + self.group_blocks - 1) // self.group_blocks
+
+        def up(n):
+            return (n + 255) // 256 * 256
+
+        buf, off, out = self.buffer, 0, {}
+        for name, count, dtype, width in (("ctrl", 64, torch.int32, 4), ("perm", nblocks * 128, torch.int32, 4),
+                                          ("tile_offs", nblocks * self.K + 1, torch.int32, 4),
+                                          ("entries", max(self.T, 1) * 2, torch.int32, 4),
+                                          ("group_order", max(ngroups, 1), torch.int32, 4)):
+            out[name] = buf[off:off + count * width].view(dtype)
+            off += up(count * width)
+        out["entries"] = out["entries"][: self.T * 2].view(-1, 2)
+        out["group_order"] = out["group_order"][:ngroups]
+        return out
+
+
+def plan_group_blocks(out_width):
+    """Blocks of 128 output rows that share the weight tiles they stream, for rows of ``out_width`` channels."""
+    return int(lib().pcx_mvmr_plan_group_blocks(int(out_width)))
+
+
+def planned_supported(weight, feat, gather, scatter, seg_offs, n_out, transpose):
+    """Whether the output-stationary kernel takes this call (fp16 / bf16, one group, tap-sorted
+    int32 triplets, channel counts that are multiples of 16, output rows of at most 256 channels)."""
+    K, G, C, M = weight.shape
+    inw, outw = (M, C) if transpose else (C, M)
+    if G != 1 or seg_offs is None or feat.dtype not in (torch.float16, torch.bfloat16) or n_out <= 0:
+        return False
+    if inw % 16 or outw % 16 or outw > 256 or inw > 1024 or K > 512:
+        return False
+    T = gather.numel()
+    nblocks = (int(n_out) + 127) // 128
+    return T < 2 ** 31 and nblocks * K * 128 <= 2 ** 32
+
+
+def mvmr_plan(scatter, gather, seg_offs, K, n_out, group_blocks):
+    """Build the plan of a tap-sorted rulebook: ``scatter`` indexes the rows that are summed
+    into (n_out of them), ``gather`` the rows that are read."""
+    require_cuda(scatter, gather, seg_offs)
+    scatter, gather = as_i32(scatter), as_i32(gather)
+    seg_offs = seg_offs.to(torch.int64).contiguous()
+    dev, T, n_out, K, G = scatter.device, scatter.numel(), int(n_out), int(K), int(group_blocks)
+    L = lib()
+    nbytes = L.pcx_mvmr_plan_bytes(T, n_out, K, G)
+    if nbytes == 0:
+        raise NotImplementedError(f"no output-stationary plan for T={T} n_out={n_out} K={K} group={G}")
+    with torch.cuda.device(dev):
+        buf = workspace(nbytes, dev)
+        ws = workspace(L.pcx_mvmr_plan_workspace_bytes(T, n_out, K, G), dev)
+        check(L.pcx_mvmr_plan_build(ptr(scatter), ptr(gather), ptr(seg_offs), T, K, n_out, G, ptr(buf), buf.numel(),
+                                    ptr(ws), ws.numel(), stream_ptr()))
+    return MvmrPlan(buf, T, K, n_out, G)
+
+
+_PLAN_CACHE = {}
+_PLAN_CACHE_MAX = 64
+
+
+def cached_mvmr_plan(scatter, gather, seg_offs, K, n_out, group_blocks):
+    """``mvmr_plan`` remembered by the identity (and version) of the index tensors, so that every
+    layer and every step that shares a rulebook builds its plan once."""
+    import weakref
+
+    key = (scatter.data_ptr(), gather.data_ptr(), seg_offs.data_ptr(), scatter.numel(), int(K), int(n_out),
+           int(group_blocks))
+    stamp = (scatter._version, gather._version, seg_offs._version)
+    hit = _PLAN_CACHE.get(key)
+    if hit is not None:
+        refs, old_stamp, value = hit
+        if old_stamp == stamp and all(r() is t for r, t in zip(refs, (scatter, gather, seg_offs))):
+            return value
+    value = mvmr_plan(scatter, gather, seg_offs, K, n_out, group_blocks)
+    for k in [k for k, (refs, _, _) in _PLAN_CACHE.items() if any(r() is None for r in refs)]:
+        _PLAN_CACHE.pop(k, None)
+    if len(_PLAN_CACHE) >= _PLAN_CACHE_MAX:
+        for k in list(_PLAN_CACHE)[: _PLAN_CACHE_MAX // 2]:
+            _PLAN_CACHE.pop(k, None)
+    _PLAN_CACHE[key] = (tuple(weakref.ref(t) for t in (scatter, gather, seg_offs)), stamp, value)
+    return value
+
+
+def mvmr_planned(weight, feat, plan, transpose):
+    """``out[scatter[t]] += feat[gather[t]] @ W[tap(t)]`` for the rulebook of ``plan``
+    (``transpose``: use W^T); returns (plan.n_out, out_width) in feat.dtype."""
+    require_cuda(weight, feat)
+    K, G, C, M = weight.shape
+    assert G == 1 and K == plan.K and weight.dtype == feat.dtype, (weight.shape, plan.K, weight.dtype, feat.dtype)
+    weight, feat = weight.contiguous(), feat.contiguous()
+    outw = C if transpose else M
+    out = torch.empty((plan.n_out, outw), dtype=feat.dtype, device=feat.device)
+    with torch.cuda.device(feat.device):
+        check(lib().pcx_mvmr_planned(ptr(weight), ptr(feat), ptr(plan.buffer), plan.buffer.numel(), ptr(out), plan.T,
+                                     feat.shape[0], plan.n_out, K, C, M, int(bool(transpose)), dtype_code(feat.dtype),
+                                     plan.group_blocks, stream_ptr()))
+    return out
+
+
+def debug_wait_runs_out(limit_ns=1_000_000):
+    """Launch the test kernel whose bounded wait runs out after ``limit_ns``."""
+    check(lib().pcx_debug_wait_runs_out(int(limit_ns), stream_ptr()))
 
 
 def mvmr(weight, feat, gather, scatter, seg_offs, tap_idx, n_out, transpose, engine=ENGINE_AUTO):

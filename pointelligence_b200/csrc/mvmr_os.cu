@@ -1,0 +1,933 @@
+// Output-stationary MVMR on sm_100a: the fp32 sums of a block of 128 output rows stay in
+// tensor memory (TMEM) across ALL taps and every output row is rounded and written exactly
+// once -- no fp32 accumulator in global memory, no zero-fill, no rounding pass, no atomics,
+// and a result that does not depend on the order in which CTAs run.
+//
+// The schedule needs the rulebook regrouped by output row.  That is done once per rulebook
+// and direction by pcx_mvmr_plan_build into a caller-owned "plan":
+//
+//   rows     output rows are ordered by their tap signature (the set of taps that touch the
+//            row), so that the 128 rows of a block use few distinct taps and the
+//            (block, tap) tiles below are well filled; perm[block * 128 + slot] = row
+//   tiles    the triplets of (block, tap), ordered by slot; tile_offs is the dense
+//            (nblocks * K + 1) table of their offsets
+//   entries  per triplet (slot | position among the triplets of the same (row, tap) << 8,
+//            gathered feature row)
+//   groups   G consecutive blocks share the weight tiles they stream; groups are handed out
+//            most expensive first (a ticket counter inside the plan)
+//
+// The kernel (one CTA per SM, TMEM columns = G accumulators of out_width fp32 each):
+//
+//   producer warps   one (block, tap, 64-channel slice) A tile each: zero the 128 x 128 B
+//                    slot, copy the feature row of every first triplet of a (row, tap) bucket
+//                    into its slot row (registers -> 128-byte-swizzled shared memory), add the
+//                    rows of further triplets of the bucket (the bucket pre-sum of the
+//                    reference's fused gather-sum schedule, sparse_engines/
+//                    fused_point_conv.py:344-423), signal the slot's mbarrier
+//   weight warp      streams the 64-channel slices of W[tap] through a small ring with TMA
+//                    (cp.async.bulk.tensor, 128-byte swizzle, no multicast); one slice serves
+//                    all blocks of the group that use the tap
+//   MMA warp         one thread issues tcgen05.mma (M = 128 rows, N = out_width, K = 16 per
+//                    instruction) with accumulate = 1 from the block's second tile on;
+//                    tcgen05.commit releases the A slot, the weight slot and finally hands
+//                    the accumulators to the epilogue
+//   epilogue         the producer warps read TMEM (tcgen05.ld), round once and write each
+//                    output row with 16-byte stores
+//
+// Every wait is bounded (one second) and abortable: a role that gives up raises a flag in the
+// status word and in shared memory, the other roles leave their waits, and the CTA frees its
+// TMEM and returns.
+#include <cub/cub.cuh>
+#include <cuda.h>
+
+#include "sparse_kernels.cuh"
+#include "tcgen05.cuh"
+
+namespace pcx {
+int device_status_address(unsigned int **d_status);
+
+namespace {
+
+using namespace tc;
+
+constexpr int ROWS = 128;             // output rows per block (the M of the MMA)
+constexpr int SLOT_BYTES = ROWS * 128;  // one A tile: 128 rows of a 64-channel slice
+constexpr int MAX_NPW = 10;           // producer warps (= A slots)
+constexpr int MAX_NW = 4;             // weight slots
+constexpr int MAX_GROUP = 8;          // blocks per group
+constexpr int MAX_TAPS = 512;         // taps the shared-memory tables are sized for
+constexpr int UNROLL = 8;             // entries a producer lane holds per batch
+constexpr int SIDE_ROWS = 16;         // rows of a warp's side buffer (further triplets of a bucket)
+constexpr int SIDE_BYTES = SIDE_ROWS * 128;
+constexpr unsigned STATUS_BIT = 4u;   // bit of the device status word this kernel raises
+constexpr unsigned PLAN_MAGIC = 0x70637832u;
+
+// control words at the head of a plan
+enum { CTRL_TICKET = 0, CTRL_DONE = 1, CTRL_MAGIC = 2, CTRL_GROUP = 3, CTRL_WORDS = 64 };
+
+struct PlanView {
+    uint32_t *ctrl;        // CTRL_WORDS
+    int32_t *perm;         // nblocks * ROWS, -1 = padding
+    int32_t *tile_offs;    // nblocks * K + 1
+    uint2 *entries;        // T
+    int32_t *group_order;  // ngroups
+    int64_t nblocks, ngroups;
+};
+
+size_t carve_plan(void *base, int64_t T, int64_t n_out, int K, int G, PlanView *out) {
+    Carver c(base);
+    PlanView v;
+    v.nblocks = (n_out + ROWS - 1) / ROWS;
+    v.ngroups = (v.nblocks + G - 1) / G;
+    v.ctrl = c.take<uint32_t>(CTRL_WORDS);
+    v.perm = c.take<int32_t>((size_t)v.nblocks * ROWS);
+    v.tile_offs = c.take<int32_t>((size_t)v.nblocks * K + 1);
+    v.entries = c.take<uint2>((size_t)std::max<int64_t>(T, 1));
+    v.group_order = c.take<int32_t>((size_t)std::max<int64_t>(v.ngroups, 1));
+    if (out) *out = v;
+    return c.off;
+}
+
+int bits_of(int64_t n) {
+    int bits = 1;
+    while (((int64_t)1 << bits) < n) ++bits;
+    return bits;
+}
+
+struct BuildWs {
+    uint32_t *sig, *sig_sorted;          // n_out
+    int32_t *row, *row_sorted, *rank;    // n_out
+    uint32_t *key, *key_sorted;          // T
+    int32_t *val, *val_sorted;           // T
+    int32_t *tile_cnt;                   // nblocks * K + 1
+    uint32_t *cost, *cost_sorted;        // ngroups
+    int32_t *gid;                        // ngroups
+    void *cub_tmp;
+    size_t cub_bytes;
+};
+
+size_t carve_build(void *base, int64_t T, int64_t n_out, int K, int G, BuildWs *out) {
+    Carver c(base);
+    BuildWs w;
+    const int64_t nblocks = (n_out + ROWS - 1) / ROWS, ngroups = (nblocks + G - 1) / G;
+    const size_t n = (size_t)std::max<int64_t>(n_out, 1), t = (size_t)std::max<int64_t>(T, 1);
+    const size_t g = (size_t)std::max<int64_t>(ngroups, 1);
+    w.sig = c.take<uint32_t>(n), w.sig_sorted = c.take<uint32_t>(n);
+    w.row = c.take<int32_t>(n), w.row_sorted = c.take<int32_t>(n), w.rank = c.take<int32_t>(n);
+    w.key = c.take<uint32_t>(t), w.key_sorted = c.take<uint32_t>(t);
+    w.val = c.take<int32_t>(t), w.val_sorted = c.take<int32_t>(t);
+    w.tile_cnt = c.take<int32_t>((size_t)nblocks * K + 1);
+    w.cost = c.take<uint32_t>(g), w.cost_sorted = c.take<uint32_t>(g);
+    w.gid = c.take<int32_t>(g);
+    size_t b1 = 0, b2 = 0, b3 = 0, b4 = 0;
+    cub::DeviceRadixSort::SortPairs(nullptr, b1, (const uint32_t *)nullptr, (uint32_t *)nullptr, (const int32_t *)nullptr,
+                                    (int32_t *)nullptr, (int)n, 0, 32);
+    cub::DeviceRadixSort::SortPairs(nullptr, b2, (const uint32_t *)nullptr, (uint32_t *)nullptr, (const int32_t *)nullptr,
+                                    (int32_t *)nullptr, (int)t, 0, 32);
+    cub::DeviceScan::ExclusiveSum(nullptr, b3, (const int32_t *)nullptr, (int32_t *)nullptr, (int)((size_t)nblocks * K + 1));
+    cub::DeviceRadixSort::SortPairsDescending(nullptr, b4, (const uint32_t *)nullptr, (uint32_t *)nullptr,
+                                              (const int32_t *)nullptr, (int32_t *)nullptr, (int)g, 0, 32);
+    w.cub_bytes = std::max(std::max(b1, b2), std::max(b3, b4));
+    w.cub_tmp = c.take<char>(w.cub_bytes);
+    if (out) *out = w;
+    return c.off;
+}
+
+__device__ __forceinline__ int tap_of(const int64_t *__restrict__ seg, int K, int64_t t) {
+    int lo = 0, hi = K;  // last k with seg[k] <= t
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (seg[mid] <= t) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__global__ void plan_init_kernel(int64_t n_out, uint32_t *sig, int32_t *row, int32_t *tile_cnt, int64_t n_tiles,
+                                 uint32_t *ctrl, int G) {
+    const int64_t x = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (x < n_out) sig[x] = 0u, row[x] = (int32_t)x;
+    if (x <= n_tiles) tile_cnt[x] = 0;
+    if (x < CTRL_WORDS) ctrl[x] = x == CTRL_MAGIC ? PLAN_MAGIC : x == CTRL_GROUP ? (uint32_t)G : 0u;
+}
+
+// Tap signature of every output row.  With more than 32 taps the taps are folded onto 32
+// bits (tap mod 32): rows that share a signature then share a superset of taps.
+__global__ void plan_sig_kernel(const int32_t *__restrict__ scatter, const int64_t *__restrict__ seg, int64_t T, int K,
+                                uint32_t *sig) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    atomicOr(&sig[scatter[t]], 1u << (tap_of(seg, K, t) & 31));
+}
+
+__global__ void plan_rank_kernel(const int32_t *__restrict__ row_sorted, int64_t n_out, int64_t n_pad, int32_t *rank,
+                                 int32_t *perm) {
+    const int64_t x = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (x >= n_pad) return;
+    if (x < n_out) {
+        const int32_t r = row_sorted[x];
+        rank[r] = (int32_t)x;
+        perm[x] = r;
+    } else {
+        perm[x] = -1;
+    }
+}
+
+__global__ void plan_keys_kernel(const int32_t *__restrict__ scatter, const int32_t *__restrict__ gather,
+                                 const int64_t *__restrict__ seg, const int32_t *__restrict__ rank, int64_t T, int K,
+                                 uint32_t *key, int32_t *val, int32_t *tile_cnt) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const int k = tap_of(seg, K, t);
+    const uint32_t r = (uint32_t)rank[scatter[t]];
+    const uint32_t tile = (r >> 7) * (uint32_t)K + (uint32_t)k;
+    key[t] = (tile << 7) | (r & 127u);
+    val[t] = gather[t];
+    atomicAdd(&tile_cnt[tile], 1);
+}
+
+// entries[t] = (slot | position within the (row, tap) bucket << 8, feature row)
+__global__ void plan_entries_kernel(const uint32_t *__restrict__ key_sorted, const int32_t *__restrict__ val_sorted,
+                                    int64_t T, uint2 *entries) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const uint32_t k = key_sorted[t];
+    uint32_t pos = 0;
+    while (pos < 0xffffffu && t - (int64_t)pos - 1 >= 0 && key_sorted[t - pos - 1] == k) ++pos;
+    entries[t] = make_uint2((k & 127u) | (pos << 8), (uint32_t)val_sorted[t]);
+}
+
+// cost of a group = its non-empty tiles (each is one A tile to gather and multiply)
+__global__ void plan_cost_kernel(const int32_t *__restrict__ tile_offs, int64_t nblocks, int K, int G, int64_t ngroups,
+                                 uint32_t *cost, int32_t *gid) {
+    const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= ngroups) return;
+    const int64_t t0 = g * G * K, t1 = min((g + 1) * (int64_t)G, nblocks) * K;
+    uint32_t c = 0;
+    for (int64_t x = t0; x < t1; ++x) c += tile_offs[x + 1] > tile_offs[x];
+    cost[g] = c;
+    gid[g] = (int32_t)g;
+}
+
+// ------------------------------------------------------------------ kernel ----
+
+struct OsParams {
+    const uint16_t *feat;
+    uint16_t *out;
+    const uint16_t *weight;
+    const int32_t *perm, *tile_offs, *group_order;
+    const uint2 *entries;
+    uint32_t *ctrl;
+    unsigned int *status;
+    int K, C, M, transpose, fmt;
+    int inw, outw, nkb, G, ngroups, nblocks;
+    int npw, nw, use_tma;
+    uint32_t w_slot_bytes, w_box_rows, w_tx_bytes;
+    uint32_t ncols, col_stride;
+    uint64_t wait_limit_ns;
+};
+
+// a + b on eight 16-bit floats (one rounding per element)
+__device__ __forceinline__ uint4 add8(uint4 a, uint4 b, int fmt) {
+    uint4 r;
+    if (fmt) {
+        const __nv_bfloat162 *pa = reinterpret_cast<const __nv_bfloat162 *>(&a), *pb = reinterpret_cast<const __nv_bfloat162 *>(&b);
+        __nv_bfloat162 *pr = reinterpret_cast<__nv_bfloat162 *>(&r);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 fa = __bfloat1622float2(pa[q]), fb = __bfloat1622float2(pb[q]);
+            pr[q] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+        }
+    } else {
+        const __half2 *pa = reinterpret_cast<const __half2 *>(&a), *pb = reinterpret_cast<const __half2 *>(&b);
+        __half2 *pr = reinterpret_cast<__half2 *>(&r);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 fa = __half22float2(pa[q]), fb = __half22float2(pb[q]);
+            pr[q] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+        }
+    }
+    return r;
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
+    if (fmt) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_nc_v2(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+// Optional cycle accounting per role (compile with -DPCX_OS_STATS): sums of clock64() spans are
+// added to the plan's spare control words 8.. and read back by the caller.
+#ifdef PCX_OS_STATS
+#define STAT_T0(name) const long long name = clock64()
+#define STAT_ADD(word, t0) do { if (lane == 0) atomicAdd(&p.ctrl[word], (uint32_t)((clock64() - (t0)) >> 4)); } while (0)
+#else
+#define STAT_T0(name)
+#define STAT_ADD(word, t0)
+#endif
+
+// Task lists of a group, built in shared memory by the whole CTA before the roles start:
+//   A task   one (block, tap, 64-channel slice) tile: its entries [lo, hi) and
+//            meta = block | slice << 4 | first-of-slice << 8 | last-of-slice << 9 | tap << 16
+//   W task   one (tap, slice) weight tile: tap | slice << 16
+// Order (every role walks the same lists): taps ascending; per tap the slices of the
+// contraction; per slice the blocks of the group that use the tap.
+__device__ __forceinline__ int pieces_of(int inw, int q) { return min(8, (inw - q * 64) >> 3); }
+__device__ __forceinline__ int piece_shift(int pieces) { return pieces > 4 ? 3 : pieces > 2 ? 2 : 1; }
+
+// entries from..end: lane (sub, piece) takes entry from + u * subs + sub
+__device__ __forceinline__ void load_entries(uint2 (&dst)[UNROLL], const uint2 *__restrict__ entries, int from, int end,
+                                             int psh, int lane) {
+    const int sub = lane >> psh, subs = 32 >> psh;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int e = from + u * subs + sub;
+        dst[u] = make_uint2(0xffffffffu, 0u);
+        if (e < end) dst[u] = ldg_nc_v2(entries + e);
+    }
+}
+
+__global__ void __launch_bounds__(512, 1)
+mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t s_a_full[MAX_NPW], s_a_empty[MAX_NPW], s_w_full[MAX_NW], s_w_empty[MAX_NW], s_d_full;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_group, s_ntiles, s_ntaps, s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_base = base, w_base = base + (uint32_t)p.npw * SLOT_BYTES;
+    const uint32_t side_base = w_base + (uint32_t)p.nw * p.w_slot_bytes;   // one side buffer per producer warp
+    uint8_t *tab_raw = smem_raw + (side_base + (uint32_t)p.npw * SIDE_BYTES - smem_u32(smem_raw));
+    // tables of the current group (16-byte aligned): A tasks, tile offsets, tile list, run ordinals, W tasks
+    int4 *s_task = reinterpret_cast<int4 *>(tab_raw);                       // G*K*nkb
+    int32_t *s_tab = reinterpret_cast<int32_t *>(s_task + p.G * p.K * p.nkb);  // G*K + 1
+    int32_t *s_list = s_tab + (p.G * p.K + 1);                                // G*K: tap << 8 | block, tap-major
+    int32_t *s_run = s_list + p.G * p.K;                                      // G*K: ordinal of the tile's tap among the group's taps
+    int32_t *s_wtask = s_run + p.G * p.K;                                     // K*nkb
+    int32_t *s_side = s_wtask + p.K * p.nkb;                                  // npw * SIDE_ROWS: target row | position << 8
+    volatile int *abort_flag = &s_abort;
+
+    if (tid == 0) {
+        for (int s = 0; s < p.npw; ++s) mbar_init(smem_u32(&s_a_full[s]), 32), mbar_init(smem_u32(&s_a_empty[s]), 1);
+        for (int s = 0; s < p.nw; ++s) mbar_init(smem_u32(&s_w_full[s]), p.use_tma ? 1 : 32), mbar_init(smem_u32(&s_w_empty[s]), 1);
+        mbar_init(smem_u32(&s_d_full), 1);
+        fence_mbar_init();
+        s_abort = 0;
+        if (p.use_tma) tma_prefetch_desc(&tmap);
+    }
+    if (warp == 0) tmem_alloc(smem_u32(&s_tmem), p.ncols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t idesc = instr_desc(p.fmt, ROWS, p.outw, 0, p.transpose ? 0 : 1);
+
+    // A tiles, weight tiles and accumulator hand-overs of the groups this CTA has finished (all
+    // roles count alike): tile n uses A slot n mod npw for the (n / npw)-th time, and so on
+    uint32_t a_n = 0, w_n = 0, d_n = 0;
+
+    for (;;) {
+        STAT_T0(t_group);
+        if (tid == 0) {
+            const uint32_t ticket = atomicAdd(&p.ctrl[CTRL_TICKET], 1u);
+            s_group = ticket < (uint32_t)p.ngroups ? p.group_order[ticket] : -1;
+        }
+        __syncthreads();
+        const int g = s_group;
+        if (g < 0 || s_abort) break;
+        const int b0 = g * p.G, nb = min(p.G, p.nblocks - b0);
+        for (int x = tid; x <= nb * p.K; x += blockDim.x) s_tab[x] = p.tile_offs[(int64_t)b0 * p.K + x];
+        __syncthreads();
+        if (warp == 0) {  // the non-empty (tap, block) pairs, tap-major, and the ordinal of each pair's tap
+            int count = 0;
+            for (int x0 = 0; x0 < nb * p.K; x0 += 32) {
+                const int x = x0 + lane;
+                int tap = 0, blk = 0;
+                bool has = false;
+                if (x < nb * p.K) {
+                    tap = x / nb, blk = x - tap * nb;
+                    has = s_tab[blk * p.K + tap + 1] > s_tab[blk * p.K + tap];
+                }
+                const unsigned m = __ballot_sync(0xffffffffu, has);
+                if (has) s_list[count + __popc(m & ((1u << lane) - 1u))] = (tap << 8) | blk;
+                count += __popc(m);
+            }
+            __syncwarp();
+            int taps = 0;
+            for (int x0 = 0; x0 < count; x0 += 32) {
+                const int x = x0 + lane;
+                const bool head = x < count && (x == 0 || (s_list[x] >> 8) != (s_list[x - 1] >> 8));
+                const unsigned m = __ballot_sync(0xffffffffu, head);
+                if (x < count) s_run[x] = taps + __popc(m & (0xffffffffu >> (31 - lane))) - 1;
+                taps += __popc(m);
+            }
+            if (lane == 0) s_ntiles = count, s_ntaps = taps;
+        }
+        __syncthreads();
+        const int ntiles = s_ntiles, a_total = ntiles * p.nkb, w_total = s_ntaps * p.nkb;
+        for (int x = tid; x < ntiles; x += blockDim.x) {  // expand the tile list into the task lists
+            const int tap = s_list[x] >> 8, blk = s_list[x] & 255;
+            int r0 = x, r1 = x + 1;
+            while (r0 > 0 && (s_list[r0 - 1] >> 8) == tap) --r0;
+            while (r1 < ntiles && (s_list[r1] >> 8) == tap) ++r1;
+            const int lo = s_tab[blk * p.K + tap], hi = s_tab[blk * p.K + tap + 1];
+            for (int q = 0; q < p.nkb; ++q) {
+                const int meta = blk | (q << 4) | ((x == r0) << 8) | ((x + 1 == r1) << 9) | (tap << 16);
+                s_task[r0 * p.nkb + q * (r1 - r0) + (x - r0)] = make_int4(lo, hi, meta, 0);
+                if (x == r0) s_wtask[s_run[x] * p.nkb + q] = tap | (q << 16);
+            }
+        }
+        __syncthreads();
+
+        if (warp == 0) STAT_ADD(8, t_group);
+        STAT_T0(t_role);
+        if (warp < p.npw) {
+            // ---------------------------------------------------------- producer ----
+            const uint32_t slot_addr = a_base + (uint32_t)warp * SLOT_BYTES;
+            const uint32_t side_addr = side_base + (uint32_t)warp * SIDE_BYTES;
+            int32_t *side_meta = s_side + warp * SIDE_ROWS;
+            const uint32_t full_bar = smem_u32(&s_a_full[warp]), empty_bar = smem_u32(&s_a_empty[warp]);
+            bool ok_role = true;
+            // this warp's tiles: those whose launch-wide index a_n + t is congruent to the warp modulo npw
+            int t = (int)(((uint32_t)warp + (uint32_t)p.npw - a_n % (uint32_t)p.npw) % (uint32_t)p.npw);
+            uint32_t use = (a_n + (uint32_t)t) / (uint32_t)p.npw;  // times this warp's slot has been filled before
+            // Entries are fetched two batches ahead of the batch being issued (a batch = UNROLL entries
+            // per lane group), across tile boundaries: `ld_*` is the position of the next batch to fetch.
+            uint2 ent[UNROLL], ent_next[UNROLL], ent_far[UNROLL];
+            int ld_t = t, ld_e = 0, ld_hi = 0, ld_psh = 3;
+            auto fetch_batch = [&](uint2 (&dst)[UNROLL]) {
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) dst[u] = make_uint2(0xffffffffu, 0u);
+                if (ld_t >= a_total) return;
+                if (ld_e >= ld_hi) {  // first batch of tile ld_t
+                    const int4 k4 = s_task[ld_t];
+                    ld_e = k4.x, ld_hi = k4.y, ld_psh = piece_shift(pieces_of(p.inw, (k4.z >> 4) & 15));
+                }
+                load_entries(dst, p.entries, ld_e, ld_hi, ld_psh, lane);
+                ld_e += UNROLL * (32 >> ld_psh);
+                if (ld_e >= ld_hi) ld_t += p.npw, ld_e = 0, ld_hi = 0;
+            };
+            fetch_batch(ent);
+            fetch_batch(ent_next);
+            while (t < a_total && ok_role) {
+                const int4 tk = s_task[t];
+                const int lo = tk.x, hi = tk.y, q = (tk.z >> 4) & 15;
+                const int pieces = pieces_of(p.inw, q), psh = piece_shift(pieces);
+                const int piece = lane & ((1 << psh) - 1), sub = lane >> psh, subs = 32 >> psh;
+                const bool piece_ok = piece < pieces;
+                const uint32_t before_my_sub = (1u << (sub << psh)) - 1u;  // lanes of the lane groups before mine
+                const uint16_t *fcol = p.feat + q * 64 + piece * 8;
+                // the tensor core has finished reading this slot's previous tile
+                STAT_T0(t_w);
+                ok_role = mbar_wait_abortable(empty_bar, (use & 1u) ^ 1u, STATUS_BIT, p.status, abort_flag, p.wait_limit_ns);
+                ok_role = __all_sync(0xffffffffu, ok_role);
+                STAT_ADD(9, t_w);
+                if (!ok_role) break;
+                uint32_t present0 = 0u, present1 = 0u, present2 = 0u, present3 = 0u;  // rows of the slot that receive a feature row
+                int nside = 0;                            // side rows in use (uniform over the warp)
+                uint32_t maxpos = 0;
+                // The rows parked in the side buffer are added to their slot rows, one bucket position
+                // per round (rows of one position have distinct targets), after all copies have landed.
+                auto apply_side = [&]() {
+                    cp_async_commit();
+                    cp_async_wait<0>();
+                    __syncwarp();
+                    maxpos = __reduce_max_sync(0xffffffffu, maxpos);
+                    for (uint32_t r = 1; r <= maxpos; ++r) {
+                        for (int sr = sub; sr < nside; sr += subs) {
+                            const uint32_t meta = (uint32_t)side_meta[sr];
+                            if ((meta >> 8) == r && piece_ok) {
+                                const uint32_t row = meta & 127u;
+                                const uint32_t addr = slot_addr + row * 128 + (((uint32_t)piece ^ (row & 7u)) << 4);
+                                sts_v4(addr, add8(lds_v4(addr), lds_v4(side_addr + (uint32_t)sr * 128 + (uint32_t)piece * 16), p.fmt));
+                            }
+                        }
+                        __syncwarp();
+                    }
+                    nside = 0, maxpos = 0;
+                };
+                for (int e0 = lo; e0 < hi; e0 += UNROLL * subs) {
+                    fetch_batch(ent_far);
+#pragma unroll
+                    for (int u = 0; u < UNROLL; ++u) {
+                        const uint32_t x = ent[u].x;
+                        const bool valid = x != 0xffffffffu;
+                        const uint32_t pos = x >> 8, row = x & 127u;
+                        // further triplets of a bucket are parked in the side buffer: make room first
+                        const unsigned heads = __ballot_sync(0xffffffffu, valid && pos > 0 && piece == 0);
+                        if (nside + __popc(heads) > SIDE_ROWS) apply_side();
+                        if (valid) {
+                            const uint16_t *src = fcol + (int64_t)ent[u].y * p.inw;
+                            if (pos == 0) {  // first triplet of a (row, tap) bucket: straight into the row of the slot
+                                if (piece_ok) cp_async16(slot_addr + row * 128 + (((uint32_t)piece ^ (row & 7u)) << 4), src);
+                                const uint32_t bit = 1u << (row & 31u), word = row >> 5;
+                                present0 |= word == 0 ? bit : 0u, present1 |= word == 1 ? bit : 0u;
+                                present2 |= word == 2 ? bit : 0u, present3 |= word == 3 ? bit : 0u;
+                            } else {
+                                const int sr = nside + __popc(heads & before_my_sub);
+                                if (piece_ok) cp_async16(side_addr + (uint32_t)sr * 128 + (uint32_t)piece * 16, src);
+                                if (piece == 0) side_meta[sr] = (int32_t)x;
+                                maxpos = max(maxpos, pos);
+                            }
+                        }
+                        nside += __popc(heads);
+                    }
+#pragma unroll
+                    for (int u = 0; u < UNROLL; ++u) ent[u] = ent_next[u], ent_next[u] = ent_far[u];
+                }
+                // rows that receive nothing are zeroed (disjoint from the rows being copied into)
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const uint32_t got = __reduce_or_sync(0xffffffffu, w == 0 ? present0 : w == 1 ? present1 : w == 2 ? present2 : present3);
+                    for (int rr = sub; rr < 32; rr += subs)
+                        if (!((got >> rr) & 1u) && piece_ok) {
+                            const uint32_t row = (uint32_t)(w * 32 + rr);
+                            sts_v4(slot_addr + row * 128 + (((uint32_t)piece ^ (row & 7u)) << 4), make_uint4(0, 0, 0, 0));
+                        }
+                }
+                apply_side();
+                fence_async_smem();
+                mbar_arrive(full_bar);
+                t += p.npw, ++use;
+            }
+            STAT_ADD(10, t_role);
+            STAT_T0(t_epi);
+            // ---------------------------------------------------------- epilogue ----
+            if (ok_role && a_total > 0) {
+                ok_role = mbar_wait_abortable(smem_u32(&s_d_full), d_n & 1u, STATUS_BIT, p.status, abort_flag, p.wait_limit_ns);
+                ok_role = __all_sync(0xffffffffu, ok_role);
+            }
+            STAT_ADD(11, t_epi);
+            tc_fence_after();
+            const int teams = p.npw >> 2;
+            if (ok_role && warp < teams * 4) {
+                const int quarter = warp & 3, team = warp >> 2;
+                const int chunks = p.outw >> 4;  // units of 16 columns
+                for (int u = team; u < nb * chunks; u += teams) {
+                    const int blk = u / chunks, cc = u - blk * chunks;
+                    const int32_t row = p.perm[(int64_t)(b0 + blk) * ROWS + quarter * 32 + lane];
+                    const bool blk_has = s_tab[(blk + 1) * p.K] > s_tab[blk * p.K];
+                    float acc[16];
+                    if (blk_has) {
+                        tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)blk * p.col_stride + (uint32_t)cc * 16, acc);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) acc[c] = 0.f;
+                    }
+                    if (row >= 0) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(p.out + (int64_t)row * p.outw + cc * 16);
+                        uint4 o;
+                        o.x = pack2(acc[0], acc[1], p.fmt), o.y = pack2(acc[2], acc[3], p.fmt);
+                        o.z = pack2(acc[4], acc[5], p.fmt), o.w = pack2(acc[6], acc[7], p.fmt);
+                        dst[0] = o;
+                        o.x = pack2(acc[8], acc[9], p.fmt), o.y = pack2(acc[10], acc[11], p.fmt);
+                        o.z = pack2(acc[12], acc[13], p.fmt), o.w = pack2(acc[14], acc[15], p.fmt);
+                        dst[1] = o;
+                    }
+                }
+            }
+            tc_fence_before();
+            STAT_ADD(12, t_epi);
+        } else if (warp == p.npw) {
+            // --------------------------------------------------------------- MMA ----
+            if (lane == 0) {
+                uint32_t slot = a_n % (uint32_t)p.npw, use = a_n / (uint32_t)p.npw;
+                uint32_t wslot = w_n % (uint32_t)p.nw, wuse = w_n / (uint32_t)p.nw;
+                uint32_t started = 0;
+                bool ok_role = true;
+                // descriptors of slot 0 / contraction step 0; the address field counts 16-byte units, so
+                // another slot or step is an addition to the low word
+                const uint64_t a_desc0 = smem_desc(a_base, 16, 1024);
+                const uint64_t b_desc0 = p.transpose ? smem_desc(w_base, 16, 1024) : smem_desc(w_base, p.w_box_rows * 128, 1024);
+                const uint32_t b_step = p.transpose ? 2u : 128u;  // 32 bytes along a K-major row / 16 contraction rows of 128 bytes
+                const uint32_t w_slot16 = p.w_slot_bytes >> 4;
+                for (int t = 0; t < a_total; ++t) {
+                    const int meta = s_task[t].z;
+                    const int blk = meta & 15, q = (meta >> 4) & 15;
+                    if (meta & 256) {  // first tile of a weight slice: the slice has landed
+                        STAT_T0(t_w);
+                        ok_role = mbar_wait_abortable(smem_u32(&s_w_full[wslot]), wuse & 1u, STATUS_BIT, p.status, abort_flag,
+                                                      p.wait_limit_ns);
+                        if (!ok_role) break;
+                        if (!p.use_tma) fence_async_smem();
+                        STAT_ADD(13, t_w);
+                    }
+                    STAT_T0(t_a);
+                    ok_role = mbar_wait_abortable(smem_u32(&s_a_full[slot]), use & 1u, STATUS_BIT, p.status, abort_flag,
+                                                  p.wait_limit_ns);
+                    if (!ok_role) break;
+                    STAT_ADD(14, t_a);
+                    tc_fence_after();
+                    const uint64_t ad = a_desc0 + (uint64_t)(slot * (SLOT_BYTES >> 4));
+                    const uint64_t bd = b_desc0 + (uint64_t)(wslot * w_slot16);
+                    const int ksteps = min(64, p.inw - q * 64) >> 4;
+                    const uint32_t d_addr = tmem + (uint32_t)blk * p.col_stride;
+                    const uint32_t first = (q > 0 || ((started >> blk) & 1u)) ? 1u : 0u;
+                    STAT_T0(t_m);
+                    tc_mma(d_addr, ad, bd, idesc, first);
+                    for (int s = 1; s < ksteps; ++s) tc_mma(d_addr, ad + (uint64_t)(2 * s), bd + (uint64_t)(b_step * s), idesc, 1u);
+                    STAT_ADD(18, t_m);
+                    started |= 1u << blk;
+                    STAT_T0(t_c);
+                    tc_commit(smem_u32(&s_a_empty[slot]));
+                    if (++slot == (uint32_t)p.npw) slot = 0, ++use;
+                    if (meta & 512) {  // last tile of the weight slice: its slot is free once these MMAs are done
+                        tc_commit(smem_u32(&s_w_empty[wslot]));
+                        if (++wslot == (uint32_t)p.nw) wslot = 0, ++wuse;
+                    }
+                    STAT_ADD(19, t_c);
+                }
+                if (ok_role && a_total > 0) tc_commit(smem_u32(&s_d_full));
+                STAT_ADD(15, t_role);
+            }
+            __syncwarp();
+        } else {
+            // ------------------------------------------------------ weight loader ----
+            uint32_t wslot = w_n % (uint32_t)p.nw, wuse = w_n / (uint32_t)p.nw;
+            bool ok_role = true;
+            for (int wt = 0; wt < w_total && ok_role; ++wt) {
+                const int tap = s_wtask[wt] & 0xffff, q = s_wtask[wt] >> 16;
+                const uint32_t w_slot = w_base + wslot * p.w_slot_bytes, full = smem_u32(&s_w_full[wslot]);
+                STAT_T0(t_w);
+                ok_role = mbar_wait_abortable(smem_u32(&s_w_empty[wslot]), (wuse & 1u) ^ 1u, STATUS_BIT, p.status, abort_flag,
+                                              p.wait_limit_ns);
+                ok_role = __all_sync(0xffffffffu, ok_role);
+                STAT_ADD(16, t_w);
+                if (!ok_role) break;
+                if (p.use_tma) {
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(full, p.w_tx_bytes);
+                        if (p.transpose) {
+                            // contraction over m: the slice is the m-block q of all C rows of W[tap]
+                            tma_load_2d(w_slot, &tmap, q * 64, tap * p.C, full);
+                        } else {
+                            // contraction over c: rows [64q, 64q + box) of W[tap], one box per 64 output channels
+                            for (int mb = 0; mb * 64 < p.M; ++mb)
+                                tma_load_2d(w_slot + (uint32_t)mb * p.w_box_rows * 128, &tmap, mb * 64, tap * p.C + q * 64, full);
+                        }
+                    }
+                } else {
+                    const uint16_t *w = p.weight + (int64_t)tap * p.C * p.M;
+                    if (p.transpose) {
+                        // rows c = 0..C-1, the 64 m-channels of block q (fewer in a last partial block)
+                        const int cpr = min(8, (p.M - q * 64) >> 3);
+                        for (int e = lane; e < p.C * cpr; e += 32) {
+                            const int c = e / cpr, ch = e - c * cpr;
+                            cp_async16(w_slot + (uint32_t)c * 128 + (uint32_t)((ch ^ (c & 7)) << 4),
+                                       w + (int64_t)c * p.M + q * 64 + ch * 8);
+                        }
+                    } else {
+                        // rows c = 64q .. 64q + rows - 1, all M channels in 64-channel blocks
+                        const int rows = min(64, p.C - q * 64), cpr = p.M >> 3;
+                        for (int e = lane; e < rows * cpr; e += 32) {
+                            const int c = e / cpr, ch = e - c * cpr;
+                            cp_async16(w_slot + (uint32_t)(ch >> 3) * p.w_box_rows * 128 + (uint32_t)c * 128 +
+                                           (uint32_t)(((ch & 7) ^ (c & 7)) << 4),
+                                       w + (int64_t)(q * 64 + c) * p.M + ch * 8);
+                        }
+                    }
+                    cp_async_mbar_arrive(full);
+                }
+                if (++wslot == (uint32_t)p.nw) wslot = 0, ++wuse;
+            }
+        }
+        if (warp == 0) STAT_ADD(17, t_group);
+        // counters advance identically in every role
+        a_n += (uint32_t)a_total;
+        w_n += (uint32_t)w_total;
+        d_n += a_total > 0 ? 1u : 0u;
+        __syncthreads();
+        if (s_abort) break;
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, p.ncols);
+    // the last CTA to finish re-arms the ticket counter for the next launch
+    if (tid == 0) {
+        __threadfence();
+        const uint32_t done = atomicAdd(&p.ctrl[CTRL_DONE], 1u);
+        if (done == gridDim.x - 1) {
+            p.ctrl[CTRL_TICKET] = 0u;
+            p.ctrl[CTRL_DONE] = 0u;
+            __threadfence();
+        }
+    }
+}
+
+// A single thread waits on an mbarrier that nothing arrives at: the bounded wait runs out,
+// raises `flag` in the status word and the kernel returns.
+__global__ void wait_runs_out_kernel(unsigned int *status, unsigned flag, uint64_t limit_ns) {
+    __shared__ uint64_t s_bar;
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&s_bar), 1);
+        fence_mbar_init();
+        s_abort = 0;
+        mbar_wait_abortable(smem_u32(&s_bar), 0u, flag, status, &s_abort, limit_ns);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point table (the library does not
+// link against libcuda); null when the driver does not offer it.
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+        else
+            (void)cudaGetLastError();
+    }
+    return fn;
+}
+
+unsigned int *status_word() {
+    static unsigned int *ptr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    if (!ptr[dev & 63] && device_status_address(&ptr[dev & 63]) != PCX_OK) return nullptr;
+    return ptr[dev & 63];
+}
+
+uint64_t wait_limit() {
+    static uint64_t v = 0;
+    if (!v) {
+        const char *e = getenv("PCX_WAIT_LIMIT_NS");
+        v = e ? strtoull(e, nullptr, 10) : 0;
+        if (!v) v = WAIT_LIMIT_NS;
+    }
+    return v;
+}
+
+bool plan_sizes_ok(int64_t T, int64_t n_out, int K, int G) {
+    if (T < 0 || T > INT32_MAX || n_out <= 0 || n_out > INT32_MAX || K <= 0 || K > MAX_TAPS) return false;
+    if (G < 1 || G > MAX_GROUP) return false;
+    const int64_t nblocks = (n_out + ROWS - 1) / ROWS;
+    return nblocks * K * ROWS <= ((int64_t)1 << 32) && nblocks * K < INT32_MAX;
+}
+
+}  // namespace
+}  // namespace pcx
+
+using namespace pcx;
+
+extern "C" {
+
+int pcx_mvmr_plan_group_blocks(int out_width) {
+    if (out_width <= 0 || out_width > 256) return 0;
+    const int stride = (out_width + 31) / 32 * 32;
+    // up to 64 channels: four accumulators in half of the tensor memory (two CTAs per SM);
+    // 128 channels: two; 256 channels: two accumulators fill the tensor memory of one CTA per SM
+    int g = stride <= 64 ? 4 : 2;
+    if (const char *e = getenv("PCX_OS_GROUP")) {
+        const int want = atoi(e);
+        if (want >= 1 && want <= MAX_GROUP && want * stride <= 512) g = want;
+    }
+    return g;
+}
+
+size_t pcx_mvmr_plan_bytes(int64_t T, int64_t n_out, int K, int group_blocks) {
+    if (!plan_sizes_ok(T, n_out, K, group_blocks)) return 0;
+    return carve_plan(nullptr, T, n_out, K, group_blocks, nullptr);
+}
+
+size_t pcx_mvmr_plan_workspace_bytes(int64_t T, int64_t n_out, int K, int group_blocks) {
+    if (!plan_sizes_ok(T, n_out, K, group_blocks)) return 0;
+    return carve_build(nullptr, T, n_out, K, group_blocks, nullptr);
+}
+
+int pcx_mvmr_plan_build(const int32_t *d_scatter, const int32_t *d_gather, const int64_t *d_seg_offs, int64_t T, int K,
+                        int64_t n_out, int group_blocks, void *d_plan, size_t plan_bytes, void *d_ws, size_t ws_bytes,
+                        void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int G = group_blocks;
+    if (!plan_sizes_ok(T, n_out, K, G))
+        PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr_plan_build: sizes out of range (T=%lld n_out=%lld K=%d group=%d)", (long long)T,
+                 (long long)n_out, K, G);
+    if (!d_plan || !d_ws || (T > 0 && (!d_scatter || !d_gather || !d_seg_offs)))
+        PCX_FAIL(PCX_E_ARG, "pcx_mvmr_plan_build: null pointer");
+    if ((uintptr_t)d_plan % 256 || (uintptr_t)d_ws % 256)
+        PCX_FAIL(PCX_E_ALIGN, "pcx_mvmr_plan_build: plan and workspace must be 256-byte aligned");
+    PlanView pv;
+    BuildWs w;
+    const size_t need_plan = carve_plan(d_plan, T, n_out, K, G, &pv), need_ws = carve_build(d_ws, T, n_out, K, G, &w);
+    if (plan_bytes < need_plan) PCX_FAIL(PCX_E_CAPACITY, "pcx_mvmr_plan_build: plan buffer %zu < %zu bytes", plan_bytes, need_plan);
+    if (ws_bytes < need_ws) PCX_FAIL(PCX_E_CAPACITY, "pcx_mvmr_plan_build: workspace %zu < %zu bytes", ws_bytes, need_ws);
+    const int TPB = 256;
+    const int64_t n_tiles = pv.nblocks * K, n_pad = pv.nblocks * ROWS;
+    auto blocks = [&](int64_t n) { return (unsigned)((n + TPB - 1) / TPB); };
+    const int64_t init_n = std::max<int64_t>(std::max<int64_t>(n_out, n_tiles + 1), CTRL_WORDS);
+    plan_init_kernel<<<blocks(init_n), TPB, 0, stream>>>(n_out, w.sig, w.row, w.tile_cnt, n_tiles, pv.ctrl, G);
+    PCX_LAUNCH_CHECK();
+    size_t bytes = w.cub_bytes;
+    if (T > 0) {
+        plan_sig_kernel<<<blocks(T), TPB, 0, stream>>>(d_scatter, d_seg_offs, T, K, w.sig);
+        PCX_LAUNCH_CHECK();
+    }
+    // rows by signature (stable: rows of equal signature keep their order)
+    PCX_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, bytes, w.sig, w.sig_sorted, w.row, w.row_sorted, (int)n_out, 0,
+                                             std::min(K, 32), stream));
+    plan_rank_kernel<<<blocks(n_pad), TPB, 0, stream>>>(w.row_sorted, n_out, n_pad, w.rank, pv.perm);
+    PCX_LAUNCH_CHECK();
+    if (T > 0) {
+        plan_keys_kernel<<<blocks(T), TPB, 0, stream>>>(d_scatter, d_gather, d_seg_offs, w.rank, T, K, w.key, w.val, w.tile_cnt);
+        PCX_LAUNCH_CHECK();
+        bytes = w.cub_bytes;
+        PCX_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, bytes, w.key, w.key_sorted, w.val, w.val_sorted, (int)T, 0,
+                                                 std::min(32, bits_of(n_tiles * ROWS)), stream));
+    }
+    bytes = w.cub_bytes;
+    PCX_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, bytes, w.tile_cnt, pv.tile_offs, (int)(n_tiles + 1), stream));
+    if (T > 0) {
+        plan_entries_kernel<<<blocks(T), TPB, 0, stream>>>(w.key_sorted, w.val_sorted, T, pv.entries);
+        PCX_LAUNCH_CHECK();
+    }
+    plan_cost_kernel<<<blocks(pv.ngroups), TPB, 0, stream>>>(pv.tile_offs, pv.nblocks, K, G, pv.ngroups, w.cost, w.gid);
+    PCX_LAUNCH_CHECK();
+    bytes = w.cub_bytes;
+    PCX_CUDA(cub::DeviceRadixSort::SortPairsDescending(w.cub_tmp, bytes, w.cost, w.cost_sorted, w.gid, pv.group_order,
+                                                       (int)pv.ngroups, 0, bits_of((int64_t)G * K + 2), stream));
+    return PCX_OK;
+}
+
+int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan, size_t plan_bytes, void *d_out, int64_t T,
+                     int64_t n_feat, int64_t n_out, int K, int C, int M, int transpose, int dtype, int group_blocks,
+                     void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int G = group_blocks;
+    if (dtype != PCX_F16 && dtype != PCX_BF16) PCX_FAIL(PCX_E_DTYPE, "pcx_mvmr_planned: fp16 or bf16 only (dtype %d)", dtype);
+    if (C <= 0 || M <= 0 || n_feat < 0) PCX_FAIL(PCX_E_ARG, "pcx_mvmr_planned: bad sizes");
+    if (!plan_sizes_ok(T, n_out, K, G))
+        PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr_planned: sizes out of range (T=%lld n_out=%lld K=%d group=%d)", (long long)T,
+                 (long long)n_out, K, G);
+    const int inw = transpose ? M : C, outw = transpose ? C : M;
+    if (inw % 16 || outw % 16 || inw > 1024 || outw > 256)
+        PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr_planned: channel counts must be multiples of 16, output width at most 256 (C=%d M=%d)", C, M);
+    if (!d_weight || !d_plan || !d_out || (T > 0 && !d_feat)) PCX_FAIL(PCX_E_ARG, "pcx_mvmr_planned: null pointer");
+    if ((uintptr_t)d_weight % 16 || (uintptr_t)d_feat % 16 || (uintptr_t)d_out % 16 || (uintptr_t)d_plan % 256)
+        PCX_FAIL(PCX_E_ALIGN, "pcx_mvmr_planned: weight, features and output must be 16-byte aligned, the plan 256-byte aligned");
+    PlanView pv;
+    const size_t need_plan = carve_plan(d_plan, T, n_out, K, G, &pv);
+    if (plan_bytes < need_plan) PCX_FAIL(PCX_E_CAPACITY, "pcx_mvmr_planned: plan buffer %zu < %zu bytes", plan_bytes, need_plan);
+
+    OsParams p = {};
+    p.feat = (const uint16_t *)d_feat, p.out = (uint16_t *)d_out, p.weight = (const uint16_t *)d_weight;
+    p.perm = pv.perm, p.tile_offs = pv.tile_offs, p.group_order = pv.group_order, p.entries = pv.entries, p.ctrl = pv.ctrl;
+    p.status = status_word();
+    if (!p.status) PCX_FAIL(PCX_E_LAUNCH, "pcx_mvmr_planned: no device status word");
+    p.K = K, p.C = C, p.M = M, p.transpose = transpose ? 1 : 0, p.fmt = dtype == PCX_BF16 ? 1 : 0;
+    p.inw = inw, p.outw = outw, p.nkb = (inw + 63) / 64, p.G = G;
+    p.ngroups = (int)pv.ngroups, p.nblocks = (int)pv.nblocks;
+    p.col_stride = (uint32_t)((outw + 31) / 32 * 32);
+    if ((uint32_t)G * p.col_stride > 512u)
+        PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr_planned: %d blocks of %d columns exceed the 512 TMEM columns", G, (int)p.col_stride);
+    p.ncols = 32;
+    while (p.ncols < (uint32_t)G * p.col_stride) p.ncols <<= 1;
+    p.w_box_rows = (uint32_t)(transpose ? C : std::min(64, C));
+    const uint32_t w_image = transpose ? (uint32_t)C * 128u : (uint32_t)((M + 63) / 64) * p.w_box_rows * 128u;
+    p.w_slot_bytes = (uint32_t)align_up(w_image, 1024);
+    p.w_tx_bytes = w_image;
+    p.wait_limit_ns = wait_limit();
+    p.use_tma = (M % 64 == 0) && encode_tiled() != nullptr;
+    if (const char *e = getenv("PCX_OS_WTMA")) p.use_tma = p.use_tma && atoi(e) != 0;
+
+    CUtensorMap tmap;
+    memset(&tmap, 0, sizeof(tmap));
+    if (p.use_tma) {
+        const cuuint64_t gdim[2] = {(cuuint64_t)M, (cuuint64_t)K * (cuuint64_t)C};
+        const cuuint64_t gstride[1] = {(cuuint64_t)M * 2};
+        const cuuint32_t box[2] = {64u, p.w_box_rows};
+        const cuuint32_t estride[2] = {1u, 1u};
+        const CUresult r = encode_tiled()(&tmap, dtype == PCX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                          2, const_cast<void *>(d_weight), gdim, gstride, box, estride,
+                                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) PCX_FAIL(PCX_E_LAUNCH, "pcx_mvmr_planned: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    }
+
+    // Two CTAs share an SM when their accumulators fit half of the tensor memory: while one
+    // writes its output rows or sets up its next group, the other keeps the tensor core and the
+    // gathers going, and two threads issue MMAs.  Shared memory per CTA: A slots and side
+    // buffers (one each per producer warp), weight slots, the group's task tables.
+    int ctas = p.ncols <= 256 ? 2 : 1;
+    if (const char *e = getenv("PCX_OS_CTAS")) ctas = (atoi(e) == 1 || p.ncols > 256) ? 1 : 2;
+    const size_t nkb = (size_t)p.nkb;
+    const size_t table_fixed = align_up((size_t)G * K * nkb * 16 + ((size_t)G * K * 3 + 1 + (size_t)K * nkb) * 4, 16);
+    const size_t per_warp = SLOT_BYTES + SIDE_BYTES + SIDE_ROWS * 4, static_smem = 512;
+    int npw = 0, nw = 0;
+    for (; ctas >= 1 && !npw; --ctas) {
+        const size_t budget = (size_t)232448 / ctas - 1024 - static_smem - 1024;
+        const int top = ctas == 2 ? 5 : MAX_NPW;
+        for (int a = top; a >= 4 && !npw; --a)
+            for (int b = (ctas == 2 ? 3 : MAX_NW); b >= 2 && !npw; --b)
+                if ((size_t)a * per_warp + (size_t)b * p.w_slot_bytes + table_fixed <= budget) npw = a, nw = b;
+        if (npw) break;
+    }
+    if (!npw) PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr_planned: shared memory does not fit (K=%d C=%d M=%d group=%d)", K, C, M, G);
+    if (const char *e = getenv("PCX_OS_WARPS")) {
+        const int want = atoi(e);
+        if (want >= 4 && want <= npw) npw = want;
+    }
+    if (const char *e = getenv("PCX_OS_WSLOTS")) {
+        const int want = atoi(e);
+        if (want >= 2 && want <= nw) nw = want;
+    }
+    p.npw = npw, p.nw = nw;
+    const size_t smem = 1024 + (size_t)npw * per_warp + (size_t)nw * p.w_slot_bytes + table_fixed;
+    static int granted[64] = {};
+    int dev = 0;
+    PCX_CUDA(cudaGetDevice(&dev));
+    if ((int)smem > granted[dev & 63]) {
+        PCX_CUDA(cudaFuncSetAttribute(mvmr_os_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PCX_CUDA(cudaFuncSetAttribute(mvmr_os_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        granted[dev & 63] = (int)smem;
+    }
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(pv.ngroups, (int64_t)ctas * num_sms()));
+    prof_begin(transpose ? "mvmr_os_kernel(dgrad)" : "mvmr_os_kernel(fwd)", stream);
+    mvmr_os_kernel<<<grid, (unsigned)(npw + 2) * 32, smem, stream>>>(tmap, p);
+    prof_end(stream);
+    PCX_LAUNCH_CHECK();
+    return PCX_OK;
+}
+
+int pcx_debug_wait_runs_out(unsigned long long limit_ns, void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (limit_ns == 0 || limit_ns > 100000000ull) PCX_FAIL(PCX_E_ARG, "pcx_debug_wait_runs_out: limit must be within (0, 100 ms]");
+    unsigned int *status = status_word();
+    if (!status) PCX_FAIL(PCX_E_LAUNCH, "pcx_debug_wait_runs_out: no device status word");
+    wait_runs_out_kernel<<<1, 32, 0, stream>>>(status, 8u, (uint64_t)limit_ns);
+    PCX_LAUNCH_CHECK();
+    return PCX_OK;
+}
+
+}  // extern "C"
