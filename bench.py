@@ -23,6 +23,11 @@ Printed JSON (rank 0, one line):
             in and its own results out; no L2 flush is needed, nothing is reused)
   roofline  the dominant kernel's algorithmic bytes / its event-timed duration
             against the measured HBM copy bandwidth
+  sustained the same resident step repeated back to back for at least two seconds
+            (no L2 flush in between), so that the clock sampler sees the GPU under load
+  backbone  one training step of the residual U-Net (8 scenes per rank, geometry rebuilt
+            every step, gradient all-reduce) with its split into geometry / convolution
+            kernels / norm kernels / all-reduce
   cpu_baseline  the reference's own CPU operators timed on a bounded spatial
             crop of the same scene (single-threaded by construction)
 
@@ -52,6 +57,7 @@ TAP_GRID = 0.02
 KERNEL = 3
 METRIC = "pointconv3d_fwd_dgrad_wgrad_throughput"
 UNIT = "Gtriplets/s"
+CPU_CROP_POINTS = 20_000   # sub-scene the CPU arms are timed on (the reference's loops run ~0.1 Mtriplets/s)
 WORKLOAD = ("indoor150k_c64_bf16: PointConv3d fwd+dgrad+wgrad, 150000-point synthetic indoor scene, "
             "R=5cm, 27 taps, C_in=C_out=64 bf16, fp32 accumulate")
 
@@ -204,8 +210,7 @@ def cpu_geometry_ms(seed, crop_points):
 def run_reference(args, rank):
     if rank != 0:
         return
-    crop = 8000
-    d = cpu_reference_step_inputs(0, crop)
+    d = cpu_reference_step_inputs(0, CPU_CROP_POINTS)
     T = len(d["i"])
     for _ in range(args.warmup):
         cpu_reference_step(d)
@@ -348,7 +353,22 @@ def run_ours(args, rank, local_rank, world):
     step_ms = [a.elapsed_time(b) for a, b in ev]
     total_ms = float(sum(step_ms))
 
-    e2e_ms, h2d, d2h = 0.0, 0, 0
+    # ---- sustained leg: the same step back to back for at least two seconds, so that the clock
+    # sampler sees the GPU under load (the scene's working set stays in the L2: no flush)
+    sustained = None
+    if not args.resident_only:
+        est = max(total_ms / args.steps, 1e-3)
+        n_sus = int(min(max(2000.0 / est, 10), 200000))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        s0.record()
+        for _ in range(n_sus):
+            step_resident()
+        s1.record()
+        barrier()
+        sustained = {"steps": n_sus, "ms_per_step": s0.elapsed_time(s1) / n_sus, "l2": "not flushed"}
+
+    e2e_ms, h2d, d2h, copy_floor_ms = 0.0, 0, 0, 0.0
     if not args.resident_only:
         # ---- e2e: public operator API, host buffers in, results out, inside the timed region
         x_h = x.cpu().pin_memory()
@@ -428,18 +448,54 @@ def run_ours(args, rank, local_rank, world):
         e2e_ms = float(e2e_start.elapsed_time(e2e_stop))
         h2d = (x_h.numel() + go_h.numel()) * 2
         d2h = (out_h.numel() + gx_h.numel() + gw_h.numel()) * 2
+
+        # copy-only floor of the same leg: the same bytes in and out per step, both directions
+        # running side by side on their streams, no compute
+        out_d, gx_d, gw_d = torch.empty_like(go), torch.empty_like(x), torch.empty_like(w)
+
+        def run_copies(steps):
+            s_in.wait_stream(main)
+            s_out.wait_stream(main)
+            for k in range(steps):
+                with torch.cuda.stream(s_in):
+                    stage_x[k & 1].data.copy_(x_h, non_blocking=True)
+                    stage_go[k & 1].copy_(go_h, non_blocking=True)
+                with torch.cuda.stream(s_out):
+                    out_h.copy_(out_d, non_blocking=True)
+                    gx_h.copy_(gx_d, non_blocking=True)
+                    gw_h.copy_(gw_d, non_blocking=True)
+            main.wait_stream(s_in)
+            main.wait_stream(s_out)
+
+        run_copies(2)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        run_copies(args.steps)
+        c1.record()
+        barrier()
+        copy_floor_ms = float(c0.elapsed_time(c1)) / args.steps
     clock_info = clocks.stop()
 
     # ---- reduce over ranks: max time, sum of triplets
-    stats = torch.tensor([total_ms, e2e_ms, float(T)], dtype=torch.float64, device=dev)
+    sus_ms = sustained["ms_per_step"] if sustained else 0.0
+    stats = torch.tensor([total_ms, e2e_ms, float(T), sus_ms, copy_floor_ms], dtype=torch.float64, device=dev)
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        total_ms, e2e_ms, T_all = float(mx[0]), float(mx[1]), float(sm[2])
+        total_ms, e2e_ms, T_all, sus_ms, copy_floor_ms = float(mx[0]), float(mx[1]), float(sm[2]), float(mx[3]), float(mx[4])
     else:
         T_all = float(T)
+    if sustained:
+        sustained["ms_per_step"] = sus_ms
+        sustained["value"] = T_all / (sus_ms * 1e-3) / 1e9
+
+    # ---- backbone training step (the second half of the metric: ResNet-18-style step ms at N GPUs)
+    backbone = None
+    if not args.resident_only and not args.no_backbone:
+        backbone = backbone_leg(args, rank, local_rank, world, dev, steps=min(args.steps, 10))
 
     if rank == 0:
         per_kernel = {}
@@ -449,20 +505,14 @@ def run_ours(args, rank, local_rank, world):
         hbm, peak_kind = _peaks()
         balg = algorithmic_bytes(T, n, n, C, M, K)
         label_to_pass = {"mvmr_tc_kernel(fwd)": "fwd", "mvmr_tc_kernel(dgrad)": "dgrad", "vvor_tc_kernel": "wgrad",
+                         "mvmr_os_kernel(fwd)": "fwd", "mvmr_os_kernel(dgrad)": "dgrad",
                          "mvmr_sorted_kernel(fwd)": "fwd", "mvmr_sorted_kernel(dgrad)": "dgrad",
                          "vvor_sorted_kernel": "wgrad"}
-        # dense neighbourhoods (large --points) take the dense-tap schedule, whose gather-sum kernel
-        # serves both the forward and the input gradient: it is reported under the forward's bytes
-        label_to_pass["idx_reduce_kernel"] = "fwd"
         avg = {name: ms for name, ms in avg.items() if name in label_to_pass}
         dominant = max(avg, key=avg.get)
         dom_pass = label_to_pass[dominant]
         achieved = balg[dom_pass] / (avg[dominant] * 1e-3) / 1e9
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised
-        # in profiles/mvmr_tc_kernel_indoor150k_c64.md (headline workload only)
-        traffic = None
-        if dominant.startswith("mvmr_tc_kernel") and (args.points, C) == (N_POINTS, CHANNELS):
-            traffic = 65.4e6
+        traffic = None   # DRAM bytes per launch come from a profiler capture, not from this run
         roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm, "unit": "GB/s",
                     "frac": achieved / hbm, "peak_source": peak_kind, "traffic": traffic,
                     "algorithmic_bytes": balg[dom_pass], "kernel_ms": avg[dominant],
@@ -483,12 +533,15 @@ def run_ours(args, rank, local_rank, world):
             "tflops": 6.0 * T_all * C * M / (per_step_ms * 1e-3) / 1e12,
             "roofline": roofline,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": None if args.resident_only else e2e_ms / args.steps},
+                    "ms_per_step": None if args.resident_only else e2e_ms / args.steps,
+                    "copy_floor_ms": None if args.resident_only else copy_floor_ms},
+            "sustained": sustained,
+            "backbone": backbone,
             "gpu_launches": int(launches),
             "clocks": clock_info,
         }
         if world == 1 and not args.resident_only:
-            d = cpu_reference_step_inputs(0, 40000)
+            d = cpu_reference_step_inputs(0, CPU_CROP_POINTS)
             dt, kind = cpu_reference_step(d)
             dt2, _ = cpu_reference_step(d)
             dt = min(dt, dt2)
@@ -501,7 +554,7 @@ def run_ours(args, rank, local_rank, world):
             dt_torch = min(dt_torch, cpu_torch_step(d)[0])
             line["cpu_baseline"]["torch_all_cores"] = {"value": len(d["i"]) / dt_torch / 1e9, "unit": UNIT,
                                                        "threads": threads, "kind": "fp32 gather-matmul-index_add"}
-            line["cpu_baseline"]["geometry_cpu_ms"] = cpu_geometry_ms(0, 40000)
+            line["cpu_baseline"]["geometry_cpu_ms"] = cpu_geometry_ms(0, CPU_CROP_POINTS)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -578,23 +631,15 @@ def run_block_ops(args, local_rank):
                       "peak": hbm, "peak_source": peak_kind, "passes": out}), flush=True)
 
 
-def run_backbone(args, rank, local_rank, world):
-    """Secondary workload (configs 4 / 5 of the survey): one training step of the residual U-Net
-    backbone -- geometry, forward, cross-entropy, backward, all-reduce of the parameter gradients
-    (optimizer excluded) -- on 8 synthetic indoor scenes per rank (weak scaling).  One JSON line."""
+def backbone_setup(args, rank, world, dev):
+    """Model, inputs and the step function of the backbone workload (configs 4 / 5 of the survey)."""
     import torch
-    import torch.distributed as dist
     import torch.nn.functional as F
 
-    from pointelligence_b200 import _cabi
     from pointelligence_b200.backbone import ResUNet
     from pointelligence_b200.dist import allreduce_gradients
     from pointelligence_b200.synthetic import indoor_scene, ragged_batch
 
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     if args.scene == "lidar":
         # config 5 stand-in: a global batch of 16 spinning-LiDAR sweeps split over the ranks,
         # de-duplicated on the 5 cm grid the model runs on
@@ -623,36 +668,105 @@ def run_backbone(args, rank, local_rank, world):
     model = ResUNet(in_channels=3, num_classes=20).to(dev)
     params = [p for p in model.parameters()]
 
-    def step():
+    def step(reduce=True):
         for p in params:
             p.grad = None
         logits = model(feat, pts, inds, lens, grid)
         loss = F.cross_entropy(logits.float(), labels)
         loss.backward()
-        if world > 1:
+        if world > 1 and reduce:
             allreduce_gradients(params)
         return loss
+
+    return step, params, n, scene_desc
+
+
+def backbone_split(step, params, world):
+    """One instrumented step: where its time goes.  Geometry = wall clock of the library's two
+    geometry entry points (each ends with a host hand-over, so the wall clock is the device time
+    plus the hand-over); convolution = the library's event timer around the MVMR / VVOR kernels;
+    norm = CUDA events around the fused layer-norm calls; all-reduce = CUDA events around it."""
+    import torch
+
+    from pointelligence_b200 import _cabi
+    from pointelligence_b200.dist import allreduce_gradients
+
+    wall = {"geometry": 0.0}
+    norm_events = []
+    originals = {name: getattr(_cabi, name) for name in
+                 ("radius_search", "grid_sample_center_nearest", "ragged_layer_norm", "ragged_layer_norm_backward")}
+
+    def timed_wall(fn):
+        def inner(*a, **kw):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            out = fn(*a, **kw)
+            torch.cuda.synchronize()
+            wall["geometry"] += (time.perf_counter() - t0) * 1e3
+            return out
+        return inner
+
+    def timed_events(fn):
+        def inner(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a, **kw)
+            e1.record()
+            norm_events.append((e0, e1))
+            return out
+        return inner
+
+    try:
+        _cabi.radius_search = timed_wall(originals["radius_search"])
+        _cabi.grid_sample_center_nearest = timed_wall(originals["grid_sample_center_nearest"])
+        _cabi.ragged_layer_norm = timed_events(originals["ragged_layer_norm"])
+        _cabi.ragged_layer_norm_backward = timed_events(originals["ragged_layer_norm_backward"])
+        _cabi.profile_enable(True)
+        t0, t1, t2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        torch.cuda.synchronize()
+        t0.record()
+        step(reduce=False)
+        t1.record()
+        if world > 1:
+            allreduce_gradients(params)
+        t2.record()
+        torch.cuda.synchronize()
+        records = _cabi.profile_records()
+    finally:
+        _cabi.profile_enable(False)
+        for name, fn in originals.items():
+            setattr(_cabi, name, fn)
+    conv = sum(ms for _, ms in records)
+    norm = sum(a.elapsed_time(b) for a, b in norm_events)
+    total = t0.elapsed_time(t2)
+    return {"instrumented_step_ms": total, "geometry_ms": wall["geometry"], "conv_kernels_ms": conv,
+            "norm_kernels_ms": norm, "allreduce_ms": t1.elapsed_time(t2),
+            "other_ms": total - wall["geometry"] - conv - norm - t1.elapsed_time(t2),
+            "note": "the instrumented step synchronises around every geometry call, so it is slower than ms_per_step"}
+
+
+def backbone_leg(args, rank, local_rank, world, dev, steps):
+    """Times the backbone training step inside the default run; returns the `backbone` object."""
+    import torch
+    import torch.distributed as dist
+
+    step, params, n, scene_desc = backbone_setup(args, rank, world, dev)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        loss = step()
+    for _ in range(3):
+        step()
     barrier()
-    clocks = ClockSampler(local_rank, enabled=(rank == 0))
-    clocks.start()
-    _cabi.launch_count(reset=True)
     a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
     a.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         loss = step()
     z.record()
     barrier()
-    clock_info = clocks.stop()
-    launches = _cabi.launch_count()
+    split = backbone_split(step, params, world)
     stats = torch.tensor([a.elapsed_time(z), float(n)], dtype=torch.float64, device=dev)
     if world > 1:
         mx, sm = stats.clone(), stats.clone()
@@ -661,18 +775,45 @@ def run_backbone(args, rank, local_rank, world):
         total_ms, n_all = float(mx[0]), float(sm[1])
     else:
         total_ms, n_all = float(stats[0]), float(n)
+    ms = total_ms / steps
+    return {"metric": "resunet_train_step", "ms_per_step": ms, "value": n_all / (ms * 1e-3) / 1e6, "unit": "Mpoints/s",
+            "steps": steps, "warmup": 3, "scaling": "weak", "points_rank0": n,
+            "parameters": int(sum(p.numel() for p in params)), "loss": float(loss.detach()),
+            "workload": f"ResUNet 32/64/128/256, BasicBlock x2 per stage, {scene_desc}, fwd + CE + bwd + gradient "
+                        "all-reduce, geometry rebuilt every step, optimizer excluded",
+            "split_rank0": split}
+
+
+def run_backbone(args, rank, local_rank, world):
+    """Secondary workload (configs 4 / 5 of the survey): one training step of the residual U-Net
+    backbone -- geometry, forward, cross-entropy, backward, all-reduce of the parameter gradients
+    (optimizer excluded) -- on 8 synthetic indoor scenes per rank (weak scaling).  One JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    from pointelligence_b200 import _cabi
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    clocks = ClockSampler(local_rank, enabled=(rank == 0))
+    clocks.start()
+    _cabi.launch_count(reset=True)
+    leg = backbone_leg(args, rank, local_rank, world, dev, steps=args.steps)
+    clock_info = clocks.stop()
+    launches = _cabi.launch_count()
     if rank == 0:
-        ms = total_ms / args.steps
         print(json.dumps({
-            "metric": "resunet_train_step_throughput", "value": n_all / (ms * 1e-3) / 1e6, "unit": "Mpoints/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "metric": "resunet_train_step_throughput", "value": leg["value"], "unit": "Mpoints/s",
+            "n_gpus": world, "steps": args.steps, "warmup": 3, "ms_per_step": leg["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"ResUNet 32/64/128/256, BasicBlock x2 per stage, {scene_desc}, "
-                                   "fwd + CE + bwd + gradient all-reduce, geometry rebuilt every step",
-                       "points_rank0": n, "parameters": int(sum(p.numel() for p in params)),
+            "config": {"workload": leg["workload"], "points_rank0": leg["points_rank0"],
+                       "parameters": leg["parameters"],
                        "l2": "working set of a step (GBs of activations) exceeds the L2",
                        "collective": "bucketed all-reduce of parameter gradients" if world > 1 else "none"},
-            "loss": float(loss.detach()), "gpu_launches": int(launches), "clocks": clock_info}), flush=True)
+            "split_rank0": leg["split_rank0"],
+            "loss": leg["loss"], "gpu_launches": int(launches), "clocks": clock_info}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -699,6 +840,8 @@ def main():
     ap.add_argument("--scene-max", type=int, default=200000, help="backbone workload: largest scene")
     ap.add_argument("--allreduce", default="overlap", choices=["serial", "overlap"],
                     help="N > 1: all-reduce of dW after the input gradient (serial) or beside it (overlap)")
+    ap.add_argument("--no-backbone", action="store_true",
+                    help="conv workload: leave the backbone training step out of the run")
     ap.add_argument("--resident-only", action="store_true",
                     help="skip the host-buffer and CPU legs (for profiler captures of the kernels)")
     args = ap.parse_args()

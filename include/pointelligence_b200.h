@@ -129,8 +129,11 @@ int pcx_mvmr(const void *d_weight, const void *d_feat, const int32_t *d_gather,
  *                 launches that use the same plan must not overlap on the GPU
  *   limits        K <= 512, channel counts multiples of 16, out_width <= 256,
  *                 T < 2^31, ceil(n_out / 128) * K * 128 <= 2^32
- * Several triplets of one (row, tap) bucket are summed in the feature type
- * before they are multiplied (one extra rounding per added row).
+ * The feature rows of a (row, tap) bucket with several triplets are summed
+ * first (fp32 sum, one rounding to the feature type) into the workspace, by a
+ * small kernel in front of the main one: pcx_mvmr_plan_multi_buckets reads the
+ * number of such buckets back from a built plan (it synchronises `stream`),
+ * pcx_mvmr_planned_workspace_bytes gives the workspace size for it.
  */
 int pcx_mvmr_plan_group_blocks(int out_width);
 size_t pcx_mvmr_plan_bytes(int64_t T, int64_t n_out, int K, int group_blocks);
@@ -141,10 +144,14 @@ int pcx_mvmr_plan_build(const int32_t *d_scatter, const int32_t *d_gather,
                         int64_t n_out, int group_blocks, void *d_plan,
                         size_t plan_bytes, void *d_ws, size_t ws_bytes,
                         void *stream);
+int pcx_mvmr_plan_multi_buckets(const void *d_plan, int64_t *h_count,
+                                void *stream);
+size_t pcx_mvmr_planned_workspace_bytes(int64_t multi_buckets, int in_width);
 int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan,
                      size_t plan_bytes, void *d_out, int64_t T, int64_t n_feat,
                      int64_t n_out, int K, int C, int M, int transpose,
-                     int dtype, int group_blocks, void *stream);
+                     int dtype, int group_blocks, int64_t multi_buckets,
+                     void *d_ws, size_t ws_bytes, void *stream);
 
 /* Launches one thread that waits on a barrier nothing arrives at: the bounded
  * wait gives up after limit_ns (at most 100 ms), sets bit 8 of the device
@@ -191,24 +198,6 @@ int pcx_vvor_static_scratch(const void *d_a, const int32_t *d_a_idx, const void 
                             void *d_out, int64_t T, int64_t n_a, int64_t n_b,
                             int64_t n_o, int G, int Ma, int Cb, int dtype,
                             void *stream);
-
-/* ------------------------------------------------------------------------
- * Per-output lists for the dense-tap schedule.
- *
- * For scenes with more triplets per feature row than taps it is cheaper to
- * multiply every feature row with every tap once (a plain GEMM,
- * (n_feat, C_in) x (C_in, K*C_out), left to the caller) and to sum, per output
- * row, the rows of that product its triplets name -- pcx_indexed_segment_reduce
- * with op = 0 over the lists built here: d_src[e] = gather * K + tap in the
- * order of ascending scatter row (stable), d_lengths[r] = triplets of output
- * row r.  n_feat * K must fit int32.  The reference never leaves the scatter
- * schedule (sparse_engines/tig.py:1090-1206); there is no counterpart.
- */
-size_t pcx_output_lists_workspace_bytes(int64_t T, int64_t n_out);
-int pcx_output_lists(const int32_t *d_scatter, const int32_t *d_gather,
-                     const int64_t *d_seg_offs, int64_t T, int K, int64_t n_feat,
-                     int64_t n_out, int32_t *d_src, int64_t *d_lengths, void *d_ws,
-                     size_t ws_bytes, void *stream);
 
 /* ------------------------------------------------------------------------
  * Segment reductions (op: 0 sum, 1 mean, 2 max, 3 min; fp32 accumulation,

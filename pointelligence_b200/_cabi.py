@@ -49,15 +49,15 @@ SIGNATURES = {
     "pcx_mvmr_plan_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int]),
     "pcx_mvmr_plan_build": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p,
                                     c_size_t, c_void_p]),
-    "pcx_mvmr_planned": (c_int, [c_void_p] * 3 + [c_size_t, c_void_p] + [c_int64] * 3 + [c_int] * 6 + [c_void_p]),
+    "pcx_mvmr_plan_multi_buckets": (c_int, [c_void_p, ctypes.POINTER(c_int64), c_void_p]),
+    "pcx_mvmr_planned_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "pcx_mvmr_planned": (c_int, [c_void_p] * 3 + [c_size_t, c_void_p] + [c_int64] * 3 + [c_int] * 6
+                         + [c_int64, c_void_p, c_size_t, c_void_p]),
     "pcx_debug_wait_runs_out": (c_int, [ctypes.c_ulonglong, c_void_p]),
     "pcx_vvor_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
     "pcx_vvor": (c_int, [c_void_p] * 7 + [c_int64] * 4 + [c_int] * 5 + [c_void_p, c_size_t, c_void_p]),
     "pcx_vvor_static_scratch_max_elements": (c_size_t, []),
     "pcx_vvor_static_scratch": (c_int, [c_void_p] * 6 + [c_int64] * 4 + [c_int] * 4 + [c_void_p]),
-    "pcx_output_lists_workspace_bytes": (c_size_t, [c_int64, c_int64]),
-    "pcx_output_lists": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 2
-                         + [c_void_p, c_size_t, c_void_p]),
     "pcx_segment_reduce_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "pcx_segment_reduce": (c_int, [c_void_p] * 3 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_size_t,
                                                    c_void_p]),
@@ -178,80 +178,16 @@ def profile_records():
 
 
 # ---------------------------------------------------------------- sparse ----
-# Dense-tap schedule for dense neighbourhoods.  With T triplets over n_feat feature rows and K
-# taps, the scatter engines multiply T rows and add T rows of fp32 into the accumulator.  Once
-# T > K * n_feat / (a few), it is cheaper to multiply EVERY feature row with EVERY tap once
-# (one plain GEMM, (n_feat, inw) x (inw, K*outw), the single library GEMM of this package) and
-# then sum, per output row, the rows of that product its triplets name (the library's indexed
-# segment sum: fp32 accumulation, one rounding, no atomics).  The reference always takes the
-# scatter schedule (sparse_engines/tig.py:1090-1206); results agree within the bf16 bound (the
-# per-tap products are rounded to the feature type before the sum).
-_DENSE_TAPS_RATIO = float(os.environ.get("PCX_DENSE_TAPS_RATIO", "12"))     # T / n_feat from which on
-_DENSE_TAPS_MAX_BYTES = int(os.environ.get("PCX_DENSE_TAPS_MAX_BYTES", str(32 << 30)))
-_LISTS_CACHE = {}
-_LISTS_CACHE_MAX = 64
-
-
-def output_lists(scatter, gather, seg_offs, K, n_out, n_feat):
-    """Triplets regrouped by output row: ``(src int32 (T,), lengths int64 (n_out,))`` with
-    ``src = gather * K + tap`` in the order of ascending scatter row (stable)."""
-    require_cuda(scatter, gather, seg_offs)
-    scatter, gather = as_i32(scatter), as_i32(gather)
-    seg_offs = seg_offs.to(torch.int64).contiguous()
-    dev, T = scatter.device, scatter.numel()
-    src = torch.empty(T, dtype=torch.int32, device=dev)
-    lengths = torch.empty(int(n_out), dtype=torch.int64, device=dev)
-    L = lib()
-    with torch.cuda.device(dev):
-        ws = workspace(L.pcx_output_lists_workspace_bytes(T, int(n_out)), dev)
-        check(L.pcx_output_lists(ptr(scatter), ptr(gather), ptr(seg_offs), T, int(K), int(n_feat), int(n_out),
-                                 ptr(src), ptr(lengths), ptr(ws), ws.numel(), stream_ptr()))
-    return src, lengths
-
-
-def cached_output_lists(scatter, gather, seg_offs, K, n_out, n_feat):
-    import weakref
-
-    key = (scatter.data_ptr(), gather.data_ptr(), seg_offs.data_ptr(), scatter.numel(), int(K), int(n_out))
-    stamp = (scatter._version, gather._version, seg_offs._version)
-    hit = _LISTS_CACHE.get(key)
-    if hit is not None:
-        refs, old_stamp, value = hit
-        if old_stamp == stamp and all(r() is t for r, t in zip(refs, (scatter, gather, seg_offs))):
-            return value
-    value = output_lists(scatter, gather, seg_offs, K, n_out, n_feat)
-    # lists of rulebooks whose index tensors are gone are dropped at once (a training loop
-    # builds new rulebooks every step); live ones are bounded by the cache size
-    for k in [k for k, (refs, _, _) in _LISTS_CACHE.items() if any(r() is None for r in refs)]:
-        _LISTS_CACHE.pop(k, None)
-    if len(_LISTS_CACHE) >= _LISTS_CACHE_MAX:
-        for k in list(_LISTS_CACHE)[: _LISTS_CACHE_MAX // 2]:
-            _LISTS_CACHE.pop(k, None)
-    _LISTS_CACHE[key] = (tuple(weakref.ref(t) for t in (scatter, gather, seg_offs)), stamp, value)
-    return value
-
-
-def dense_taps_applies(weight, feat, gather, scatter, seg_offs, n_out):
-    K, G, C, M = weight.shape
-    if _DENSE_TAPS_RATIO <= 0 or G != 1 or seg_offs is None or feat.dtype not in (torch.float16, torch.bfloat16):
-        return False
-    n_feat, T = feat.shape[0], gather.numel()
-    if T < _DENSE_TAPS_RATIO * n_feat or n_out <= 0 or n_feat * K >= 2 ** 31:
-        return False
-    if gather.dtype != torch.int32 or scatter.dtype != torch.int32 or C % 8 or M % 8:
-        return False
-    return n_feat * K * max(C, M) * feat.element_size() <= _DENSE_TAPS_MAX_BYTES
-
-
-def mvmr_dense_taps(weight, feat, gather, scatter, seg_offs, n_out, transpose):
-    """MVMR by the dense-tap schedule (see above); same arguments and result as ``mvmr``."""
-    K, G, C, M = weight.shape
-    inw, outw = (M, C) if transpose else (C, M)
-    src, lengths = cached_output_lists(scatter, gather, seg_offs, K, n_out, feat.shape[0])
-    w3 = weight[:, 0]
-    wcat = (w3.permute(2, 0, 1) if transpose else w3.permute(1, 0, 2)).reshape(inw, K * outw)
-    product = feat @ wcat                                   # (n_feat, K * outw): every row with every tap
-    return indexed_segment_reduce(product.view(feat.shape[0] * K, outw), src, lengths, REDUCE_OPS["sum"])
+# Engine choice of ``mvmr`` with the automatic engine.  The output-stationary kernel
+# (``pcx_mvmr_planned``: accumulators in tensor memory across all taps, every output row written
+# once) needs a plan of the rulebook, built once per rulebook and direction and remembered by the
+# identity of the index tensors.  Measured on B200 it wins for rows of 128 channels and more at any
+# density and for narrower rows once a scene has about a dozen triplets per output row (the deeper
+# levels of a U-Net, dense scans); sparse narrow layers stay on the scatter kernel of ``pcx_mvmr``.
+ENGINE_PLANNED = 3
+_PLANNED_MIN_WIDTH = int(os.environ.get("PCX_PLANNED_MIN_WIDTH", "128"))     # output width from which on, at any density
+_PLANNED_MIN_RATIO = float(os.environ.get("PCX_PLANNED_MIN_RATIO", "12"))     # triplets per output row from which on
+_PLANNED_ENABLED = os.environ.get("PCX_PLANNED", "1") != "0"
 
 
 class MvmrPlan:
@@ -261,10 +197,11 @@ class MvmrPlan:
     one direction (which index is scattered) and one ``group_blocks`` value.
     """
 
-    __slots__ = ("buffer", "T", "K", "n_out", "group_blocks", "__weakref__")
+    __slots__ = ("buffer", "T", "K", "n_out", "group_blocks", "multi_buckets", "__weakref__")
 
-    def __init__(self, buffer, T, K, n_out, group_blocks):
+    def __init__(self, buffer, T, K, n_out, group_blocks, multi_buckets):
         self.buffer, self.T, self.K, self.n_out, self.group_blocks = buffer, T, K, n_out, group_blocks
+        self.multi_buckets = multi_buckets   # (row, tap) buckets with several triplets
 
     def views(self):
         """The plan's arrays as tensors (for tests): perm, tile_offs, entries (T, 2), group_order."""
@@ -278,11 +215,15 @@ class MvmrPlan:
         for name, count, dtype, width in (("ctrl", 64, torch.int32, 4), ("perm", nblocks * 128, torch.int32, 4),
                                           ("tile_offs", nblocks * self.K + 1, torch.int32, 4),
                                           ("entries", max(self.T, 1) * 2, torch.int32, 4),
-                                          ("group_order", max(ngroups, 1), torch.int32, 4)):
+                                          ("group_order", max(ngroups, 1), torch.int32, 4),
+                                          ("tile_rows", nblocks * self.K * 128, torch.int32, 4),
+                                          ("buckets", (self.T // 2 + 1) * 2, torch.int32, 4)):
             out[name] = buf[off:off + count * width].view(dtype)
             off += up(count * width)
         out["entries"] = out["entries"][: self.T * 2].view(-1, 2)
         out["group_order"] = out["group_order"][:ngroups]
+        out["tile_rows"] = out["tile_rows"].view(-1, 128)
+        out["buckets"] = out["buckets"].view(-1, 2)[: self.multi_buckets]
         return out
 
 
@@ -321,7 +262,9 @@ def mvmr_plan(scatter, gather, seg_offs, K, n_out, group_blocks):
         ws = workspace(L.pcx_mvmr_plan_workspace_bytes(T, n_out, K, G), dev)
         check(L.pcx_mvmr_plan_build(ptr(scatter), ptr(gather), ptr(seg_offs), T, K, n_out, G, ptr(buf), buf.numel(),
                                     ptr(ws), ws.numel(), stream_ptr()))
-    return MvmrPlan(buf, T, K, n_out, G)
+        multi = c_int64(0)
+        check(L.pcx_mvmr_plan_multi_buckets(ptr(buf), ctypes.byref(multi), stream_ptr()))
+    return MvmrPlan(buf, T, K, n_out, G, int(multi.value))
 
 
 _PLAN_CACHE = {}
@@ -358,12 +301,14 @@ def mvmr_planned(weight, feat, plan, transpose):
     K, G, C, M = weight.shape
     assert G == 1 and K == plan.K and weight.dtype == feat.dtype, (weight.shape, plan.K, weight.dtype, feat.dtype)
     weight, feat = weight.contiguous(), feat.contiguous()
-    outw = C if transpose else M
+    inw, outw = (M, C) if transpose else (C, M)
     out = torch.empty((plan.n_out, outw), dtype=feat.dtype, device=feat.device)
+    L = lib()
     with torch.cuda.device(feat.device):
-        check(lib().pcx_mvmr_planned(ptr(weight), ptr(feat), ptr(plan.buffer), plan.buffer.numel(), ptr(out), plan.T,
-                                     feat.shape[0], plan.n_out, K, C, M, int(bool(transpose)), dtype_code(feat.dtype),
-                                     plan.group_blocks, stream_ptr()))
+        ws = workspace(L.pcx_mvmr_planned_workspace_bytes(plan.multi_buckets, inw), feat.device)
+        check(L.pcx_mvmr_planned(ptr(weight), ptr(feat), ptr(plan.buffer), plan.buffer.numel(), ptr(out), plan.T,
+                                 feat.shape[0], plan.n_out, K, C, M, int(bool(transpose)), dtype_code(feat.dtype),
+                                 plan.group_blocks, plan.multi_buckets, ptr(ws), ws.numel(), stream_ptr()))
     return out
 
 
@@ -376,8 +321,8 @@ def mvmr(weight, feat, gather, scatter, seg_offs, tap_idx, n_out, transpose, eng
     """``out[scatter[t]] += feat[gather[t]] @ W[tap(t)]`` (``transpose``: use W^T).
 
     weight (K,G,C,M); feat (n_feat, G*inw); returns (n_out, G*outw) in feat.dtype.  With the
-    automatic engine, dense neighbourhoods (many triplets per feature row) take the dense-tap
-    schedule, everything else the scatter engines of ``pcx_mvmr``.
+    automatic engine, wide rows and dense neighbourhoods take the output-stationary kernel
+    (``ENGINE_PLANNED`` forces it), everything else the scatter engines of ``pcx_mvmr``.
     """
     require_cuda(weight, feat, gather, scatter, seg_offs, tap_idx)
     K, G, C, M = weight.shape
@@ -385,8 +330,17 @@ def mvmr(weight, feat, gather, scatter, seg_offs, tap_idx, n_out, transpose, eng
     assert weight.dtype == feat.dtype, (weight.dtype, feat.dtype)
     weight, feat = weight.contiguous(), feat.contiguous()
     n_out = int(n_out)
-    if engine == ENGINE_AUTO and dense_taps_applies(weight, feat, gather, scatter, seg_offs, n_out):
-        return mvmr_dense_taps(weight, feat, gather, scatter, seg_offs, n_out, transpose)
+    if engine in (ENGINE_AUTO, ENGINE_PLANNED):
+        fits = planned_supported(weight, feat, gather, scatter, seg_offs, n_out, transpose)
+        if engine == ENGINE_PLANNED and not fits:
+            raise NotImplementedError("the output-stationary engine needs fp16/bf16 features, one group, tap-sorted "
+                                      "triplets, channel counts that are multiples of 16 and rows of at most 256 channels")
+        outw = C if transpose else M
+        if fits and (engine == ENGINE_PLANNED or (_PLANNED_ENABLED and (
+                outw >= _PLANNED_MIN_WIDTH or gather.numel() >= _PLANNED_MIN_RATIO * n_out))):
+            plan = cached_mvmr_plan(scatter, gather, seg_offs, K, n_out, plan_group_blocks(outw))
+            return mvmr_planned(weight, feat, plan, transpose)
+        engine = ENGINE_AUTO
     gather, scatter, tap_idx = as_i32(gather), as_i32(scatter), as_i32(tap_idx)
     if seg_offs is not None:
         seg_offs = seg_offs.to(torch.int64).contiguous()

@@ -9,21 +9,26 @@
 //   rows     output rows are ordered by their tap signature (the set of taps that touch the
 //            row), so that the 128 rows of a block use few distinct taps and the
 //            (block, tap) tiles below are well filled; perm[block * 128 + slot] = row
-//   tiles    the triplets of (block, tap), ordered by slot; tile_offs is the dense
-//            (nblocks * K + 1) table of their offsets
-//   entries  per triplet (slot | position among the triplets of the same (row, tap) << 8,
-//            gathered feature row)
+//   tiles    per (block, tap) a table of 128 source rows, one per slot: a feature row, "none",
+//            or a row of the per-call scratch that holds the SUM of the feature rows of a
+//            (row, tap) bucket with several triplets (the bucket pre-sum of the reference's fused
+//            gather-sum schedule, sparse_engines/fused_point_conv.py:344-423); tile_offs is the
+//            dense (nblocks * K + 1) table of triplet counts that tells which tiles exist
+//   entries  per triplet (slot | position in its bucket << 8, feature row), ordered by
+//            (block, tap, slot): the members of a bucket are consecutive
+//   buckets  (first entry, length) of every bucket with more than one triplet
 //   groups   G consecutive blocks share the weight tiles they stream; groups are handed out
 //            most expensive first (a ticket counter inside the plan)
 //
-// The kernel (one CTA per SM, TMEM columns = G accumulators of out_width fp32 each):
+// Per call: a small kernel sums the rows of the multi-triplet buckets into the scratch (fp32 sum,
+// one rounding), then the main kernel (TMEM columns = G accumulators of out_width fp32 each):
 //
-//   producer warps   one (block, tap, 64-channel slice) A tile each: zero the 128 x 128 B
-//                    slot, copy the feature row of every first triplet of a (row, tap) bucket
-//                    into its slot row (registers -> 128-byte-swizzled shared memory), add the
-//                    rows of further triplets of the bucket (the bucket pre-sum of the
-//                    reference's fused gather-sum schedule, sparse_engines/
-//                    fused_point_conv.py:344-423), signal the slot's mbarrier
+//   producer warps   together, one (block, tap, 64-channel slice) A tile after the other: every
+//                    thread issues its 16-byte cp.async copies of the tile's source rows straight
+//                    into the 128-byte-swizzled slot (rows without a source are zero-filled by the
+//                    same instruction with a source size of 0) and hands the slot's mbarrier an
+//                    arrival that fires when its copies have landed; nothing waits for data, so
+//                    as many tiles are in flight as there are slots
 //   weight warp      streams the 64-channel slices of W[tap] through a small ring with TMA
 //                    (cp.async.bulk.tensor, 128-byte swizzle, no multicast); one slice serves
 //                    all blocks of the group that use the tap
@@ -52,18 +57,17 @@ using namespace tc;
 
 constexpr int ROWS = 128;             // output rows per block (the M of the MMA)
 constexpr int SLOT_BYTES = ROWS * 128;  // one A tile: 128 rows of a 64-channel slice
-constexpr int MAX_NPW = 10;           // producer warps (= A slots)
+constexpr int MAX_NPW = 8;            // producer warps
+constexpr int MAX_SLOTS = 12;         // A slots
 constexpr int MAX_NW = 4;             // weight slots
 constexpr int MAX_GROUP = 8;          // blocks per group
 constexpr int MAX_TAPS = 512;         // taps the shared-memory tables are sized for
-constexpr int UNROLL = 8;             // entries a producer lane holds per batch
-constexpr int SIDE_ROWS = 16;         // rows of a warp's side buffer (further triplets of a bucket)
-constexpr int SIDE_BYTES = SIDE_ROWS * 128;
+constexpr int ROW_PASSES = 8;         // rows a producer thread copies per tile, at most (128 rows / (4 warps * 4 row lanes))
 constexpr unsigned STATUS_BIT = 4u;   // bit of the device status word this kernel raises
 constexpr unsigned PLAN_MAGIC = 0x70637832u;
 
 // control words at the head of a plan
-enum { CTRL_TICKET = 0, CTRL_DONE = 1, CTRL_MAGIC = 2, CTRL_GROUP = 3, CTRL_WORDS = 64 };
+enum { CTRL_TICKET = 0, CTRL_DONE = 1, CTRL_MAGIC = 2, CTRL_GROUP = 3, CTRL_NMULTI = 4, CTRL_WORDS = 64 };
 
 struct PlanView {
     uint32_t *ctrl;        // CTRL_WORDS
@@ -71,6 +75,8 @@ struct PlanView {
     int32_t *tile_offs;    // nblocks * K + 1
     uint2 *entries;        // T
     int32_t *group_order;  // ngroups
+    int32_t *tile_rows;    // nblocks * K * ROWS: source row of (tile, slot): >= 0 feature row, -1 none, <= -2 scratch row -2 - x
+    uint2 *buckets;        // T / 2 + 1: (first entry, length) of the buckets with several triplets
     int64_t nblocks, ngroups;
 };
 
@@ -84,6 +90,8 @@ size_t carve_plan(void *base, int64_t T, int64_t n_out, int K, int G, PlanView *
     v.tile_offs = c.take<int32_t>((size_t)v.nblocks * K + 1);
     v.entries = c.take<uint2>((size_t)std::max<int64_t>(T, 1));
     v.group_order = c.take<int32_t>((size_t)std::max<int64_t>(v.ngroups, 1));
+    v.tile_rows = c.take<int32_t>((size_t)v.nblocks * K * ROWS);
+    v.buckets = c.take<uint2>((size_t)(T / 2 + 1));
     if (out) *out = v;
     return c.off;
 }
@@ -131,6 +139,15 @@ size_t carve_build(void *base, int64_t T, int64_t n_out, int K, int G, BuildWs *
     w.cub_tmp = c.take<char>(w.cub_bytes);
     if (out) *out = w;
     return c.off;
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
+    if (fmt) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&v);
 }
 
 __device__ __forceinline__ int tap_of(const int64_t *__restrict__ seg, int K, int64_t t) {
@@ -185,15 +202,55 @@ __global__ void plan_keys_kernel(const int32_t *__restrict__ scatter, const int3
     atomicAdd(&tile_cnt[tile], 1);
 }
 
-// entries[t] = (slot | position within the (row, tap) bucket << 8, feature row)
+// entries[t] = (slot | position within the (row, tap) bucket << 8, feature row); the first entry
+// of a bucket also fills the bucket's slot of its tile's row table: the feature row itself, or,
+// when more triplets follow, the scratch row the bucket's sum will be written to
 __global__ void plan_entries_kernel(const uint32_t *__restrict__ key_sorted, const int32_t *__restrict__ val_sorted,
-                                    int64_t T, uint2 *entries) {
+                                    int64_t T, uint2 *entries, int32_t *tile_rows, uint2 *buckets, uint32_t *ctrl) {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
     const uint32_t k = key_sorted[t];
     uint32_t pos = 0;
     while (pos < 0xffffffu && t - (int64_t)pos - 1 >= 0 && key_sorted[t - pos - 1] == k) ++pos;
     entries[t] = make_uint2((k & 127u) | (pos << 8), (uint32_t)val_sorted[t]);
+    if (pos != 0) return;
+    uint32_t len = 1;
+    while (t + len < T && key_sorted[t + len] == k) ++len;
+    if (len == 1) {
+        tile_rows[k] = val_sorted[t];   // key = tile * 128 + slot
+    } else {
+        const uint32_t b = atomicAdd(&ctrl[CTRL_NMULTI], 1u);
+        buckets[b] = make_uint2((uint32_t)t, len);
+        tile_rows[k] = -2 - (int32_t)b;
+    }
+}
+
+// scratch[b] = sum of the feature rows of bucket b (fp32 sum, one rounding); one thread per 16-byte piece
+__global__ void bucket_sum_kernel(const uint16_t *__restrict__ feat, const uint2 *__restrict__ entries,
+                                  const uint2 *__restrict__ buckets, const uint32_t *__restrict__ ctrl, int inw, int fmt,
+                                  uint16_t *scratch) {
+    const int ppr = inw >> 3;
+    const int64_t x = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t b = x / ppr;
+    const int piece = (int)(x - b * ppr);
+    if (b >= (int64_t)ctrl[CTRL_NMULTI]) return;
+    const uint2 bk = buckets[b];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (uint32_t m = 0; m < bk.y; ++m) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(feat + (int64_t)entries[bk.x + m].y * inw + piece * 8);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float2 f;
+            if (fmt) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[q]));
+            else f = __half22float2(*reinterpret_cast<const __half2 *>(&w[q]));
+            acc[2 * q] += f.x, acc[2 * q + 1] += f.y;
+        }
+    }
+    uint4 o;
+    o.x = pack2(acc[0], acc[1], fmt), o.y = pack2(acc[2], acc[3], fmt);
+    o.z = pack2(acc[4], acc[5], fmt), o.w = pack2(acc[6], acc[7], fmt);
+    *reinterpret_cast<uint4 *>(scratch + b * inw + piece * 8) = o;
 }
 
 // cost of a group = its non-empty tiles (each is one A tile to gather and multiply)
@@ -214,49 +271,18 @@ struct OsParams {
     const uint16_t *feat;
     uint16_t *out;
     const uint16_t *weight;
-    const int32_t *perm, *tile_offs, *group_order;
+    const int32_t *perm, *tile_offs, *group_order, *tile_rows;
+    const uint16_t *scratch;   // sums of the multi-triplet buckets
     const uint2 *entries;
     uint32_t *ctrl;
     unsigned int *status;
     int K, C, M, transpose, fmt;
     int inw, outw, nkb, G, ngroups, nblocks;
-    int npw, nw, use_tma;
+    int npw, nslots, nw, use_tma;
     uint32_t w_slot_bytes, w_box_rows, w_tx_bytes;
     uint32_t ncols, col_stride;
     uint64_t wait_limit_ns;
 };
-
-// a + b on eight 16-bit floats (one rounding per element)
-__device__ __forceinline__ uint4 add8(uint4 a, uint4 b, int fmt) {
-    uint4 r;
-    if (fmt) {
-        const __nv_bfloat162 *pa = reinterpret_cast<const __nv_bfloat162 *>(&a), *pb = reinterpret_cast<const __nv_bfloat162 *>(&b);
-        __nv_bfloat162 *pr = reinterpret_cast<__nv_bfloat162 *>(&r);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float2 fa = __bfloat1622float2(pa[q]), fb = __bfloat1622float2(pb[q]);
-            pr[q] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
-        }
-    } else {
-        const __half2 *pa = reinterpret_cast<const __half2 *>(&a), *pb = reinterpret_cast<const __half2 *>(&b);
-        __half2 *pr = reinterpret_cast<__half2 *>(&r);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float2 fa = __half22float2(pa[q]), fb = __half22float2(pb[q]);
-            pr[q] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
-        }
-    }
-    return r;
-}
-
-__device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
-    if (fmt) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-        return *reinterpret_cast<uint32_t *>(&v);
-    }
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
 
 __device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
     uint4 v;
@@ -294,42 +320,27 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
 // Order (every role walks the same lists): taps ascending; per tap the slices of the
 // contraction; per slice the blocks of the group that use the tap.
 __device__ __forceinline__ int pieces_of(int inw, int q) { return min(8, (inw - q * 64) >> 3); }
-__device__ __forceinline__ int piece_shift(int pieces) { return pieces > 4 ? 3 : pieces > 2 ? 2 : 1; }
-
-// entries from..end: lane (sub, piece) takes entry from + u * subs + sub
-__device__ __forceinline__ void load_entries(uint2 (&dst)[UNROLL], const uint2 *__restrict__ entries, int from, int end,
-                                             int psh, int lane) {
-    const int sub = lane >> psh, subs = 32 >> psh;
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-        const int e = from + u * subs + sub;
-        dst[u] = make_uint2(0xffffffffu, 0u);
-        if (e < end) dst[u] = ldg_nc_v2(entries + e);
-    }
-}
 
 __global__ void __launch_bounds__(512, 1)
 mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t s_a_full[MAX_NPW], s_a_empty[MAX_NPW], s_w_full[MAX_NW], s_w_empty[MAX_NW], s_d_full;
+    __shared__ uint64_t s_a_full[MAX_SLOTS], s_a_empty[MAX_SLOTS], s_w_full[MAX_NW], s_w_empty[MAX_NW], s_d_full;
     __shared__ uint32_t s_tmem;
     __shared__ int s_group, s_ntiles, s_ntaps, s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t a_base = base, w_base = base + (uint32_t)p.npw * SLOT_BYTES;
-    const uint32_t side_base = w_base + (uint32_t)p.nw * p.w_slot_bytes;   // one side buffer per producer warp
-    uint8_t *tab_raw = smem_raw + (side_base + (uint32_t)p.npw * SIDE_BYTES - smem_u32(smem_raw));
+    const uint32_t a_base = base, w_base = base + (uint32_t)p.nslots * SLOT_BYTES;
+    uint8_t *tab_raw = smem_raw + (w_base + (uint32_t)p.nw * p.w_slot_bytes - smem_u32(smem_raw));
     // tables of the current group (16-byte aligned): A tasks, tile offsets, tile list, run ordinals, W tasks
     int4 *s_task = reinterpret_cast<int4 *>(tab_raw);                       // G*K*nkb
     int32_t *s_tab = reinterpret_cast<int32_t *>(s_task + p.G * p.K * p.nkb);  // G*K + 1
     int32_t *s_list = s_tab + (p.G * p.K + 1);                                // G*K: tap << 8 | block, tap-major
     int32_t *s_run = s_list + p.G * p.K;                                      // G*K: ordinal of the tile's tap among the group's taps
     int32_t *s_wtask = s_run + p.G * p.K;                                     // K*nkb
-    int32_t *s_side = s_wtask + p.K * p.nkb;                                  // npw * SIDE_ROWS: target row | position << 8
     volatile int *abort_flag = &s_abort;
 
     if (tid == 0) {
-        for (int s = 0; s < p.npw; ++s) mbar_init(smem_u32(&s_a_full[s]), 32), mbar_init(smem_u32(&s_a_empty[s]), 1);
+        for (int s = 0; s < p.nslots; ++s) mbar_init(smem_u32(&s_a_full[s]), (uint32_t)p.npw * 32), mbar_init(smem_u32(&s_a_empty[s]), 1);
         for (int s = 0; s < p.nw; ++s) mbar_init(smem_u32(&s_w_full[s]), p.use_tma ? 1 : 32), mbar_init(smem_u32(&s_w_empty[s]), 1);
         mbar_init(smem_u32(&s_d_full), 1);
         fence_mbar_init();
@@ -344,7 +355,7 @@ mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
     const uint32_t idesc = instr_desc(p.fmt, ROWS, p.outw, 0, p.transpose ? 0 : 1);
 
     // A tiles, weight tiles and accumulator hand-overs of the groups this CTA has finished (all
-    // roles count alike): tile n uses A slot n mod npw for the (n / npw)-th time, and so on
+    // roles count alike): tile n uses A slot n mod nslots for the (n / nslots)-th time, and so on
     uint32_t a_n = 0, w_n = 0, d_n = 0;
 
     for (;;) {
@@ -404,113 +415,55 @@ mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
         STAT_T0(t_role);
         if (warp < p.npw) {
             // ---------------------------------------------------------- producer ----
-            const uint32_t slot_addr = a_base + (uint32_t)warp * SLOT_BYTES;
-            const uint32_t side_addr = side_base + (uint32_t)warp * SIDE_BYTES;
-            int32_t *side_meta = s_side + warp * SIDE_ROWS;
-            const uint32_t full_bar = smem_u32(&s_a_full[warp]), empty_bar = smem_u32(&s_a_empty[warp]);
+            // All producer threads fill every tile together: 8 threads per row (one 16-byte piece
+            // each), npw * 4 rows per pass.  The source rows of the next tile are fetched while
+            // the current one is issued.
+            const int piece = tid & 7, row_lane = tid >> 3, row_lanes = p.npw * 4;
+            uint32_t slot = a_n % (uint32_t)p.nslots, use = a_n / (uint32_t)p.nslots;
             bool ok_role = true;
-            // this warp's tiles: those whose launch-wide index a_n + t is congruent to the warp modulo npw
-            int t = (int)(((uint32_t)warp + (uint32_t)p.npw - a_n % (uint32_t)p.npw) % (uint32_t)p.npw);
-            uint32_t use = (a_n + (uint32_t)t) / (uint32_t)p.npw;  // times this warp's slot has been filled before
-            // Entries are fetched two batches ahead of the batch being issued (a batch = UNROLL entries
-            // per lane group), across tile boundaries: `ld_*` is the position of the next batch to fetch.
-            uint2 ent[UNROLL], ent_next[UNROLL], ent_far[UNROLL];
-            int ld_t = t, ld_e = 0, ld_hi = 0, ld_psh = 3;
-            auto fetch_batch = [&](uint2 (&dst)[UNROLL]) {
+            int rows_next[ROW_PASSES];
+            auto fetch_rows = [&](int task) {
+                const int meta = s_task[task].z;
+                const int32_t *table = p.tile_rows + ((int64_t)(b0 + (meta & 15)) * p.K + (meta >> 16)) * ROWS;
 #pragma unroll
-                for (int u = 0; u < UNROLL; ++u) dst[u] = make_uint2(0xffffffffu, 0u);
-                if (ld_t >= a_total) return;
-                if (ld_e >= ld_hi) {  // first batch of tile ld_t
-                    const int4 k4 = s_task[ld_t];
-                    ld_e = k4.x, ld_hi = k4.y, ld_psh = piece_shift(pieces_of(p.inw, (k4.z >> 4) & 15));
+                for (int k = 0; k < ROW_PASSES; ++k) {
+                    const int r = row_lane + k * row_lanes;
+                    rows_next[k] = -1;
+                    if (r < ROWS) rows_next[k] = __ldg(table + r);
                 }
-                load_entries(dst, p.entries, ld_e, ld_hi, ld_psh, lane);
-                ld_e += UNROLL * (32 >> ld_psh);
-                if (ld_e >= ld_hi) ld_t += p.npw, ld_e = 0, ld_hi = 0;
             };
-            fetch_batch(ent);
-            fetch_batch(ent_next);
-            while (t < a_total && ok_role) {
-                const int4 tk = s_task[t];
-                const int lo = tk.x, hi = tk.y, q = (tk.z >> 4) & 15;
-                const int pieces = pieces_of(p.inw, q), psh = piece_shift(pieces);
-                const int piece = lane & ((1 << psh) - 1), sub = lane >> psh, subs = 32 >> psh;
-                const bool piece_ok = piece < pieces;
-                const uint32_t before_my_sub = (1u << (sub << psh)) - 1u;  // lanes of the lane groups before mine
-                const uint16_t *fcol = p.feat + q * 64 + piece * 8;
+            if (a_total > 0) fetch_rows(0);
+            for (int t = 0; t < a_total; ++t) {
+                int rows_cur[ROW_PASSES];
+#pragma unroll
+                for (int k = 0; k < ROW_PASSES; ++k) rows_cur[k] = rows_next[k];
+                const int q = (s_task[t].z >> 4) & 15;
+                if (t + 1 < a_total) fetch_rows(t + 1);
+                const bool piece_ok = piece < pieces_of(p.inw, q);
+                const int col = q * 64 + piece * 8;
+                const uint32_t slot_addr = a_base + slot * SLOT_BYTES;
                 // the tensor core has finished reading this slot's previous tile
                 STAT_T0(t_w);
-                ok_role = mbar_wait_abortable(empty_bar, (use & 1u) ^ 1u, STATUS_BIT, p.status, abort_flag, p.wait_limit_ns);
-                ok_role = __all_sync(0xffffffffu, ok_role);
+                ok_role = mbar_wait_abortable(smem_u32(&s_a_empty[slot]), (use & 1u) ^ 1u, STATUS_BIT, p.status, abort_flag,
+                                              p.wait_limit_ns);
                 STAT_ADD(9, t_w);
                 if (!ok_role) break;
-                uint32_t present0 = 0u, present1 = 0u, present2 = 0u, present3 = 0u;  // rows of the slot that receive a feature row
-                int nside = 0;                            // side rows in use (uniform over the warp)
-                uint32_t maxpos = 0;
-                // The rows parked in the side buffer are added to their slot rows, one bucket position
-                // per round (rows of one position have distinct targets), after all copies have landed.
-                auto apply_side = [&]() {
-                    cp_async_commit();
-                    cp_async_wait<0>();
-                    __syncwarp();
-                    maxpos = __reduce_max_sync(0xffffffffu, maxpos);
-                    for (uint32_t r = 1; r <= maxpos; ++r) {
-                        for (int sr = sub; sr < nside; sr += subs) {
-                            const uint32_t meta = (uint32_t)side_meta[sr];
-                            if ((meta >> 8) == r && piece_ok) {
-                                const uint32_t row = meta & 127u;
-                                const uint32_t addr = slot_addr + row * 128 + (((uint32_t)piece ^ (row & 7u)) << 4);
-                                sts_v4(addr, add8(lds_v4(addr), lds_v4(side_addr + (uint32_t)sr * 128 + (uint32_t)piece * 16), p.fmt));
-                            }
-                        }
-                        __syncwarp();
+#pragma unroll
+                for (int k = 0; k < ROW_PASSES; ++k) {
+                    const int r = row_lane + k * row_lanes;
+                    if (r < ROWS && piece_ok) {
+                        const int src_row = rows_cur[k];
+                        // a feature row, a row of bucket sums, or nothing (16 bytes of zeros: source size 0)
+                        const uint16_t *src = src_row >= 0 ? p.feat + (int64_t)src_row * p.inw
+                                              : src_row == -1 ? p.feat : p.scratch + (int64_t)(-2 - src_row) * p.inw;
+                        cp_async16_zfill(slot_addr + (uint32_t)r * 128 + (uint32_t)((piece ^ (r & 7)) << 4), src + col,
+                                         src_row == -1 ? 0u : 16u);
                     }
-                    nside = 0, maxpos = 0;
-                };
-                for (int e0 = lo; e0 < hi; e0 += UNROLL * subs) {
-                    fetch_batch(ent_far);
-#pragma unroll
-                    for (int u = 0; u < UNROLL; ++u) {
-                        const uint32_t x = ent[u].x;
-                        const bool valid = x != 0xffffffffu;
-                        const uint32_t pos = x >> 8, row = x & 127u;
-                        // further triplets of a bucket are parked in the side buffer: make room first
-                        const unsigned heads = __ballot_sync(0xffffffffu, valid && pos > 0 && piece == 0);
-                        if (nside + __popc(heads) > SIDE_ROWS) apply_side();
-                        if (valid) {
-                            const uint16_t *src = fcol + (int64_t)ent[u].y * p.inw;
-                            if (pos == 0) {  // first triplet of a (row, tap) bucket: straight into the row of the slot
-                                if (piece_ok) cp_async16(slot_addr + row * 128 + (((uint32_t)piece ^ (row & 7u)) << 4), src);
-                                const uint32_t bit = 1u << (row & 31u), word = row >> 5;
-                                present0 |= word == 0 ? bit : 0u, present1 |= word == 1 ? bit : 0u;
-                                present2 |= word == 2 ? bit : 0u, present3 |= word == 3 ? bit : 0u;
-                            } else {
-                                const int sr = nside + __popc(heads & before_my_sub);
-                                if (piece_ok) cp_async16(side_addr + (uint32_t)sr * 128 + (uint32_t)piece * 16, src);
-                                if (piece == 0) side_meta[sr] = (int32_t)x;
-                                maxpos = max(maxpos, pos);
-                            }
-                        }
-                        nside += __popc(heads);
-                    }
-#pragma unroll
-                    for (int u = 0; u < UNROLL; ++u) ent[u] = ent_next[u], ent_next[u] = ent_far[u];
                 }
-                // rows that receive nothing are zeroed (disjoint from the rows being copied into)
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const uint32_t got = __reduce_or_sync(0xffffffffu, w == 0 ? present0 : w == 1 ? present1 : w == 2 ? present2 : present3);
-                    for (int rr = sub; rr < 32; rr += subs)
-                        if (!((got >> rr) & 1u) && piece_ok) {
-                            const uint32_t row = (uint32_t)(w * 32 + rr);
-                            sts_v4(slot_addr + row * 128 + (((uint32_t)piece ^ (row & 7u)) << 4), make_uint4(0, 0, 0, 0));
-                        }
-                }
-                apply_side();
-                fence_async_smem();
-                mbar_arrive(full_bar);
-                t += p.npw, ++use;
+                cp_async_mbar_arrive(smem_u32(&s_a_full[slot]));   // fires once this thread's copies have landed
+                if (++slot == (uint32_t)p.nslots) slot = 0, ++use;
             }
+            ok_role = __all_sync(0xffffffffu, ok_role);
             STAT_ADD(10, t_role);
             STAT_T0(t_epi);
             // ---------------------------------------------------------- epilogue ----
@@ -552,7 +505,7 @@ mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
         } else if (warp == p.npw) {
             // --------------------------------------------------------------- MMA ----
             if (lane == 0) {
-                uint32_t slot = a_n % (uint32_t)p.npw, use = a_n / (uint32_t)p.npw;
+                uint32_t slot = a_n % (uint32_t)p.nslots, use = a_n / (uint32_t)p.nslots;
                 uint32_t wslot = w_n % (uint32_t)p.nw, wuse = w_n / (uint32_t)p.nw;
                 uint32_t started = 0;
                 bool ok_role = true;
@@ -578,6 +531,7 @@ mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
                                                   p.wait_limit_ns);
                     if (!ok_role) break;
                     STAT_ADD(14, t_a);
+                    fence_async_smem();   // the tile was written by cp.async (generic proxy), the tensor core reads through the async proxy
                     tc_fence_after();
                     const uint64_t ad = a_desc0 + (uint64_t)(slot * (SLOT_BYTES >> 4));
                     const uint64_t bd = b_desc0 + (uint64_t)(wslot * w_slot16);
@@ -591,7 +545,7 @@ mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
                     started |= 1u << blk;
                     STAT_T0(t_c);
                     tc_commit(smem_u32(&s_a_empty[slot]));
-                    if (++slot == (uint32_t)p.npw) slot = 0, ++use;
+                    if (++slot == (uint32_t)p.nslots) slot = 0, ++use;
                     if (meta & 512) {  // last tile of the weight slice: its slot is free once these MMAs are done
                         tc_commit(smem_u32(&s_w_empty[wslot]));
                         if (++wslot == (uint32_t)p.nw) wslot = 0, ++wuse;
@@ -746,9 +700,10 @@ extern "C" {
 int pcx_mvmr_plan_group_blocks(int out_width) {
     if (out_width <= 0 || out_width > 256) return 0;
     const int stride = (out_width + 31) / 32 * 32;
-    // up to 64 channels: four accumulators in half of the tensor memory (two CTAs per SM);
-    // 128 channels: two; 256 channels: two accumulators fill the tensor memory of one CTA per SM
-    int g = stride <= 64 ? 4 : 2;
+    // Two blocks per group, measured best at every width: up to 128 channels two accumulators fit
+    // half of the tensor memory (two CTAs per SM), at 256 channels they fill it (one CTA per SM);
+    // larger groups share each weight tile among more blocks but balance worse.
+    int g = 2;
     if (const char *e = getenv("PCX_OS_GROUP")) {
         const int want = atoi(e);
         if (want >= 1 && want <= MAX_GROUP && want * stride <= 512) g = want;
@@ -787,6 +742,7 @@ int pcx_mvmr_plan_build(const int32_t *d_scatter, const int32_t *d_gather, const
     const int64_t n_tiles = pv.nblocks * K, n_pad = pv.nblocks * ROWS;
     auto blocks = [&](int64_t n) { return (unsigned)((n + TPB - 1) / TPB); };
     const int64_t init_n = std::max<int64_t>(std::max<int64_t>(n_out, n_tiles + 1), CTRL_WORDS);
+    PCX_CUDA(cudaMemsetAsync(pv.tile_rows, 0xff, (size_t)n_tiles * ROWS * sizeof(int32_t), stream));
     plan_init_kernel<<<blocks(init_n), TPB, 0, stream>>>(n_out, w.sig, w.row, w.tile_cnt, n_tiles, pv.ctrl, G);
     PCX_LAUNCH_CHECK();
     size_t bytes = w.cub_bytes;
@@ -809,7 +765,8 @@ int pcx_mvmr_plan_build(const int32_t *d_scatter, const int32_t *d_gather, const
     bytes = w.cub_bytes;
     PCX_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, bytes, w.tile_cnt, pv.tile_offs, (int)(n_tiles + 1), stream));
     if (T > 0) {
-        plan_entries_kernel<<<blocks(T), TPB, 0, stream>>>(w.key_sorted, w.val_sorted, T, pv.entries);
+        plan_entries_kernel<<<blocks(T), TPB, 0, stream>>>(w.key_sorted, w.val_sorted, T, pv.entries, pv.tile_rows, pv.buckets,
+                                                           pv.ctrl);
         PCX_LAUNCH_CHECK();
     }
     plan_cost_kernel<<<blocks(pv.ngroups), TPB, 0, stream>>>(pv.tile_offs, pv.nblocks, K, G, pv.ngroups, w.cost, w.gid);
@@ -820,9 +777,24 @@ int pcx_mvmr_plan_build(const int32_t *d_scatter, const int32_t *d_gather, const
     return PCX_OK;
 }
 
+size_t pcx_mvmr_planned_workspace_bytes(int64_t multi_buckets, int in_width) {
+    if (multi_buckets < 0 || in_width <= 0) return 0;
+    return align_up((size_t)std::max<int64_t>(multi_buckets, 1) * in_width * 2, 256);
+}
+
+int pcx_mvmr_plan_multi_buckets(const void *d_plan, int64_t *h_count, void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!d_plan || !h_count) PCX_FAIL(PCX_E_ARG, "pcx_mvmr_plan_multi_buckets: null pointer");
+    uint32_t n = 0;
+    PCX_CUDA(cudaMemcpyAsync(&n, (const uint32_t *)d_plan + CTRL_NMULTI, sizeof(n), cudaMemcpyDeviceToHost, stream));
+    PCX_CUDA(cudaStreamSynchronize(stream));
+    *h_count = n;
+    return PCX_OK;
+}
+
 int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan, size_t plan_bytes, void *d_out, int64_t T,
                      int64_t n_feat, int64_t n_out, int K, int C, int M, int transpose, int dtype, int group_blocks,
-                     void *stream_) {
+                     int64_t multi_buckets, void *d_ws, size_t ws_bytes, void *stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     const int G = group_blocks;
     if (dtype != PCX_F16 && dtype != PCX_BF16) PCX_FAIL(PCX_E_DTYPE, "pcx_mvmr_planned: fp16 or bf16 only (dtype %d)", dtype);
@@ -834,8 +806,12 @@ int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan, siz
     if (inw % 16 || outw % 16 || inw > 1024 || outw > 256)
         PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr_planned: channel counts must be multiples of 16, output width at most 256 (C=%d M=%d)", C, M);
     if (!d_weight || !d_plan || !d_out || (T > 0 && !d_feat)) PCX_FAIL(PCX_E_ARG, "pcx_mvmr_planned: null pointer");
-    if ((uintptr_t)d_weight % 16 || (uintptr_t)d_feat % 16 || (uintptr_t)d_out % 16 || (uintptr_t)d_plan % 256)
-        PCX_FAIL(PCX_E_ALIGN, "pcx_mvmr_planned: weight, features and output must be 16-byte aligned, the plan 256-byte aligned");
+    if ((uintptr_t)d_weight % 16 || (uintptr_t)d_feat % 16 || (uintptr_t)d_out % 16 || (uintptr_t)d_plan % 256 || (uintptr_t)d_ws % 256)
+        PCX_FAIL(PCX_E_ALIGN, "pcx_mvmr_planned: weight, features and output must be 16-byte aligned, plan and workspace 256-byte aligned");
+    if (multi_buckets < 0 || multi_buckets > T / 2) PCX_FAIL(PCX_E_ARG, "pcx_mvmr_planned: multi_buckets out of range");
+    if (multi_buckets > 0 && (!d_ws || ws_bytes < pcx_mvmr_planned_workspace_bytes(multi_buckets, transpose ? M : C)))
+        PCX_FAIL(PCX_E_CAPACITY, "pcx_mvmr_planned: workspace %zu < %zu bytes", ws_bytes,
+                 pcx_mvmr_planned_workspace_bytes(multi_buckets, transpose ? M : C));
     PlanView pv;
     const size_t need_plan = carve_plan(d_plan, T, n_out, K, G, &pv);
     if (plan_bytes < need_plan) PCX_FAIL(PCX_E_CAPACITY, "pcx_mvmr_planned: plan buffer %zu < %zu bytes", plan_bytes, need_plan);
@@ -843,6 +819,7 @@ int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan, siz
     OsParams p = {};
     p.feat = (const uint16_t *)d_feat, p.out = (uint16_t *)d_out, p.weight = (const uint16_t *)d_weight;
     p.perm = pv.perm, p.tile_offs = pv.tile_offs, p.group_order = pv.group_order, p.entries = pv.entries, p.ctrl = pv.ctrl;
+    p.tile_rows = pv.tile_rows, p.scratch = (const uint16_t *)d_ws;
     p.status = status_word();
     if (!p.status) PCX_FAIL(PCX_E_LAUNCH, "pcx_mvmr_planned: no device status word");
     p.K = K, p.C = C, p.M = M, p.transpose = transpose ? 1 : 0, p.fmt = dtype == PCX_BF16 ? 1 : 0;
@@ -877,33 +854,37 @@ int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan, siz
 
     // Two CTAs share an SM when their accumulators fit half of the tensor memory: while one
     // writes its output rows or sets up its next group, the other keeps the tensor core and the
-    // gathers going, and two threads issue MMAs.  Shared memory per CTA: A slots and side
-    // buffers (one each per producer warp), weight slots, the group's task tables.
+    // gathers going, and two threads issue MMAs.  Shared memory per CTA: A slots, weight slots,
+    // the group's task tables.
     int ctas = p.ncols <= 256 ? 2 : 1;
     if (const char *e = getenv("PCX_OS_CTAS")) ctas = (atoi(e) == 1 || p.ncols > 256) ? 1 : 2;
     const size_t nkb = (size_t)p.nkb;
     const size_t table_fixed = align_up((size_t)G * K * nkb * 16 + ((size_t)G * K * 3 + 1 + (size_t)K * nkb) * 4, 16);
-    const size_t per_warp = SLOT_BYTES + SIDE_BYTES + SIDE_ROWS * 4, static_smem = 512;
-    int npw = 0, nw = 0;
-    for (; ctas >= 1 && !npw; --ctas) {
+    const size_t static_smem = 512;
+    int nslots = 0, nw = 0;
+    for (; ctas >= 1 && !nslots; --ctas) {
         const size_t budget = (size_t)232448 / ctas - 1024 - static_smem - 1024;
-        const int top = ctas == 2 ? 5 : MAX_NPW;
-        for (int a = top; a >= 4 && !npw; --a)
-            for (int b = (ctas == 2 ? 3 : MAX_NW); b >= 2 && !npw; --b)
-                if ((size_t)a * per_warp + (size_t)b * p.w_slot_bytes + table_fixed <= budget) npw = a, nw = b;
-        if (npw) break;
+        for (int a = MAX_SLOTS; a >= 3 && !nslots; --a)
+            for (int b = (ctas == 2 ? 3 : MAX_NW); b >= 2 && !nslots; --b)
+                if ((size_t)a * SLOT_BYTES + (size_t)b * p.w_slot_bytes + table_fixed <= budget) nslots = a, nw = b;
+        if (nslots) break;
     }
-    if (!npw) PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr_planned: shared memory does not fit (K=%d C=%d M=%d group=%d)", K, C, M, G);
+    if (!nslots) PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr_planned: shared memory does not fit (K=%d C=%d M=%d group=%d)", K, C, M, G);
+    int npw = ctas == 2 ? 4 : MAX_NPW;
     if (const char *e = getenv("PCX_OS_WARPS")) {
         const int want = atoi(e);
-        if (want >= 4 && want <= npw) npw = want;
+        if (want == 4 || want == 8) npw = want;
+    }
+    if (const char *e = getenv("PCX_OS_SLOTS")) {
+        const int want = atoi(e);
+        if (want >= 2 && want <= nslots) nslots = want;
     }
     if (const char *e = getenv("PCX_OS_WSLOTS")) {
         const int want = atoi(e);
         if (want >= 2 && want <= nw) nw = want;
     }
-    p.npw = npw, p.nw = nw;
-    const size_t smem = 1024 + (size_t)npw * per_warp + (size_t)nw * p.w_slot_bytes + table_fixed;
+    p.npw = npw, p.nslots = nslots, p.nw = nw;
+    const size_t smem = 1024 + (size_t)nslots * SLOT_BYTES + (size_t)nw * p.w_slot_bytes + table_fixed;
     static int granted[64] = {};
     int dev = 0;
     PCX_CUDA(cudaGetDevice(&dev));
@@ -913,6 +894,12 @@ int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan, siz
         granted[dev & 63] = (int)smem;
     }
     const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(pv.ngroups, (int64_t)ctas * num_sms()));
+    if (multi_buckets > 0) {
+        const int64_t threads = multi_buckets * (inw >> 3);
+        bucket_sum_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(p.feat, pv.entries, pv.buckets, pv.ctrl, inw, p.fmt,
+                                                                               (uint16_t *)d_ws);
+        PCX_LAUNCH_CHECK();
+    }
     prof_begin(transpose ? "mvmr_os_kernel(dgrad)" : "mvmr_os_kernel(fwd)", stream);
     mvmr_os_kernel<<<grid, (unsigned)(npw + 2) * 32, smem, stream>>>(tmap, p);
     prof_end(stream);
