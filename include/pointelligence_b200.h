@@ -200,6 +200,37 @@ int pcx_vvor_static_scratch(const void *d_a, const int32_t *d_a_idx, const void 
                             void *stream);
 
 /* ------------------------------------------------------------------------
+ * Residual R-net selector of the full-cover strided rulebook.
+ *
+ * Replaces layers/triplets.py:156-232 (_select_residual_full_cover_centers
+ * with its _rank_priorities): among the n points that no initial centre
+ * covers, choose centres in rounds -- a point whose priority (most active
+ * neighbours, then farthest from its stride cell's initial centre, then lowest
+ * source index) is the best of its active neighbourhood becomes a centre and
+ * retires that neighbourhood -- until no point is active.
+ *
+ *   pcx_rnet_far     d_far[v] = |points[v] - centres[centre_of[v]]|^2, one
+ *                    rounding per operation ((dx^2 + dy^2) + dz^2)
+ *   pcx_rnet_rounds  runs `rounds` (1..64) rounds on the lists d_neighbors /
+ *                    d_offsets (query-major neighbours within R, self
+ *                    included; offsets n+1), updating d_active (1 = still to be
+ *                    covered; all ones before the first call) and setting
+ *                    d_chosen[v] = 1 for new centres (zeroed by the caller).
+ *                    h_remaining[r] = active points after round r; the call
+ *                    synchronises the stream once to hand these back.  Rounds
+ *                    on an exhausted set change nothing.
+ */
+size_t pcx_rnet_workspace_bytes(int64_t n, int rounds);
+int pcx_rnet_far(const float *d_points, const float *d_centres,
+                 const int64_t *d_centre_of, int64_t n, float *d_far,
+                 void *stream);
+int pcx_rnet_rounds(const int64_t *d_neighbors, const int64_t *d_offsets,
+                    const float *d_far, const int64_t *d_source, int64_t n,
+                    int rounds, uint8_t *d_active, uint8_t *d_chosen,
+                    int32_t *h_remaining, void *d_ws, size_t ws_bytes,
+                    void *stream);
+
+/* ------------------------------------------------------------------------
  * Segment reductions (op: 0 sum, 1 mean, 2 max, 3 min; fp32 accumulation,
  * inputs, outputs and gradients all in `dtype`).
  *

@@ -73,6 +73,10 @@ SIGNATURES = {
                                                       c_size_t, c_void_p]),
     "pcx_ragged_layer_norm_backward": (c_int, [c_void_p] * 11 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
                                                                 c_size_t, c_void_p]),
+    "pcx_rnet_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "pcx_rnet_far": (c_int, [c_void_p] * 3 + [c_int64, c_void_p, c_void_p]),
+    "pcx_rnet_rounds": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_void_p, c_void_p, ctypes.POINTER(ctypes.c_int32),
+                                c_void_p, c_size_t, c_void_p]),
     "pcx_seg_offs": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "pcx_expand_taps": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "pcx_set_radius_predicate": (c_int, [c_int]),
@@ -157,6 +161,16 @@ def device_status(clear=True):
     return int(out.value)
 
 
+def raise_if_device_reported():
+    """Raise ``RuntimeError`` (PCX_E_DEVICE) if a kernel of the library gave up on one of its bounded
+    waits since the last check; its result is incomplete.  Called where the host synchronises
+    anyway (the geometry hand-overs), so that such a result cannot go unnoticed for long."""
+    status = device_status(clear=True)
+    if status:
+        raise RuntimeError(f"a kernel of the library gave up on a bounded wait (device status word {status:#x}): "
+                           "results computed since the last check are incomplete [pcx status -7]")
+
+
 def launch_count(reset=False):
     """Kernels launched by the library so far (optionally resetting the counter)."""
     return int(lib().pcx_launch_count(1 if reset else 0))
@@ -183,7 +197,8 @@ def profile_records():
 # once) needs a plan of the rulebook, built once per rulebook and direction and remembered by the
 # identity of the index tensors.  Measured on B200 it wins for rows of 128 channels and more at any
 # density and for narrower rows once a scene has about a dozen triplets per output row (the deeper
-# levels of a U-Net, dense scans); sparse narrow layers stay on the scatter kernel of ``pcx_mvmr``.
+# levels of a U-Net, dense scans); sparse narrow layers and single-tap rulebooks (nothing to keep
+# across taps) stay on the scatter kernel of ``pcx_mvmr``.
 ENGINE_PLANNED = 3
 _PLANNED_MIN_WIDTH = int(os.environ.get("PCX_PLANNED_MIN_WIDTH", "128"))     # output width from which on, at any density
 _PLANNED_MIN_RATIO = float(os.environ.get("PCX_PLANNED_MIN_RATIO", "12"))     # triplets per output row from which on
@@ -336,7 +351,7 @@ def mvmr(weight, feat, gather, scatter, seg_offs, tap_idx, n_out, transpose, eng
             raise NotImplementedError("the output-stationary engine needs fp16/bf16 features, one group, tap-sorted "
                                       "triplets, channel counts that are multiples of 16 and rows of at most 256 channels")
         outw = C if transpose else M
-        if fits and (engine == ENGINE_PLANNED or (_PLANNED_ENABLED and (
+        if fits and (engine == ENGINE_PLANNED or (_PLANNED_ENABLED and K > 1 and (
                 outw >= _PLANNED_MIN_WIDTH or gather.numel() >= _PLANNED_MIN_RATIO * n_out))):
             plan = cached_mvmr_plan(scatter, gather, seg_offs, K, n_out, plan_group_blocks(outw))
             return mvmr_planned(weight, feat, plan, transpose)
@@ -421,6 +436,9 @@ def segment_reduce(x, lengths, op):
 def segment_reduce_backward(grad_out, x, out, lengths, op, n_rows):
     require_cuda(grad_out, lengths)
     grad_out = grad_out.contiguous()
+    if op >= 2:   # max / min compare x with out: both are read row-major in the gradient's element type
+        assert x.dtype == grad_out.dtype and out.dtype == grad_out.dtype, (x.dtype, out.dtype, grad_out.dtype)
+        x, out = x.contiguous(), out.contiguous()
     lengths = lengths.to(torch.int64).contiguous()
     S, C = grad_out.shape
     grad_x = torch.empty((n_rows, C), dtype=grad_out.dtype, device=grad_out.device)
@@ -531,6 +549,39 @@ def expand_taps(seg_offs, K, T):
     return out
 
 
+def rnet_select(points, centres, centre_of, neighbors, offsets, source, rounds_per_call=4):
+    """Residual R-net over ``points`` (n, 3): returns ``(chosen bool (n,), rounds)``.
+
+    ``neighbors`` / ``offsets``: query-major neighbour lists within R (self included);
+    ``centres[centre_of[v]]`` is the initial centre of v's stride cell; ``source`` breaks ties.
+    The host sees the device once per ``rounds_per_call`` rounds."""
+    require_cuda(points, centres, centre_of, neighbors, offsets, source)
+    dev, n = points.device, points.shape[0]
+    points, centres = points.contiguous().float(), centres.contiguous().float()
+    centre_of, neighbors = centre_of.to(torch.int64).contiguous(), neighbors.to(torch.int64).contiguous()
+    offsets, source = offsets.to(torch.int64).contiguous(), source.to(torch.int64).contiguous()
+    far = torch.empty(n, dtype=torch.float32, device=dev)
+    active = torch.ones(n, dtype=torch.uint8, device=dev)
+    chosen = torch.zeros(n, dtype=torch.uint8, device=dev)
+    L = lib()
+    rounds = 0
+    with torch.cuda.device(dev):
+        check(L.pcx_rnet_far(ptr(points), ptr(centres), ptr(centre_of), n, ptr(far), stream_ptr()))
+        ws = workspace(L.pcx_rnet_workspace_bytes(n, rounds_per_call), dev)
+        remaining = (ctypes.c_int32 * rounds_per_call)()
+        for _ in range(n + 1):           # every productive round retires at least one point
+            check(L.pcx_rnet_rounds(ptr(neighbors), ptr(offsets), ptr(far), ptr(source), n, rounds_per_call,
+                                    ptr(active), ptr(chosen), remaining, ptr(ws), ws.numel(), stream_ptr()))
+            left = list(remaining)
+            if 0 in left:
+                rounds += left.index(0) + 1
+                break
+            rounds += rounds_per_call
+        else:
+            raise RuntimeError("full-cover R-net selector made no progress")
+    return chosen.bool(), rounds
+
+
 # -------------------------------------------------------------- geometry ----
 def radius_search(points, queries, radius, point_sample, query_sample, distance_type,
                   kernel_size=0, kernel_grid_size=0.0, return_distances=False, want_k=False):
@@ -556,6 +607,7 @@ def radius_search(points, queries, radius, point_sample, query_sample, distance_
                                  distance_type, kernel_size, float(kernel_grid_size), ptr(num_neighbors),
                                  ptr(seg), ctypes.byref(total), ptr(ws), ws.numel(), stream_ptr()))
         total = int(total.value)
+        raise_if_device_reported()   # the count above was a host hand-over: the stream is idle
         if kernel_size == 0:
             neighbors = torch.empty(total, dtype=torch.int64, device=dev)
             dist = torch.empty(total, dtype=torch.float32, device=dev) if return_distances else None

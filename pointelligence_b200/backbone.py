@@ -9,8 +9,8 @@ full resolution and a 1x1x1 classifier.  Differences, all stated by the benchmar
 configuration: the norm is ``RaggedLayerNorm`` (per-sample statistics, so ranks
 need no collective for it), activations and convolution operands are bf16 with
 fp32 master weights, every norm -> (+ identity) -> ReLU tail runs as one fused
-kernel (``layers.norm.fused_layer_norm``), the shortcut projection is a plain
-``Linear``, and every decoder stage rebuilds the submanifold triplets of its own
+kernel (``layers.norm.fused_layer_norm``), the shortcut projection (with its row gather at a
+stride) is a one-tap MVMR of the library instead of a ``Linear``, and every decoder stage rebuilds the submanifold triplets of its own
 cloud instead of inheriting the up-sampling layer's.
 """
 from __future__ import annotations
@@ -57,6 +57,23 @@ class Bf16PointConv3d(PointConv3d):
         return out
 
 
+def project_rows(x: Tensor, rows, weight: Tensor) -> Tensor:
+    """``x[rows] @ weight.T`` (``rows`` None: every row) as one MVMR with a single tap: the gather
+    of the strided shortcut and its projection run in the library's own tensor-core kernels, and
+    so do both gradients (VVOR for the weight, transposed MVMR for the input).  The reference
+    gathers and calls a ``Linear`` (models/resnet.py:119-130)."""
+    from .sparse_engines._dispatch_override import current_engine
+    from .sparse_engines._ops import mvmr_op
+
+    n_out = x.shape[0] if rows is None else rows.shape[0]
+    gather = (torch.arange(n_out, device=x.device, dtype=torch.int32) if rows is None
+              else rows.to(torch.int32))
+    scatter = torch.arange(n_out, device=x.device, dtype=torch.int32)
+    seg = torch.tensor([0, n_out], device=x.device, dtype=torch.int64)
+    w = weight.to(x.dtype).t().contiguous().view(1, 1, weight.shape[1], weight.shape[0])
+    return mvmr_op(w, x.contiguous(), gather, scatter, seg, None, n_out, False, current_engine())
+
+
 def _norm_act(norm: RaggedLayerNorm, x: Tensor, lengths: Tensor, residual=None, relu=True) -> Tensor:
     return fused_layer_norm(x, lengths, norm.weight, norm.bias, norm.eps, residual=residual, relu=relu)
 
@@ -84,11 +101,12 @@ class BasicBlock(nn.Module):
                 points=m.points, sample_inds=m.sample_inds, sample_sizes=m.sample_sizes,
                 neighbor_radius=m.grid_size * scaler, kernel_size=3, radius_scaler=scaler)
         x = self.conv2(x, m.i, m.j, m.k, m.num_points(), seg_offs=m.seg_offs)
-        if self.stride != 1.0:
-            identity = identity[m.downsample_indices]
+        rows = m.downsample_indices if self.stride != 1.0 else None
         if self.shortcut is not None:
-            identity = F.linear(identity, self.shortcut.weight.to(identity.dtype))
+            identity = project_rows(identity, rows, self.shortcut.weight)
             identity = _norm_act(self.shortcut_norm, identity, m.sample_sizes, relu=False)
+        elif rows is not None:
+            identity = identity[rows]
         return _norm_act(self.bn2, x, m.sample_sizes, residual=identity), m
 
     def _strided(self, x, m):

@@ -53,6 +53,19 @@ struct Carver {
     }
 };
 
+// Product of non-negative sizes; false when a factor is negative or the product exceeds `limit`
+// (checked factor by factor, so it cannot wrap on the way).
+static inline bool product_within(uint64_t limit, uint64_t *out, int64_t a, int64_t b = 1, int64_t c = 1, int64_t d = 1) {
+    const int64_t f[4] = {a, b, c, d};
+    uint64_t p = 1;
+    for (int i = 0; i < 4; ++i) {
+        if (f[i] < 0) return false;
+        if (__builtin_mul_overflow(p, (uint64_t)f[i], &p) || p > limit) return false;
+    }
+    *out = p;
+    return true;
+}
+
 static inline size_t elem_size(int dtype) { return dtype == PCX_F32 ? 4 : 2; }
 
 template <typename T>

@@ -1,6 +1,8 @@
 // extern "C" entry points of the sparse engines: argument checks, workspace
 // carving, engine selection (tcgen05 tensor path vs CUDA-core path) and the
 // single rounding of the fp32 accumulator into the output element type.
+#include <algorithm>
+
 #include "sparse_kernels.cuh"
 
 namespace pcx {
@@ -56,6 +58,8 @@ extern "C" {
 
 size_t pcx_mvmr_workspace_bytes(int64_t n_out, int K, int G, int C, int M, int transpose, int dtype) {
     if (n_out < 0 || K <= 0 || G <= 0 || C <= 0 || M <= 0) return 0;
+    uint64_t checked = 0;
+    if (!product_within((uint64_t)1 << 46, &checked, n_out, G, std::max(C, M))) return 0;
     return carve_mvmr(nullptr, n_out, K, G, C, M, transpose, dtype, nullptr);
 }
 
@@ -74,6 +78,10 @@ int pcx_mvmr(const void *d_weight, const void *d_feat, const int32_t *d_gather, 
     if (T > 0 && !d_seg_offs && !d_tap_idx) PCX_FAIL(PCX_E_ARG, "pcx_mvmr: either d_seg_offs or d_tap_idx is required");
     if ((uintptr_t)d_ws % 256) PCX_FAIL(PCX_E_ALIGN, "pcx_mvmr: workspace must be 256-byte aligned");
     if (n_feat > INT32_MAX || n_out > INT32_MAX) PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr: more than 2^31-1 rows");
+    uint64_t checked = 0;
+    if (!product_within((uint64_t)1 << 46, &checked, n_out, G, std::max(C, M)) ||
+        !product_within((uint64_t)1 << 46, &checked, K, G, C, M))
+        PCX_FAIL(PCX_E_CAPACITY, "pcx_mvmr: n_out*G*width or K*G*C*M is beyond 2^46 elements");
     MvmrWs w;
     size_t need = carve_mvmr(d_ws, n_out, K, G, C, M, transpose, dtype, &w);
     if (ws_bytes < need) PCX_FAIL(PCX_E_CAPACITY, "pcx_mvmr: workspace %zu < %zu bytes", ws_bytes, need);
@@ -103,6 +111,8 @@ int pcx_mvmr(const void *d_weight, const void *d_feat, const int32_t *d_gather, 
 
 size_t pcx_vvor_workspace_bytes(int64_t n_o, int G, int Ma, int Cb, int dtype) {
     if (n_o < 0 || G <= 0 || Ma <= 0 || Cb <= 0) return 0;
+    uint64_t checked = 0;
+    if (!product_within((uint64_t)1 << 46, &checked, n_o, G, Ma, Cb)) return 0;
     return carve_vvor(nullptr, n_o, G, Ma, Cb, dtype, nullptr);
 }
 
@@ -120,6 +130,9 @@ int pcx_vvor(const void *d_a, const int32_t *d_a_idx, const void *d_b, const int
     if (T > 0 && !d_seg_offs && !d_o_idx) PCX_FAIL(PCX_E_ARG, "pcx_vvor: either d_seg_offs or d_o_idx is required");
     if ((uintptr_t)d_ws % 256) PCX_FAIL(PCX_E_ALIGN, "pcx_vvor: workspace must be 256-byte aligned");
     if (n_a > INT32_MAX || n_b > INT32_MAX || n_o > INT32_MAX) PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_vvor: more than 2^31-1 rows");
+    uint64_t checked = 0;
+    if (!product_within((uint64_t)1 << 46, &checked, n_o, G, Ma, Cb))
+        PCX_FAIL(PCX_E_CAPACITY, "pcx_vvor: n_o*G*Ma*Cb is beyond 2^46 elements");
     VvorWs w;
     size_t need = carve_vvor(d_ws, n_o, G, Ma, Cb, dtype, &w);
     if (ws_bytes < need) PCX_FAIL(PCX_E_CAPACITY, "pcx_vvor: workspace %zu < %zu bytes", ws_bytes, need);

@@ -73,12 +73,12 @@ int pcx_vvor_static_scratch(const void *d_a, const int32_t *d_a_idx, const void 
     if (!d_out || !d_seg_offs) PCX_FAIL(PCX_E_ARG, "pcx_vvor_static_scratch: d_out and d_seg_offs are required");
     if (T > 0 && (!d_a || !d_b || !d_a_idx || !d_b_idx)) PCX_FAIL(PCX_E_ARG, "pcx_vvor_static_scratch: null pointer");
     if (n_a > INT32_MAX || n_b > INT32_MAX) PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_vvor_static_scratch: more than 2^31-1 rows");
-    const size_t out_elems = (size_t)n_o * G * Ma * Cb;
-    if ((size_t)n_o > kMaxOutputs || out_elems > kMaxAccumulatorFloats)
+    uint64_t out_elems = 0;   // checked factor by factor: a product that wraps must not pass for a small one
+    if ((size_t)n_o > kMaxOutputs || !product_within(kMaxAccumulatorFloats, &out_elems, n_o, G, Ma, Cb))
         PCX_FAIL(PCX_E_CAPACITY,
-                 "pcx_vvor_static_scratch: output of %zu elements over %lld rows exceeds the built-in scratch "
+                 "pcx_vvor_static_scratch: output of %lld x %d x %d x %d elements exceeds the built-in scratch "
                  "(at most %zu elements and %zu rows); use pcx_vvor with a caller-owned workspace",
-                 out_elems, (long long)n_o, kMaxAccumulatorFloats, kMaxOutputs);
+                 (long long)n_o, G, Ma, Cb, kMaxAccumulatorFloats, kMaxOutputs);
     void *scratch = nullptr;
     int rc = static_scratch_address(&scratch);
     if (rc != PCX_OK) return rc;

@@ -1,13 +1,14 @@
 """Normalisation layers for ragged batches (samples of different length stored
 back to back).
 
-Mirror of the reference's ``layers/norm.py:12-172``: ``RaggedNorm`` with its
-four wrappers, the same constructor arguments, the same fp32 arithmetic with a
-cast back to the input type, the same two-pass statistics (mean, then variance
-of the centred values).  The per-sample reductions run through the library's
-segment reduction (the reference defaults to ``torch.segment_reduce`` and lets
-a caller plug ``large_segment_reduce`` in as ``reduce_fn``, :22-57; here the
-library kernel is the default and ``reduce_fn`` still overrides it).
+Stand in for the reference's ``layers/norm.py:12-172``: ``RaggedNorm`` and its four wrappers
+with the same constructor arguments and the same arithmetic (fp32, mean first, then the variance
+of the centred values, cast back to the input type).  Layer norm on CUDA runs as the library's
+fused kernels; the other per-sample norms share one code path that treats layer / group /
+instance as the same computation over (groups, width) views, with the per-sample sums done by
+the library's segment reduction (the reference defaults to ``torch.segment_reduce`` and lets a
+caller plug ``large_segment_reduce`` in as ``reduce_fn``, :22-57; ``reduce_fn`` still overrides
+the library kernel here, and is called with ``reduce="sum"``).
 """
 from __future__ import annotations
 
@@ -74,53 +75,44 @@ class RaggedNorm(nn.Module):
             self.register_parameter("weight", None)
             self.register_parameter("bias", None)
 
-    def _reduce(self, x, reduce_op, lengths):
+    def _segment_sum(self, x, lengths):
         fn = self.reduce_fn if self.reduce_fn is not None else large_segment_reduce
-        return fn(x, reduce=reduce_op, lengths=lengths)
+        return fn(x, reduce="sum", lengths=lengths)
+
+    def _groups(self):
+        """Statistics groups per sample: the three per-sample norms differ only in how the channels
+        are pooled -- all of them (layer), ``num_groups`` blocks (group), or none (instance)."""
+        if self.norm_type == "layer":
+            return 1
+        if self.norm_type == "group":
+            return self.num_groups
+        if self.norm_type == "instance":
+            return self.num_features
+        raise ValueError(f"Unknown norm_type: {self.norm_type}")
 
     def forward(self, x, lengths=None):
         input_dtype = x.dtype
         if self.norm_type == "batch":
             return self.bn(x.float()).to(input_dtype)
+        groups = self._groups()
         if lengths is None:
             raise ValueError(f"lengths argument is required for {self.norm_type} norm")
         if self.norm_type == "layer" and self.reduce_fn is None and x.is_cuda:
             return fused_layer_norm(x, lengths, self.weight, self.bias, self.eps)
-        x = x.float()
-        if self.norm_type == "instance":
-            x_norm = self._instance_norm(x, lengths)
-        elif self.norm_type == "group":
-            x_norm = self._group_norm(x, lengths)
-        elif self.norm_type == "layer":
-            x_norm = self._layer_norm(x, lengths)
-        else:
-            raise ValueError(f"Unknown norm_type: {self.norm_type}")
+        # fp32, two passes (mean, then variance of the centred values) as layers/norm.py:86-130 of
+        # the reference; one code path for the three norms: rows are viewed as (groups, width),
+        # every pass is a per-row sum over the width followed by one segment sum over the sample
+        n, width = x.shape[0], self.num_features // groups
+        rows = x.float().view(n, groups, width)
+        sample = torch.repeat_interleave(torch.arange(lengths.numel(), device=x.device), lengths, output_size=n)
+        count = (lengths.to(torch.float32) * width).clamp_min(1.0).unsqueeze(1)
+        mean = self._segment_sum(rows.sum(dim=2), lengths) / count                     # (samples, groups)
+        centred = rows - mean[sample].unsqueeze(2)
+        var = self._segment_sum(centred.square().sum(dim=2), lengths) / count
+        out = (centred * torch.rsqrt(var + self.eps)[sample].unsqueeze(2)).view(n, self.num_features)
         if self.affine:
-            x_norm = x_norm * self.weight.float() + self.bias.float()
-        return x_norm.to(input_dtype)
-
-    def _expand(self, per_sample, lengths):
-        return torch.repeat_interleave(per_sample, lengths, dim=0)
-
-    def _instance_norm(self, x, lengths):
-        centred = x - self._expand(self._reduce(x, "mean", lengths), lengths)
-        var = self._reduce(centred.pow(2), "mean", lengths)
-        return centred / self._expand((var + self.eps).sqrt(), lengths)
-
-    def _group_norm(self, x, lengths):
-        per_group = self.num_features // self.num_groups
-        xg = x.view(x.size(0), self.num_groups, per_group)
-        mean = self._reduce(xg.mean(dim=2), "mean", lengths)
-        centred = xg - self._expand(mean, lengths).unsqueeze(2)
-        var = self._reduce(centred.pow(2).mean(dim=2), "mean", lengths)
-        std = self._expand((var + self.eps).sqrt(), lengths).unsqueeze(2)
-        return (centred / std).view(x.size(0), self.num_features)
-
-    def _layer_norm(self, x, lengths):
-        mean = self._reduce(x.mean(dim=1, keepdim=True), "mean", lengths)
-        centred = x - self._expand(mean, lengths)
-        var = self._reduce(centred.pow(2).mean(dim=1, keepdim=True), "mean", lengths)
-        return centred / self._expand((var + self.eps).sqrt(), lengths)
+            out = out * self.weight.float() + self.bias.float()
+        return out.to(input_dtype)
 
 
 class RaggedBatchNorm(RaggedNorm):

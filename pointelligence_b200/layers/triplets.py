@@ -276,44 +276,21 @@ def _edges(points, sample_inds, centers, center_sample, radius, backend):
 
 
 def _residual_net(points, sample_inds, c0_points, point_to_c0, uncovered, radius, backend):
-    """Deterministic maximal R-net over the points no initial centre covers.
+    """Deterministic maximal R-net over the points no initial centre covers (the device selector
+    ``pcx_rnet_rounds``; the reference's host loop is layers/triplets.py:156-232).  Returns the
+    chosen source indices ordered by (sample, index) and the number of rounds."""
+    from .. import _cabi
 
-    Rounds: every still-active point gets a priority (most active neighbours
-    first, then farthest from its cell's initial centre, then lowest index); a
-    point whose priority is the best of its active neighbourhood becomes a
-    centre and retires that neighbourhood."""
-    dev = points.device
     src = torch.nonzero(uncovered).squeeze(1)
     if src.numel() == 0:
-        return torch.empty(0, dtype=torch.long, device=dev), 0
+        return torch.empty(0, dtype=torch.long, device=points.device), 0
     up, us = points[src], sample_inds[src]
-    q, p, _ = _edges(up, us, up, us, radius, backend)
-    far = torch.sum((up - c0_points[point_to_c0[src]]).square(), dim=1)
-    n = src.numel()
-    active = torch.ones(n, dtype=torch.bool, device=dev)
-    chosen, rounds = [], 0
-    while bool(active.any().item()):
-        live = active[q] & active[p]
-        gain = torch.zeros(n, dtype=torch.long, device=dev)
-        gain.index_add_(0, q[live], torch.ones(int(live.sum().item()), dtype=torch.long, device=dev))
-        order = torch.argsort(src, stable=True)
-        order = order[torch.argsort(-far[order], stable=True)]
-        order = order[torch.argsort(-gain[order], stable=True)]
-        rank = torch.empty_like(order)
-        rank[order] = torch.arange(n, device=dev)
-        nb_rank = torch.where(active[p], rank[p], torch.full_like(p, n + 1))
-        best = torch.full((n,), n + 1, dtype=torch.long, device=dev)
-        best.scatter_reduce_(0, q, nb_rank, reduce="amin", include_self=True)
-        pick = active & (rank == best)
-        if not bool(pick.any().item()):
-            raise RuntimeError("full-cover R-net selector made no progress")
-        chosen.append(src[pick])
-        retire = pick[q] & active[p]
-        active[p[retire]] = False
-        rounds += 1
-    added = torch.cat(chosen)
-    order = torch.argsort(sample_inds[added] * (points.shape[0] + 1) + added, stable=True)
-    return added[order], rounds
+    _, nb, counts = _edges(up, us, up, us, radius, backend)
+    offsets = torch.zeros(src.numel() + 1, dtype=torch.int64, device=points.device)
+    torch.cumsum(counts, 0, out=offsets[1:])
+    chosen, rounds = _cabi.rnet_select(up, c0_points, point_to_c0[src], nb, offsets, src)
+    added = src[chosen]      # ascending source index; stable by sample below
+    return added[torch.argsort(sample_inds[added], stable=True)], rounds
 
 
 @torch.compiler.disable

@@ -67,7 +67,9 @@ _large_op.register_autograd(_large_backward, setup_context=_large_setup)
 
 def large_segment_reduce(x, reduce, *, lengths):
     """``out[s] = reduce`` of the ``lengths[s]`` consecutive rows of ``x`` (N, C) -> (S, C) in ``x.dtype``."""
-    return _large_op(x, lengths, _op_code(reduce))
+    # contiguous here, not inside the operator: the tensor saved for the max / min gradient must be
+    # the one the kernel read (a column slice or a transposed view has another memory layout)
+    return _large_op(x.contiguous(), lengths, _op_code(reduce))
 
 
 @torch.library.custom_op(f"{_NS}::indexed_segment_reduce", mutates_args=())

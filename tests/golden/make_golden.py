@@ -22,6 +22,12 @@ What runs, per file:
 ``voxelize.npz``     ``layers.triplets.voxelize_3d`` and the scalar formulas.
 ``sparse.npz``       the reference's CPU MVMR / VVOR operators compiled from
     its C++ sources (oracle/build_ref.py).
+``full_cover.npz``   ``layers.triplets.build_full_cover_strided_rulebook`` on CPU tensors.  Its body is
+    plain torch except for ``radius_search`` (a Triton launch); that one name is pointed at the
+    numpy restatement of the search (``oracle/geometry.py``, one rounding per operation like the
+    interpreter), everything else -- centre choice, residual R-net selector, ordering, taps -- is
+    the reference's own code.  Inputs: the fixture of tests/unittest/test_full_cover_strided.py:52-120
+    and a two-sample synthetic scene with enough uncovered points to need the residual selector.
 ``segment.npz``      ``sparse_engines.ops.large_segment_reduce`` and
     ``indexed_segment_reduce`` (Triton kernels under the interpreter, forward
     and autograd backward) and ``layers.norm.Ragged{Layer,Instance,Group}Norm``
@@ -236,6 +242,55 @@ def gen_sparse(torch, out):
         out[f"{name}.vvor"] = sparse_ops.vvor_ref(b, bi, go, oi, ai, K)
 
 
+def gen_full_cover(torch, out):
+    sys.path.insert(0, ROOT)
+    import layers.triplets as rt
+    from oracle import geometry as og
+    from pointelligence_b200.synthetic import indoor_scene, ragged_batch
+
+    def restated_radius_search(points, query_points, radius, sample_inds=None, query_sample_inds=None, **_):
+        nb, counts = og.radius_search_sorted_grid8(
+            points.numpy(), query_points.numpy(), float(radius),
+            None if sample_inds is None else sample_inds.numpy(),
+            None if query_sample_inds is None else query_sample_inds.numpy())
+        return torch.from_numpy(nb), torch.from_numpy(counts)
+
+    rt.radius_search = restated_radius_search
+    p0 = torch.tensor([[0.001, 0.001, 0.001], [0.399, 0.399, 0.399], [0.401, 0.001, 0.001], [0.799, 0.399, 0.399]])
+    cases = {"fixture": (torch.cat([p0, p0 + torch.tensor([2.0, 0.0, 0.0])]),
+                         torch.cat([torch.zeros(4, dtype=torch.long), torch.ones(4, dtype=torch.long)]), 8, 0.05, 15)}
+    pts, inds, _ = ragged_batch([indoor_scene(3000, 5), indoor_scene(2000, 6)])
+    cases["scene"] = (torch.from_numpy(pts), torch.from_numpy(inds).long(), 2, 0.02, 5)
+    # a slab whose points avoid the middle of every stride cell: the initial centres sit off-centre,
+    # their balls miss the far corners, thousands of points stay uncovered and the residual selector
+    # runs for several rounds (past its 2048-point dense branch, i.e. through radius_search)
+    g = torch.Generator().manual_seed(9)
+    slab = torch.rand(40000, 3, generator=g) * torch.tensor([2.0, 2.0, 0.16])
+    cell = 8 * 0.02
+    off = slab[:, :2] - (torch.floor(slab[:, :2] / cell) + 0.5) * cell
+    slab = slab[off.norm(dim=1) > 0.07]
+    cases["hollow_cells"] = (slab, (torch.arange(slab.shape[0]) >= slab.shape[0] // 2).long(), 8, 0.02, 15)
+    for name, (points, sample, stride, grid, ks) in cases.items():
+        rb = rt.build_full_cover_strided_rulebook(points, sample, torch.bincount(sample), stride=stride,
+                                                  input_grid_size=grid, kernel_size=ks)
+        n, nc = points.shape[0], rb.points.shape[0]
+        out[f"{name}.points"], out[f"{name}.sample_inds"] = points.numpy(), sample.numpy()
+        out[f"{name}.stride"], out[f"{name}.grid"], out[f"{name}.kernel_size"] = np.float64(stride), np.float64(grid), np.int64(ks)
+        for f in ("center_source_indices", "initial_center_source_indices", "additional_center_source_indices",
+                  "point_to_initial_center", "num_neighbors", "coverage_per_input", "initial_center_counts",
+                  "additional_center_counts", "sample_sizes"):
+            out[f"{name}.{f}"] = getattr(rb, f).numpy().astype(np.int64)
+        out[f"{name}.radius"] = np.float64(rb.radius)
+        out[f"{name}.rounds"] = np.int64(rb.selector_round_count)
+        # edges in canonical order (the order inside a tap is unspecified)
+        key = (rb.k.long() * nc + rb.i.long()) * n + rb.j.long()
+        out[f"{name}.edges"] = torch.sort(key).values.numpy()
+        key = (rb.k_upsample.long() * n + rb.i_upsample.long()) * nc + rb.j_upsample.long()
+        out[f"{name}.edges_upsample"] = torch.sort(key).values.numpy()
+        print(name, "centres", nc, "initial", rb.initial_center_source_indices.numel(), "added",
+              rb.additional_center_source_indices.numel(), "rounds", rb.selector_round_count, "edges", rb.i.numel())
+
+
 def gen_segment(torch, out):
     """Segment reductions (Triton kernels under the interpreter, forward and
     autograd backward) and the ragged norm layers (plain torch on CPU)."""
@@ -308,7 +363,7 @@ def main():
 
     _patch_libdevice()
     gens = dict(downsample=gen_downsample, radius=gen_radius, voxelize=gen_voxelize,
-                sparse=gen_sparse, segment=gen_segment)
+                sparse=gen_sparse, segment=gen_segment, full_cover=gen_full_cover)
     for name, fn in gens.items():
         if args.only and name not in args.only.split(","):
             continue

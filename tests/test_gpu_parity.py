@@ -455,6 +455,70 @@ def test_full_cover_rulebook_fixture():
     assert torch.equal(torch.bincount(rb.i.long(), minlength=nc), rb.num_neighbors)
 
 
+@pytest.mark.parametrize("sort_by", ["k", "i", "j"])
+def test_generic_build_triplets_against_oracle(sort_by):
+    """The generic builder (query-major search, tap from a caller-supplied indexer, global sort;
+    layers/triplets.py:686-764 of the reference): its triplet set equals the oracle's canonical
+    set for the library's own ``voxelize_3d`` indexer and for a custom one, it is ordered by the
+    requested column, and the per-query counts are the oracle's."""
+    from functools import partial
+
+    from pointelligence_b200.layers.triplets import build_triplets, voxelize_3d
+    from pointelligence_b200.synthetic import indoor_scene, ragged_batch
+
+    pts, inds, sizes = ragged_batch([indoor_scene(3000, 11), indoor_scene(2000, 12)])
+    qp, qi, _, _ = og.grid_sample_center_nearest(pts, 0.04, inds)           # a separate, coarser query set
+    qsizes = np.bincount(qi, minlength=2)
+    radius, scaler = 0.06, 2.0
+
+    def octant(points, grid_size):   # a custom indexer: the octant of the offset (8 taps)
+        return ((points[:, 0] > 0).long() * 2 + (points[:, 1] > 0).long()) * 2 + (points[:, 2] > 0).long()
+
+    onb, ocnt = og.radius_search_sorted_grid8(pts, qp, radius, inds, qi, fma=True)
+    oi = np.repeat(np.arange(len(qp)), ocnt)
+    off = pts[onb] - qp[oi]
+    for indexer, taps, ok in ((partial(voxelize_3d, 3), 27, og.voxelize_3d(3, off, radius / scaler)),
+                              (octant, 8, ((off[:, 0] > 0) * 2 + (off[:, 1] > 0)) * 2 + (off[:, 2] > 0))):
+        i, j, k, cnt = build_triplets(_t(pts), _t(inds), _t(sizes), radius, indexer, query_points=_t(qp),
+                                      query_sample_inds=_t(qi), query_sample_sizes=_t(qsizes), sort_by=sort_by,
+                                      return_num_neighbors=True, radius_scaler=scaler)
+        assert i.dtype == torch.int32 and j.dtype == torch.int32 and k.dtype == torch.int32
+        assert np.array_equal(cnt.cpu().numpy(), ocnt)
+        got = og.canonical_triplet_keys(i.cpu().numpy(), j.cpu().numpy(), k.cpu().numpy(), len(qp), len(pts))
+        want = og.canonical_triplet_keys(oi, onb, np.asarray(ok), len(qp), len(pts))
+        assert np.array_equal(got, want), (sort_by, taps)
+        col = {"i": i, "j": j, "k": k}[sort_by]
+        assert torch.all(col[1:] >= col[:-1])
+
+
+def test_full_cover_rulebook_matches_reference_golden(golden):
+    """The centres, their order, the per-point bookkeeping and both edge sets equal what the
+    reference's own ``build_full_cover_strided_rulebook`` produces on the same inputs (run on CPU
+    with its radius search pointed at the restated one; ``tests/golden/make_golden.py``): the
+    unit-test fixture, a two-sample scene, and a cloud whose residual selector runs for several
+    rounds.  The order of edges inside a tap is unspecified, so edges are compared sorted."""
+    from pointelligence_b200.internals.neighbors import radius_predicate
+    from pointelligence_b200.layers import build_full_cover_strided_rulebook
+
+    z = golden("full_cover")
+    for name in _cases(z):
+        pts, si = _t(z[f"{name}.points"]), _t(z[f"{name}.sample_inds"])
+        with radius_predicate("ieee"):   # the golden search rounds once per operation
+            rb = build_full_cover_strided_rulebook(pts, si, torch.bincount(si), stride=float(z[f"{name}.stride"]),
+                                                   input_grid_size=float(z[f"{name}.grid"]),
+                                                   kernel_size=int(z[f"{name}.kernel_size"]))
+        for f in ("center_source_indices", "initial_center_source_indices", "additional_center_source_indices",
+                  "point_to_initial_center", "num_neighbors", "coverage_per_input", "initial_center_counts",
+                  "additional_center_counts", "sample_sizes"):
+            assert np.array_equal(getattr(rb, f).cpu().numpy().astype(np.int64), z[f"{name}.{f}"]), (name, f)
+        assert rb.radius == float(z[f"{name}.radius"]) and rb.selector_round_count == int(z[f"{name}.rounds"]), name
+        n, nc = pts.shape[0], rb.points.shape[0]
+        edges = torch.sort((rb.k.long() * nc + rb.i.long()) * n + rb.j.long()).values
+        assert np.array_equal(edges.cpu().numpy(), z[f"{name}.edges"]), name
+        up = torch.sort((rb.k_upsample.long() * n + rb.i_upsample.long()) * nc + rb.j_upsample.long()).values
+        assert np.array_equal(up.cpu().numpy(), z[f"{name}.edges_upsample"]), name
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_conv_with_stride_full_cover_on_scene(dtype):
     """Stride 2 needs a 5x5x5 kernel (125 taps); centres cover every input and

@@ -125,24 +125,44 @@ def test_planned_engine_against_oracle(case, monkeypatch):
     assert _cabi.device_status() == 0
 
 
-def test_planned_engine_agrees_with_scatter_engine_and_is_chosen_for_wide_or_dense_layers():
+def _kernels_of(fn):
+    """Labels of the dominant kernels the library launched during ``fn()``."""
     from pointelligence_b200 import _cabi
+
+    _cabi.profile_enable(True)
+    try:
+        out = fn()
+        torch.cuda.synchronize()
+        names = [name for name, _ in _cabi.profile_records()]
+    finally:
+        _cabi.profile_enable(False)
+    return out, names
+
+
+def test_automatic_engine_takes_the_planned_kernel_for_wide_or_dense_layers():
+    from pointelligence_b200 import _cabi
+
+    def close(a, b):   # the scatter engine adds in fp32 in an order that varies from run to run
+        return float((a.float() - b.float()).norm() / b.float().norm()) < 1e-2
 
     i, j, k, seg = _rulebook(3, 900, 800, 27, 30000)          # 37 triplets per output row
     w = torch.randn(27, 1, 64, 64, device=DEV).bfloat16() / 8
     x = torch.randn(900, 64, device=DEV).bfloat16()
     ti, tj, tseg = _t(i), _t(j), _t(seg)
-    auto = _cabi.mvmr(w, x, tj, ti, tseg, None, 800, False)
+    auto, names = _kernels_of(lambda: _cabi.mvmr(w, x, tj, ti, tseg, None, 800, False))
+    assert names == ["mvmr_os_kernel(fwd)"]                    # dense neighbourhood
     forced = _cabi.mvmr(w, x, tj, ti, tseg, None, 800, False, engine=_cabi.ENGINE_PLANNED)
-    scatter = _cabi.mvmr(w, x, tj, ti, tseg, None, 800, False, engine=_cabi.ENGINE_TENSOR)
-    assert torch.equal(auto, forced)                           # dense neighbourhood: planned engine
-    assert float((auto.float() - scatter.float()).norm() / scatter.float().norm()) < 1e-2
-    i, j, k, seg = _rulebook(4, 4000, 4000, 27, 12000, dup=0.0)   # 3 triplets per row, 64 channels: scatter engine
+    scatter, names = _kernels_of(lambda: _cabi.mvmr(w, x, tj, ti, tseg, None, 800, False, engine=_cabi.ENGINE_TENSOR))
+    assert names == ["mvmr_tc_kernel(fwd)"] and torch.equal(auto, forced) and close(auto, scatter)
+    i, j, k, seg = _rulebook(4, 4000, 4000, 27, 12000, dup=0.0)   # 3 triplets per row
     ti, tj, tseg = _t(i), _t(j), _t(seg)
     x = torch.randn(4000, 64, device=DEV).bfloat16()
-    auto = _cabi.mvmr(w, x, tj, ti, tseg, None, 4000, False)
-    scatter = _cabi.mvmr(w, x, tj, ti, tseg, None, 4000, False, engine=_cabi.ENGINE_TENSOR)
-    assert torch.equal(auto, scatter)
+    _, names = _kernels_of(lambda: _cabi.mvmr(w, x, tj, ti, tseg, None, 4000, False))
+    assert names == ["mvmr_tc_kernel(fwd)"]                    # sparse and 64 channels wide: scatter engine
+    w128 = torch.randn(27, 1, 64, 128, device=DEV).bfloat16() / 8
+    out, names = _kernels_of(lambda: _cabi.mvmr(w128, x, tj, ti, tseg, None, 4000, False))
+    assert names == ["mvmr_os_kernel(fwd)"]                    # 128 channels wide: planned engine at any density
+    assert close(out, _cabi.mvmr(w128, x, tj, ti, tseg, None, 4000, False, engine=_cabi.ENGINE_TENSOR))
     with pytest.raises(NotImplementedError):                   # fp32 has no tensor-core engine
         _cabi.mvmr(w.float(), x.float(), tj, ti, tseg, None, 4000, False, engine=_cabi.ENGINE_PLANNED)
 
@@ -177,5 +197,14 @@ def test_bounded_wait_that_runs_out_is_reported():
     torch.cuda.synchronize()
     assert _cabi.device_status() == 8
     assert _cabi.device_status() == 0
+    # the host-side wrappers notice it at their next hand-over: the geometry stage raises
+    from pointelligence_b200.internals.neighbors import radius_search_sorted_grid8
+
+    _cabi.debug_wait_runs_out(1_000_000)
+    pts = torch.rand(64, 3, device=DEV)
+    with pytest.raises(RuntimeError, match="gave up on a bounded wait"):
+        radius_search_sorted_grid8(pts, pts, 0.2)
+    assert _cabi.device_status() == 0
+    radius_search_sorted_grid8(pts, pts, 0.2)
     with pytest.raises(ValueError):
         _cabi.debug_wait_runs_out(10 ** 12)

@@ -92,6 +92,33 @@ def test_large_segment_reduce_against_oracle(dtype, C):
         _close(xr.grad, seg.large_segment_reduce_grad(gn, xn, got_out, lengths, op), TOL[dtype], op + " grad")
 
 
+@pytest.mark.parametrize("op", ["max", "min"])
+def test_large_segment_reduce_gradient_of_a_column_slice(op):
+    """max / min gradients of a non-contiguous input (a column slice of a wider matrix): the
+    backward must compare against the values the forward read, not against the wider rows."""
+    from pointelligence_b200.sparse_engines.ops import large_segment_reduce
+
+    rng = np.random.default_rng(2)
+    lengths = np.array([40, 0, 300, 7])
+    wide = _t(np.round(rng.standard_normal((lengths.sum(), 96)) * 4) / 4, torch.float32).requires_grad_(True)
+    go = _t(rng.standard_normal((len(lengths), 64)), torch.float32)
+    y = large_segment_reduce(wide[:, :64], op, lengths=_t(lengths))
+    y.backward(go)
+    ref = wide.detach().clone().requires_grad_(True)
+    want = torch.segment_reduce(ref[:, :64].contiguous(), op, lengths=_t(lengths), unsafe=True)
+    ok = torch.isfinite(want)                     # the empty segment reduces to +-inf in torch
+    assert torch.equal(y[ok], want[ok])
+    torch.where(ok, want, torch.zeros_like(want)).backward(go)
+    # torch splits the gradient among ties, the reference (and this library) gives it to every
+    # tied row: compare where the extreme value is unique
+    xs = wide.detach()[:, :64]
+    seg_id = torch.repeat_interleave(torch.arange(len(lengths), device=xs.device), _t(lengths))
+    hit = xs == y.detach()[seg_id]
+    unique = (torch.zeros_like(y).index_add_(0, seg_id, hit.float()) == 1)[seg_id]
+    assert torch.allclose(wide.grad[:, :64][unique], ref.grad[:, :64][unique])
+    assert torch.all(wide.grad[:, 64:] == 0)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_max_pool3d_and_global_pool_on_scene(dtype):
     from pointelligence_b200.layers import GlobalPool, MetaData, max_pool3d

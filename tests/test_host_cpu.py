@@ -235,3 +235,68 @@ def test_block_layers_construct_on_cpu_and_fail_loudly_without_cuda():
     net = ResUNet(in_channels=3, num_classes=20)
     assert sum(p.numel() for p in net.parameters()) == 22_834_100
     assert net.conv1.weight.shape == (125, 1, 3, 32) and net.final_conv.weight.shape == (1, 1, 96, 20)
+
+
+def test_size_products_that_would_wrap_are_rejected_before_any_launch():
+    """n_o * G * Ma * Cb is checked factor by factor: a product that wraps around 2^64 must not
+    pass for a small one (the static-scratch entry would then write far past its built-in array).
+    The check comes before any CUDA call, so it runs without a GPU; the pointers are never read."""
+    import ctypes
+
+    from pointelligence_b200 import _cabi
+
+    L = _cabi.lib()
+    fake = ctypes.c_void_p(4096)
+    big = 1 << 21                                   # 4095 * 2^63 wraps to a multiple of 2^63 modulo 2^64
+    rc = L.pcx_vvor_static_scratch(None, None, None, None, fake, fake, 0, 0, 0, 4095, big, big, big, _cabi.PCX_BF16, None)
+    assert rc == -4 and b"exceeds the built-in scratch" in L.pcx_last_error_string()
+    assert L.pcx_vvor_workspace_bytes(4095, big, big, big, _cabi.PCX_BF16) == 0
+    assert L.pcx_mvmr_workspace_bytes(1 << 40, 27, big, big, big, 0, _cabi.PCX_BF16) == 0
+    rc = L.pcx_vvor(None, None, None, None, fake, None, fake, 0, 0, 0, 4095, big, big, big, _cabi.PCX_BF16, 0, fake, 256,
+                    None)
+    assert rc == -4
+
+
+def test_reference_style_imports_and_operator_namespace():
+    """After ``compat.install()`` the reference's import lines resolve to this library and the
+    three operators exist under ``sparse_engines::`` with the reference's schemas
+    (sparse_engines/tig.py:1508-1515, mvmr_triton.py:145-152, vvor_triton.py:113-120).  Runs in
+    a child interpreter: the aliases are process-wide."""
+    code = r"""
+import torch
+import pointelligence_b200.compat as compat
+compat.install(); compat.install()
+from sparse_engines.ops import (sparse_matrix_vector_multiplication_reduction,
+                                sparse_vector_vector_outer_product_reduction)
+from sparse_engines.tig import TigIndex, tig_forward, tig_grad_input, tig_grad_weight, tig_mvmr
+from sparse_engines._dispatch_override import current_mode, dispatch_mode, precision_mode
+from layers import (MetaData, PointConv3d, TripletContract, build_triplets, build_triplets_segmented,
+                    conv_with_stride, conv_with_stride_full_cover, radius_scaler_for_kernel_size, voxelize_3d)
+from layers.downsample import downsample
+from internals.neighbors import radius_search, radius_search_sorted_grid8, radius_search_sorted_grid8_segments
+from internals.grid_sample import grid_sample_filter
+import pointelligence_b200.layers as ours, layers
+assert layers is ours and layers.PointConv3d is ours.PointConv3d
+import sparse_engines.tig, pointelligence_b200.sparse_engines.tig as t
+assert sparse_engines.tig is t
+s = str(torch.ops.sparse_engines.tig_mvmr.default._schema)
+assert s == ("sparse_engines::tig_mvmr(Tensor weight, Tensor feat, Tensor flat_i, Tensor flat_j, Tensor flat_seg, "
+             "SymInt n_out, SymInt n_in, SymInt num_kernel_offsets, bool exact_cover_out, bool exact_cover_in, "
+             "SymInt uniform_seg_len, str input_precision) -> Tensor"), s
+for name in ("sparse_matrix_vector_multiplication_reduction", "sparse_vector_vector_outer_product_reduction"):
+    s = str(getattr(torch.ops.sparse_engines, name).default._schema)
+    assert s == (f"sparse_engines::{name}(Tensor a, Tensor a_idx, Tensor b, Tensor b_idx, Tensor o_idx, SymInt n_o, "
+                 "Tensor? seg_offs=None) -> Tensor"), s
+# shape-only fake kernels: traceable leaves
+from torch._subclasses.fake_tensor import FakeTensorMode
+with FakeTensorMode():
+    w = torch.empty(27, 1, 16, 32); x = torch.empty(50, 16); idx = torch.empty(400, dtype=torch.int32)
+    seg = torch.empty(28, dtype=torch.int64)
+    y = torch.ops.sparse_engines.tig_mvmr(w, x, idx, idx, seg, 40, 50, 27, False, False, -1, "ieee")
+    assert y.shape == (40, 32)
+    o = torch.ops.sparse_engines.sparse_matrix_vector_multiplication_reduction(w, idx, x.view(50, 1, 16), idx, idx, 40)
+    assert o.shape == (40, 1, 32)
+print("ok")
+"""
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-3000:]

@@ -45,6 +45,12 @@ def test_static_scratch_matches_workspace_entry_point_twice(dtype, C, M):
         torch.cuda.synchronize()
         err = (out.float() - expected.float()).norm() / expected.float().norm()
         assert float(err) < TOL[dtype], (call, float(err))
+        # and against the fp64 oracle, so that the entry point has a pin of its own
+        from oracle import sparse_ops as oso
+
+        ref = oso.vvor_f64(x.float().cpu().numpy(), j.cpu().numpy(), go.float().cpu().numpy(), i.cpu().numpy(),
+                           k.cpu().numpy(), K)
+        assert oso.rel_frobenius(out.float().cpu().numpy(), ref) < TOL[dtype], call
     assert _cabi.device_status() == 0
 
 
