@@ -26,9 +26,9 @@
 //   producer warps   together, one (block, tap, 64-channel slice) A tile after the other: every
 //                    thread issues its 16-byte cp.async copies of the tile's source rows straight
 //                    into the 128-byte-swizzled slot (rows without a source are zero-filled by the
-//                    same instruction with a source size of 0) and hands the slot's mbarrier an
-//                    arrival that fires when its copies have landed; nothing waits for data, so
-//                    as many tiles are in flight as there are slots
+//                    same instruction with a source size of 0); a tile is handed to the tensor
+//                    core two tiles later, when its copies have landed anyway, with one mbarrier
+//                    arrival per warp; the copies of several tiles are in flight at any time
 //   weight warp      streams the 64-channel slices of W[tap] through a small ring with TMA
 //                    (cp.async.bulk.tensor, 128-byte swizzle, no multicast); one slice serves
 //                    all blocks of the group that use the tap
@@ -62,6 +62,8 @@ constexpr int MAX_SLOTS = 12;         // A slots
 constexpr int MAX_NW = 4;             // weight slots
 constexpr int MAX_GROUP = 8;          // blocks per group
 constexpr int MAX_TAPS = 512;         // taps the shared-memory tables are sized for
+constexpr int SIGNAL_LAG = 2;          // a tile is handed to the tensor core once the copies of the two tiles after it are issued
+constexpr int ROW_PREFETCH = 1;        // tiles whose source rows a producer thread holds ahead of the one it issues (deeper did not pay: the copies, not this table, bound the producer)
 constexpr int ROW_PASSES = 8;         // rows a producer thread copies per tile, at most (128 rows / (4 warps * 4 row lanes))
 constexpr unsigned STATUS_BIT = 4u;   // bit of the device status word this kernel raises
 constexpr unsigned PLAN_MAGIC = 0x70637832u;
@@ -279,6 +281,7 @@ struct OsParams {
     int K, C, M, transpose, fmt;
     int inw, outw, nkb, G, ngroups, nblocks;
     int npw, nslots, nw, use_tma;
+    int lag;   // 0: every thread's copies report to the slot's barrier themselves; SIGNAL_LAG: one arrival per warp, SIGNAL_LAG tiles later
     uint32_t w_slot_bytes, w_box_rows, w_tx_bytes;
     uint32_t ncols, col_stride;
     uint64_t wait_limit_ns;
@@ -340,7 +343,7 @@ mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
     volatile int *abort_flag = &s_abort;
 
     if (tid == 0) {
-        for (int s = 0; s < p.nslots; ++s) mbar_init(smem_u32(&s_a_full[s]), (uint32_t)p.npw * 32), mbar_init(smem_u32(&s_a_empty[s]), 1);
+        for (int s = 0; s < p.nslots; ++s) mbar_init(smem_u32(&s_a_full[s]), (uint32_t)p.npw * (p.lag ? 1u : 32u)), mbar_init(smem_u32(&s_a_empty[s]), 1);
         for (int s = 0; s < p.nw; ++s) mbar_init(smem_u32(&s_w_full[s]), p.use_tma ? 1 : 32), mbar_init(smem_u32(&s_w_empty[s]), 1);
         mbar_init(smem_u32(&s_d_full), 1);
         fence_mbar_init();
@@ -418,50 +421,89 @@ mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
             // All producer threads fill every tile together: 8 threads per row (one 16-byte piece
             // each), npw * 4 rows per pass.  The source rows of the next tile are fetched while
             // the current one is issued.
-            const int piece = tid & 7, row_lane = tid >> 3, row_lanes = p.npw * 4;
+            const int piece = tid & 7, row_lane = tid >> 3, row_lanes = p.npw * 4, passes = ROWS / row_lanes;
+            // row_lanes is a multiple of 8, so the rows of a thread share their low three bits and
+            // with them the swizzled position of the thread's piece inside a row
+            const uint32_t lane_offset = (uint32_t)row_lane * 128 + (uint32_t)((piece ^ (row_lane & 7)) << 4);
+            const uint32_t pass_stride = (uint32_t)row_lanes * 128;
             uint32_t slot = a_n % (uint32_t)p.nslots, use = a_n / (uint32_t)p.nslots;
+            uint32_t signal_slot = slot;   // slot of the oldest tile not handed over yet
             bool ok_role = true;
-            int rows_next[ROW_PASSES];
-            auto fetch_rows = [&](int task) {
-                const int meta = s_task[task].z;
-                const int32_t *table = p.tile_rows + ((int64_t)(b0 + (meta & 15)) * p.K + (meta >> 16)) * ROWS;
+            // source rows of the next ROW_PREFETCH tiles: buffer u holds tile t with t mod ROW_PREFETCH == u
+            // (static indexing: the loop below is unrolled by ROW_PREFETCH, so no register is moved
+            // while its load is in flight)
+            int rows_q[ROW_PREFETCH][ROW_PASSES];
+            auto fetch_rows = [&](int task, int (&dst)[ROW_PASSES]) {
 #pragma unroll
-                for (int k = 0; k < ROW_PASSES; ++k) {
-                    const int r = row_lane + k * row_lanes;
-                    rows_next[k] = -1;
-                    if (r < ROWS) rows_next[k] = __ldg(table + r);
-                }
+                for (int k = 0; k < ROW_PASSES; ++k) dst[k] = -1;
+                if (task >= a_total) return;
+                const int meta = s_task[task].z;
+                const int32_t *table = p.tile_rows + ((int64_t)(b0 + (meta & 15)) * p.K + (meta >> 16)) * ROWS + row_lane;
+#pragma unroll
+                for (int k = 0; k < ROW_PASSES; ++k)
+                    if (k < passes) dst[k] = __ldg(table + k * row_lanes);
             };
-            if (a_total > 0) fetch_rows(0);
-            for (int t = 0; t < a_total; ++t) {
+#pragma unroll
+            for (int u = 0; u < ROW_PREFETCH; ++u) fetch_rows(u, rows_q[u]);
+            for (int t0 = 0; t0 < a_total && ok_role; t0 += ROW_PREFETCH) {
+#pragma unroll
+              for (int u = 0; u < ROW_PREFETCH; ++u) {
+                const int t = t0 + u;
+                if (t >= a_total || !ok_role) break;
                 int rows_cur[ROW_PASSES];
 #pragma unroll
-                for (int k = 0; k < ROW_PASSES; ++k) rows_cur[k] = rows_next[k];
+                for (int k = 0; k < ROW_PASSES; ++k) rows_cur[k] = rows_q[u][k];
+                fetch_rows(t + ROW_PREFETCH, rows_q[u]);
                 const int q = (s_task[t].z >> 4) & 15;
-                if (t + 1 < a_total) fetch_rows(t + 1);
                 const bool piece_ok = piece < pieces_of(p.inw, q);
-                const int col = q * 64 + piece * 8;
-                const uint32_t slot_addr = a_base + slot * SLOT_BYTES;
+                const uint16_t *feat_col = p.feat + q * 64 + piece * 8, *sum_col = p.scratch + q * 64 + piece * 8;
+                const uint32_t dst0 = a_base + slot * SLOT_BYTES + lane_offset;
                 // the tensor core has finished reading this slot's previous tile
                 STAT_T0(t_w);
                 ok_role = mbar_wait_abortable(smem_u32(&s_a_empty[slot]), (use & 1u) ^ 1u, STATUS_BIT, p.status, abort_flag,
                                               p.wait_limit_ns);
                 STAT_ADD(9, t_w);
                 if (!ok_role) break;
+                if (piece_ok) {
 #pragma unroll
-                for (int k = 0; k < ROW_PASSES; ++k) {
-                    const int r = row_lane + k * row_lanes;
-                    if (r < ROWS && piece_ok) {
-                        const int src_row = rows_cur[k];
-                        // a feature row, a row of bucket sums, or nothing (16 bytes of zeros: source size 0)
-                        const uint16_t *src = src_row >= 0 ? p.feat + (int64_t)src_row * p.inw
-                                              : src_row == -1 ? p.feat : p.scratch + (int64_t)(-2 - src_row) * p.inw;
-                        cp_async16_zfill(slot_addr + (uint32_t)r * 128 + (uint32_t)((piece ^ (r & 7)) << 4), src + col,
-                                         src_row == -1 ? 0u : 16u);
+                    for (int k = 0; k < ROW_PASSES; ++k) {
+                        if (k < passes) {
+                            const int src_row = rows_cur[k];
+                            // a feature row, a row of bucket sums, or nothing (16 bytes of zeros: source size 0)
+                            const uint16_t *src = src_row >= 0 ? feat_col + (int64_t)src_row * p.inw
+                                                               : sum_col + (int64_t)(src_row == -1 ? 0 : -2 - src_row) * p.inw;
+                            cp_async16_zfill(dst0 + (uint32_t)k * pass_stride, src_row == -1 ? (const void *)feat_col : (const void *)src,
+                                             src_row == -1 ? 0u : 16u);
+                        }
                     }
                 }
-                cp_async_mbar_arrive(smem_u32(&s_a_full[slot]));   // fires once this thread's copies have landed
+                if (p.lag == 0) {
+                    cp_async_mbar_arrive(smem_u32(&s_a_full[slot]));   // fires once this thread's copies have landed
+                    if (++slot == (uint32_t)p.nslots) slot = 0, ++use;
+                    continue;
+                }
+                cp_async_commit();
+                // Hand over the tile issued SIGNAL_LAG tiles ago: its copies (a cp.async group of this
+                // thread) have landed once at most SIGNAL_LAG newer groups are pending.  One arrival
+                // per warp: an mbarrier takes arrivals one at a time, and one per thread and tile
+                // would cost more than the copies.
+                if (t >= SIGNAL_LAG) {
+                    cp_async_wait<SIGNAL_LAG>();
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&s_a_full[signal_slot]));
+                    if (++signal_slot == (uint32_t)p.nslots) signal_slot = 0;
+                }
                 if (++slot == (uint32_t)p.nslots) slot = 0, ++use;
+              }
+            }
+            // the last tiles of the group
+            cp_async_wait<0>();
+            fence_async_smem();
+            __syncwarp();
+            for (int t = max(a_total - SIGNAL_LAG, 0); t < a_total && ok_role && p.lag; ++t) {
+                if (lane == 0) mbar_arrive(smem_u32(&s_a_full[signal_slot]));
+                if (++signal_slot == (uint32_t)p.nslots) signal_slot = 0;
             }
             ok_role = __all_sync(0xffffffffu, ok_role);
             STAT_ADD(10, t_role);
@@ -531,7 +573,7 @@ mvmr_os_kernel(const __grid_constant__ CUtensorMap tmap, const OsParams p) {
                                                   p.wait_limit_ns);
                     if (!ok_role) break;
                     STAT_ADD(14, t_a);
-                    fence_async_smem();   // the tile was written by cp.async (generic proxy), the tensor core reads through the async proxy
+                    fence_async_smem();   // the tile was written through the generic proxy, the tensor core reads through the async proxy
                     tc_fence_after();
                     const uint64_t ad = a_desc0 + (uint64_t)(slot * (SLOT_BYTES >> 4));
                     const uint64_t bd = b_desc0 + (uint64_t)(wslot * w_slot16);
@@ -864,26 +906,28 @@ int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan, siz
     int nslots = 0, nw = 0;
     for (; ctas >= 1 && !nslots; --ctas) {
         const size_t budget = (size_t)232448 / ctas - 1024 - static_smem - 1024;
-        for (int a = MAX_SLOTS; a >= 3 && !nslots; --a)
+        for (int a = MAX_SLOTS; a >= SIGNAL_LAG + 2 && !nslots; --a)
             for (int b = (ctas == 2 ? 3 : MAX_NW); b >= 2 && !nslots; --b)
                 if ((size_t)a * SLOT_BYTES + (size_t)b * p.w_slot_bytes + table_fixed <= budget) nslots = a, nw = b;
         if (nslots) break;
     }
     if (!nslots) PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr_planned: shared memory does not fit (K=%d C=%d M=%d group=%d)", K, C, M, G);
-    int npw = ctas == 2 ? 4 : MAX_NPW;
+    int npw = MAX_NPW;
     if (const char *e = getenv("PCX_OS_WARPS")) {
         const int want = atoi(e);
         if (want == 4 || want == 8) npw = want;
     }
     if (const char *e = getenv("PCX_OS_SLOTS")) {
         const int want = atoi(e);
-        if (want >= 2 && want <= nslots) nslots = want;
+        if (want >= SIGNAL_LAG + 2 && want <= nslots) nslots = want;
     }
     if (const char *e = getenv("PCX_OS_WSLOTS")) {
         const int want = atoi(e);
         if (want >= 2 && want <= nw) nw = want;
     }
     p.npw = npw, p.nslots = nslots, p.nw = nw;
+    p.lag = 0;
+    if (const char *e = getenv("PCX_OS_LAG")) p.lag = atoi(e) ? SIGNAL_LAG : 0;
     const size_t smem = 1024 + (size_t)nslots * SLOT_BYTES + (size_t)nw * p.w_slot_bytes + table_fixed;
     static int granted[64] = {};
     int dev = 0;

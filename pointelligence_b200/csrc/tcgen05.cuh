@@ -44,6 +44,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Same test, but the thread may be parked by the hardware for up to `suspend_ns` while the phase
+// is incomplete: a waiting role then stops competing for issue slots with the working ones.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t suspend_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(suspend_ns)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -71,12 +84,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
 __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, unsigned flag,
                                                     unsigned int *status, volatile int *abort_flag,
                                                     uint64_t limit_ns = WAIT_LIMIT_NS) {
-    for (int it = 0; it < 64; ++it)
-        if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (;;) {
-        for (int it = 0; it < 64; ++it)
-            if (mbar_try_wait(bar, parity)) return true;
+        for (int it = 0; it < 16; ++it)
+            if (mbar_try_wait_parked(bar, parity, 2000u)) return true;
         if (*abort_flag) return false;
         if (global_timer_ns() - t0 > limit_ns) break;
     }
