@@ -196,12 +196,13 @@ def profile_records():
 # (``pcx_mvmr_planned``: accumulators in tensor memory across all taps, every output row written
 # once) needs a plan of the rulebook, built once per rulebook and direction and remembered by the
 # identity of the index tensors.  Measured on B200 it wins for rows of 128 channels and more at any
-# density and for narrower rows once a scene has about a dozen triplets per output row (the deeper
-# levels of a U-Net, dense scans); sparse narrow layers and single-tap rulebooks (nothing to keep
-# across taps) stay on the scatter kernel of ``pcx_mvmr``.
+# density and for narrower rows from about six triplets per output row on (on the residual U-Net
+# of the benchmark: 282 ms per step on the scatter kernel alone, 216 ms with a threshold of 12, 206 ms
+# with 6 or lower); very sparse narrow layers and single-tap rulebooks (nothing to keep across taps)
+# stay on the scatter kernel of ``pcx_mvmr``.
 ENGINE_PLANNED = 3
 _PLANNED_MIN_WIDTH = int(os.environ.get("PCX_PLANNED_MIN_WIDTH", "128"))     # output width from which on, at any density
-_PLANNED_MIN_RATIO = float(os.environ.get("PCX_PLANNED_MIN_RATIO", "12"))     # triplets per output row from which on
+_PLANNED_MIN_RATIO = float(os.environ.get("PCX_PLANNED_MIN_RATIO", "6"))      # triplets per output row from which on
 _PLANNED_ENABLED = os.environ.get("PCX_PLANNED", "1") != "0"
 
 

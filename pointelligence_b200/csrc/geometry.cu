@@ -89,42 +89,50 @@ __device__ __forceinline__ int corner_of(float v, float r32, float inv) {
     return (int)floorf(__fmul_rn(__fsub_rn(v, r32), inv));
 }
 
-__device__ __forceinline__ void warp_minmax3(int x, int y, int z, bool valid, int32_t *ext) {
-    int lo[3] = {valid ? x : INT_MAX, valid ? y : INT_MAX, valid ? z : INT_MAX};
-    int hi[3] = {valid ? x : INT_MIN, valid ? y : INT_MIN, valid ? z : INT_MIN};
+// Running min / max of a thread's cells; folded per warp, then per block in shared memory, and
+// only then into the global extents (one atomic per block and bound instead of one per warp).
+struct Extent4 {
+    int lo[4], hi[4];
+    __device__ __forceinline__ void reset() {
 #pragma unroll
-    for (int a = 0; a < 3; ++a) {
-        lo[a] = __reduce_min_sync(0xffffffffu, lo[a]);
-        hi[a] = __reduce_max_sync(0xffffffffu, hi[a]);
+        for (int a = 0; a < 4; ++a) lo[a] = INT_MAX, hi[a] = INT_MIN;
     }
-    if ((threadIdx.x & 31) == 0) {
-#pragma unroll
-        for (int a = 0; a < 3; ++a) {
-            if (lo[a] != INT_MAX) atomicMin(&ext[a], lo[a]);
-            if (hi[a] != INT_MIN) atomicMax(&ext[4 + a], hi[a]);
+    __device__ __forceinline__ void add(int a, int v) { lo[a] = min(lo[a], v), hi[a] = max(hi[a], v); }
+};
+
+__device__ __forceinline__ void block_minmax(Extent4 &e, int dims, int32_t *ext) {
+    __shared__ int s_lo[4], s_hi[4];
+    if (threadIdx.x < 4) s_lo[threadIdx.x] = INT_MAX, s_hi[threadIdx.x] = INT_MIN;
+    __syncthreads();
+    for (int a = 0; a < dims; ++a) {
+        const int lo = __reduce_min_sync(0xffffffffu, e.lo[a]), hi = __reduce_max_sync(0xffffffffu, e.hi[a]);
+        if ((threadIdx.x & 31) == 0) {
+            if (lo != INT_MAX) atomicMin(&s_lo[a], lo);
+            if (hi != INT_MIN) atomicMax(&s_hi[a], hi);
         }
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < dims) {
+        if (s_lo[threadIdx.x] != INT_MAX) atomicMin(&ext[threadIdx.x], s_lo[threadIdx.x]);
+        if (s_hi[threadIdx.x] != INT_MIN) atomicMax(&ext[4 + threadIdx.x], s_hi[threadIdx.x]);
     }
 }
 
 __global__ void radius_extent_kernel(const float *__restrict__ pts, const float *__restrict__ qry,
                                      int64_t P, int64_t Q, float inv, float r32, int32_t *ext) {
-    int64_t n = P + Q;
-    int64_t rounded = (n + 31) / 32 * 32;
-    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < rounded;
-         t += (int64_t)gridDim.x * blockDim.x) {
-        bool valid = t < n;
-        int x = 0, y = 0, z = 0;
-        if (valid) {
-            if (t < P) {
-                x = cell_of(pts[3 * t], inv), y = cell_of(pts[3 * t + 1], inv), z = cell_of(pts[3 * t + 2], inv);
-            } else {
-                int64_t q = t - P;
-                x = corner_of(qry[3 * q], r32, inv), y = corner_of(qry[3 * q + 1], r32, inv),
-                z = corner_of(qry[3 * q + 2], r32, inv);
-            }
+    const int64_t n = P + Q;
+    Extent4 e;
+    e.reset();
+    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) {
+        if (t < P) {
+            e.add(0, cell_of(pts[3 * t], inv)), e.add(1, cell_of(pts[3 * t + 1], inv)), e.add(2, cell_of(pts[3 * t + 2], inv));
+        } else {
+            const int64_t q = t - P;
+            e.add(0, corner_of(qry[3 * q], r32, inv)), e.add(1, corner_of(qry[3 * q + 1], r32, inv));
+            e.add(2, corner_of(qry[3 * q + 2], r32, inv));
         }
-        warp_minmax3(x, y, z, valid, ext);
     }
+    block_minmax(e, 3, ext);
 }
 
 // Injective key of a cell of one sample.  Extents include the +1 candidate offset.
@@ -304,40 +312,58 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) radius_scan_kernel(ScanAr
         }
         int64_t out_base = MODE == 0 ? 0 : a.offsets[q];
         int found = 0;
-#pragma unroll 1
+        // The candidates of the 8 cells form one list (cell after cell, each in sorted order); the warp
+        // walks it 64 at a time -- two independent loads per lane -- instead of one cell at a time, so
+        // that half-empty cells cost no extra round trip to memory.
+        int c_start[8], c_first[8];   // start of cell c in the sorted points, position of its first candidate in the list
+        int total = 0;
+#pragma unroll
         for (int c = 0; c < 8; ++c) {
-            int s = __shfl_sync(0xffffffffu, start, c), e = __shfl_sync(0xffffffffu, end, c);
-            for (int base = s; base < e; base += 32) {
-                int p = base + lane;
-                bool ok = false;
-                float4 pt = make_float4(0.f, 0.f, 0.f, 0.f);
-                float dist = 0.f;
-                if (p < e) {
-                    pt = a.sorted_pts[p];
-                    ok = radius_accept(qx, qy, qz, pt, a.r32, a.distance_type, a.variant, &dist);
-                }
-                unsigned m = __ballot_sync(0xffffffffu, ok);
-                if (ok) {
-                    int tap = (a.K > 0) ? tap_of(qx, qy, qz, pt, a.g32, a.K) : 0;
-                    if (MODE == 0) {
-                        if (a.K > 0) {
-                            if (a.use_smem_hist) atomicAdd(&s_hist[tap], 1u);
-                            else atomicAdd(&a.tap_hist[tap], 1u);
-                        }
+            const int s = __shfl_sync(0xffffffffu, start, c), e = __shfl_sync(0xffffffffu, end, c);
+            c_start[c] = s, c_first[c] = total;
+            total += e - s;
+        }
+        auto point_of = [&](int idx) {   // sorted-point index of list position idx
+            int p = c_start[0] + idx;
+#pragma unroll
+            for (int c = 1; c < 8; ++c)
+                if (idx >= c_first[c]) p = c_start[c] + (idx - c_first[c]);
+            return p;
+        };
+        auto emit = [&](bool ok, float4 pt, float dist) {
+            const unsigned m = __ballot_sync(0xffffffffu, ok);
+            if (ok) {
+                int tap = (a.K > 0) ? tap_of(qx, qy, qz, pt, a.g32, a.K) : 0;
+                if (MODE == 0) {
+                    if (a.K > 0) {
+                        if (a.use_smem_hist) atomicAdd(&s_hist[tap], 1u);
+                        else atomicAdd(&a.tap_hist[tap], 1u);
+                    }
+                } else {
+                    int64_t pos = out_base + found + __popc(m & ((1u << lane) - 1u));
+                    int32_t j = __float_as_int(pt.w);
+                    if (MODE == 1) {
+                        a.neighbors[pos] = j;
+                        if (a.distances) a.distances[pos] = dist;
                     } else {
-                        int64_t pos = out_base + found + __popc(m & ((1u << lane) - 1u));
-                        int32_t j = __float_as_int(pt.w);
-                        if (MODE == 1) {
-                            a.neighbors[pos] = j;
-                            if (a.distances) a.distances[pos] = dist;
-                        } else {
-                            a.tap_keys[pos] = (uint16_t)tap;
-                            a.packed[pos] = ((uint64_t)(uint32_t)q << 32) | (uint32_t)j;
-                        }
+                        a.tap_keys[pos] = (uint16_t)tap;
+                        a.packed[pos] = ((uint64_t)(uint32_t)q << 32) | (uint32_t)j;
                     }
                 }
-                found += __popc(m);
             }
+            found += __popc(m);
+        };
+#pragma unroll 1
+        for (int base = 0; base < total; base += 64) {
+            const int i0 = base + lane, i1 = base + 32 + lane;
+            float4 p0 = make_float4(0.f, 0.f, 0.f, 0.f), p1 = p0;
+            if (i0 < total) p0 = a.sorted_pts[point_of(i0)];
+            if (i1 < total) p1 = a.sorted_pts[point_of(i1)];
+            float d0 = 0.f, d1 = 0.f;
+            const bool ok0 = i0 < total && radius_accept(qx, qy, qz, p0, a.r32, a.distance_type, a.variant, &d0);
+            const bool ok1 = i1 < total && radius_accept(qx, qy, qz, p1, a.r32, a.distance_type, a.variant, &d1);
+            emit(ok0, p0, d0);
+            if (base + 32 < total) emit(ok1, p1, d1);
         }
         if (MODE == 0 && lane == 0) {
             a.counts[q] = found;
@@ -452,24 +478,14 @@ __device__ __forceinline__ int floor_div_cell(float a, float b) {
 
 __global__ void grid_extent_kernel(const float *__restrict__ pts, const int32_t *__restrict__ sample,
                                    int64_t N, float cell, int32_t *ext) {
-    int64_t rounded = (N + 31) / 32 * 32;
-    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < rounded;
-         t += (int64_t)gridDim.x * blockDim.x) {
-        bool valid = t < N;
-        int x = 0, y = 0, z = 0, b = 0;
-        if (valid) {
-            x = floor_div_cell(pts[3 * t], cell), y = floor_div_cell(pts[3 * t + 1], cell),
-            z = floor_div_cell(pts[3 * t + 2], cell);
-            b = sample ? sample[t] : 0;
-        }
-        warp_minmax3(x, y, z, valid, ext);
-        int blo = __reduce_min_sync(0xffffffffu, valid ? b : INT_MAX);
-        int bhi = __reduce_max_sync(0xffffffffu, valid ? b : INT_MIN);
-        if ((threadIdx.x & 31) == 0 && blo != INT_MAX) {
-            atomicMin(&ext[3], blo);
-            atomicMax(&ext[7], bhi);
-        }
+    Extent4 e;
+    e.reset();
+    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < N; t += (int64_t)gridDim.x * blockDim.x) {
+        e.add(0, floor_div_cell(pts[3 * t], cell)), e.add(1, floor_div_cell(pts[3 * t + 1], cell));
+        e.add(2, floor_div_cell(pts[3 * t + 2], cell));
+        e.add(3, sample ? sample[t] : 0);
     }
+    block_minmax(e, 4, ext);
 }
 
 __global__ void grid_key_kernel(const float *__restrict__ pts, const int32_t *__restrict__ sample,

@@ -227,7 +227,20 @@ __global__ void plan_entries_kernel(const uint32_t *__restrict__ key_sorted, con
     }
 }
 
-// scratch[b] = sum of the feature rows of bucket b (fp32 sum, one rounding); one thread per 16-byte piece
+// scratch[b] = sum of the feature rows of bucket b (fp32 sum in entry order, one rounding); one thread
+// per 16-byte piece.  The row indices of up to four members are fetched together and their pieces
+// together after that, so that a bucket costs two memory latencies instead of two per member.
+__device__ __forceinline__ void add_piece(float (&acc)[8], uint4 v, int fmt) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        float2 f;
+        if (fmt) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[q]));
+        else f = __half22float2(*reinterpret_cast<const __half2 *>(&w[q]));
+        acc[2 * q] += f.x, acc[2 * q + 1] += f.y;
+    }
+}
+
 __global__ void bucket_sum_kernel(const uint16_t *__restrict__ feat, const uint2 *__restrict__ entries,
                                   const uint2 *__restrict__ buckets, const uint32_t *__restrict__ ctrl, int inw, int fmt,
                                   uint16_t *scratch) {
@@ -236,18 +249,20 @@ __global__ void bucket_sum_kernel(const uint16_t *__restrict__ feat, const uint2
     const int64_t b = x / ppr;
     const int piece = (int)(x - b * ppr);
     if (b >= (int64_t)ctrl[CTRL_NMULTI]) return;
-    const uint2 bk = buckets[b];
+    const uint2 bk = __ldg(buckets + b);
+    const uint16_t *col = feat + piece * 8;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (uint32_t m = 0; m < bk.y; ++m) {
-        const uint4 v = *reinterpret_cast<const uint4 *>(feat + (int64_t)entries[bk.x + m].y * inw + piece * 8);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    for (uint32_t m0 = 0; m0 < bk.y; m0 += 4) {
+        uint32_t rows[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            float2 f;
-            if (fmt) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[q]));
-            else f = __half22float2(*reinterpret_cast<const __half2 *>(&w[q]));
-            acc[2 * q] += f.x, acc[2 * q + 1] += f.y;
-        }
+        for (int m = 0; m < 4; ++m) rows[m] = m0 + m < bk.y ? __ldg(&entries[bk.x + m0 + m].y) : 0u;
+        uint4 v[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m)
+            v[m] = m0 + m < bk.y ? __ldg(reinterpret_cast<const uint4 *>(col + (int64_t)rows[m] * inw)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int m = 0; m < 4; ++m)
+            if (m0 + m < bk.y) add_piece(acc, v[m], fmt);
     }
     uint4 o;
     o.x = pack2(acc[0], acc[1], fmt), o.y = pack2(acc[2], acc[3], fmt);
@@ -940,8 +955,10 @@ int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan, siz
     const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(pv.ngroups, (int64_t)ctas * num_sms()));
     if (multi_buckets > 0) {
         const int64_t threads = multi_buckets * (inw >> 3);
+        prof_begin("bucket_sum_kernel", stream);
         bucket_sum_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(p.feat, pv.entries, pv.buckets, pv.ctrl, inw, p.fmt,
                                                                                (uint16_t *)d_ws);
+        prof_end(stream);
         PCX_LAUNCH_CHECK();
     }
     prof_begin(transpose ? "mvmr_os_kernel(dgrad)" : "mvmr_os_kernel(fwd)", stream);

@@ -150,7 +150,7 @@ def test_automatic_engine_takes_the_planned_kernel_for_wide_or_dense_layers():
     x = torch.randn(900, 64, device=DEV).bfloat16()
     ti, tj, tseg = _t(i), _t(j), _t(seg)
     auto, names = _kernels_of(lambda: _cabi.mvmr(w, x, tj, ti, tseg, None, 800, False))
-    assert names == ["mvmr_os_kernel(fwd)"]                    # dense neighbourhood
+    assert [n for n in names if n != "bucket_sum_kernel"] == ["mvmr_os_kernel(fwd)"]   # dense neighbourhood
     forced = _cabi.mvmr(w, x, tj, ti, tseg, None, 800, False, engine=_cabi.ENGINE_PLANNED)
     scatter, names = _kernels_of(lambda: _cabi.mvmr(w, x, tj, ti, tseg, None, 800, False, engine=_cabi.ENGINE_TENSOR))
     assert names == ["mvmr_tc_kernel(fwd)"] and torch.equal(auto, forced) and close(auto, scatter)
@@ -161,7 +161,7 @@ def test_automatic_engine_takes_the_planned_kernel_for_wide_or_dense_layers():
     assert names == ["mvmr_tc_kernel(fwd)"]                    # sparse and 64 channels wide: scatter engine
     w128 = torch.randn(27, 1, 64, 128, device=DEV).bfloat16() / 8
     out, names = _kernels_of(lambda: _cabi.mvmr(w128, x, tj, ti, tseg, None, 4000, False))
-    assert names == ["mvmr_os_kernel(fwd)"]                    # 128 channels wide: planned engine at any density
+    assert [n for n in names if n != "bucket_sum_kernel"] == ["mvmr_os_kernel(fwd)"]   # 128 channels wide: at any density
     assert close(out, _cabi.mvmr(w128, x, tj, ti, tseg, None, 4000, False, engine=_cabi.ENGINE_TENSOR))
     with pytest.raises(NotImplementedError):                   # fp32 has no tensor-core engine
         _cabi.mvmr(w.float(), x.float(), tj, ti, tseg, None, 4000, False, engine=_cabi.ENGINE_PLANNED)
