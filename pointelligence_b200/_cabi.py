@@ -195,15 +195,27 @@ def profile_records():
 # Engine choice of ``mvmr`` with the automatic engine.  The output-stationary kernel
 # (``pcx_mvmr_planned``: accumulators in tensor memory across all taps, every output row written
 # once) needs a plan of the rulebook, built once per rulebook and direction and remembered by the
-# identity of the index tensors.  Measured on B200 it wins for rows of 128 channels and more at any
-# density and for narrower rows from about six triplets per output row on (on the residual U-Net
-# of the benchmark: 282 ms per step on the scatter kernel alone, 216 ms with a threshold of 12, 206 ms
-# with 6 or lower); very sparse narrow layers and single-tap rulebooks (nothing to keep across taps)
-# stay on the scatter kernel of ``pcx_mvmr``.
+# identity of the index tensors.  Measured on B200 it beats the scatter kernel of ``pcx_mvmr``
+#   - for dense neighbourhoods (a dozen triplets per output row and more: the deeper levels of a
+#     U-Net, dense scans), at every width, and
+#   - from four triplets per row on once the scatter kernel's fp32 accumulator (n_out x width x 4
+#     bytes) outgrows half of the 126 MB L2 and its reductions start to go to HBM: wide layers and
+#     large clouds (on the residual U-Net of the benchmark: 282 ms per step on the scatter kernel
+#     alone, 203 ms with this rule).
+# Sparse rulebooks over small accumulators and single-tap rulebooks (nothing to keep across taps)
+# stay on the scatter kernel.
 ENGINE_PLANNED = 3
-_PLANNED_MIN_WIDTH = int(os.environ.get("PCX_PLANNED_MIN_WIDTH", "128"))     # output width from which on, at any density
-_PLANNED_MIN_RATIO = float(os.environ.get("PCX_PLANNED_MIN_RATIO", "6"))      # triplets per output row from which on
+_PLANNED_DENSE_RATIO = float(os.environ.get("PCX_PLANNED_DENSE_RATIO", "12"))   # triplets per output row: always planned
+_PLANNED_MIN_RATIO = float(os.environ.get("PCX_PLANNED_MIN_RATIO", "4"))        # ... planned when the accumulator is large
+_PLANNED_MIN_ACC_BYTES = int(os.environ.get("PCX_PLANNED_MIN_ACC_BYTES", str(64 << 20)))
 _PLANNED_ENABLED = os.environ.get("PCX_PLANNED", "1") != "0"
+
+
+def _planned_pays(T, n_out, outw, K):
+    if not _PLANNED_ENABLED or K <= 1 or n_out <= 0:
+        return False
+    ratio = T / n_out
+    return ratio >= _PLANNED_DENSE_RATIO or (ratio >= _PLANNED_MIN_RATIO and n_out * outw * 4 >= _PLANNED_MIN_ACC_BYTES)
 
 
 class MvmrPlan:
@@ -352,8 +364,7 @@ def mvmr(weight, feat, gather, scatter, seg_offs, tap_idx, n_out, transpose, eng
             raise NotImplementedError("the output-stationary engine needs fp16/bf16 features, one group, tap-sorted "
                                       "triplets, channel counts that are multiples of 16 and rows of at most 256 channels")
         outw = C if transpose else M
-        if fits and (engine == ENGINE_PLANNED or (_PLANNED_ENABLED and K > 1 and (
-                outw >= _PLANNED_MIN_WIDTH or gather.numel() >= _PLANNED_MIN_RATIO * n_out))):
+        if fits and (engine == ENGINE_PLANNED or _planned_pays(gather.numel(), n_out, outw, K)):
             plan = cached_mvmr_plan(scatter, gather, seg_offs, K, n_out, plan_group_blocks(outw))
             return mvmr_planned(weight, feat, plan, transpose)
         engine = ENGINE_AUTO

@@ -30,7 +30,7 @@
 //                    core two tiles later, when its copies have landed anyway, with one mbarrier
 //                    arrival per warp; the copies of several tiles are in flight at any time
 //   weight warp      streams the 64-channel slices of W[tap] through a small ring with TMA
-//                    (cp.async.bulk.tensor, 128-byte swizzle, no multicast); one slice serves
+//                    (cp.async.bulk.tensor tile loads, 128-byte swizzle); one slice serves
 //                    all blocks of the group that use the tap
 //   MMA warp         one thread issues tcgen05.mma (M = 128 rows, N = out_width, K = 16 per
 //                    instruction) with accumulate = 1 from the block's second tile on;

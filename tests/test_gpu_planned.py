@@ -139,7 +139,7 @@ def _kernels_of(fn):
     return out, names
 
 
-def test_automatic_engine_takes_the_planned_kernel_for_wide_or_dense_layers():
+def test_automatic_engine_takes_the_planned_kernel_for_dense_or_large_layers():
     from pointelligence_b200 import _cabi
 
     def close(a, b):   # the scatter engine adds in fp32 in an order that varies from run to run
@@ -159,10 +159,12 @@ def test_automatic_engine_takes_the_planned_kernel_for_wide_or_dense_layers():
     x = torch.randn(4000, 64, device=DEV).bfloat16()
     _, names = _kernels_of(lambda: _cabi.mvmr(w, x, tj, ti, tseg, None, 4000, False))
     assert names == ["mvmr_tc_kernel(fwd)"]                    # sparse and 64 channels wide: scatter engine
-    w128 = torch.randn(27, 1, 64, 128, device=DEV).bfloat16() / 8
-    out, names = _kernels_of(lambda: _cabi.mvmr(w128, x, tj, ti, tseg, None, 4000, False))
-    assert [n for n in names if n != "bucket_sum_kernel"] == ["mvmr_os_kernel(fwd)"]   # 128 channels wide: at any density
-    assert close(out, _cabi.mvmr(w128, x, tj, ti, tseg, None, 4000, False, engine=_cabi.ENGINE_TENSOR))
+    # a large accumulator (n_out x width x 4 bytes beyond half of the L2) at four triplets per row and more
+    assert _cabi._planned_pays(T=900_000, n_out=150_000, outw=128, K=27)
+    assert not _cabi._planned_pays(T=900_000, n_out=150_000, outw=64, K=27)
+    assert not _cabi._planned_pays(T=133_000, n_out=50_000, outw=256, K=27)      # too sparse
+    assert _cabi._planned_pays(T=7_000_000, n_out=1_100_000, outw=32, K=27)
+    assert not _cabi._planned_pays(T=1_100_000, n_out=1_100_000, outw=256, K=1)   # a single tap
     with pytest.raises(NotImplementedError):                   # fp32 has no tensor-core engine
         _cabi.mvmr(w.float(), x.float(), tj, ti, tseg, None, 4000, False, engine=_cabi.ENGINE_PLANNED)
 
