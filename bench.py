@@ -36,6 +36,7 @@ Printed JSON (rank 0, one line):
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -251,7 +252,8 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: ranks that fall out of step fail within minutes instead of hanging
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     # ---- scene, rulebook (geometry stage on the GPU), operands
     pts_np = indoor_scene(args.points, rank)
@@ -297,18 +299,20 @@ def run_ours(args, rank, local_rank, world):
     side = torch.cuda.Stream()
     ev_fwd, ev_side = torch.cuda.Event(), torch.cuda.Event()
 
+    engine = {"auto": _cabi.ENGINE_AUTO, "scatter": _cabi.ENGINE_TENSOR, "planned": _cabi.ENGINE_PLANNED}[args.engine]
+
     def step_resident():
         # forward, then the two gradients side by side as a backward pass is free to run them:
         # weight gradient (and its all-reduce) on a second stream, input gradient on the main one
         main = torch.cuda.current_stream()
-        out = _cabi.mvmr(w, x, j, i, seg, None, n, False)
+        out = _cabi.mvmr(w, x, j, i, seg, None, n, False, engine=engine)
         ev_fwd.record(main)
         if not args.overlap_grads:
             gw = _cabi.vvor(x.view(n, 1, C), j, go.view(n, 1, M), i, seg, None, K)
             work = None
             if world > 1 and args.allreduce == "overlap":
                 work = dist.all_reduce(gw, async_op=True)   # runs beside the input gradient
-            gx = _cabi.mvmr(w, go, i, j, seg, None, n, True)
+            gx = _cabi.mvmr(w, go, i, j, seg, None, n, True, engine=engine)
             if work is not None:
                 work.wait()
             elif world > 1:
@@ -320,7 +324,7 @@ def run_ours(args, rank, local_rank, world):
             if world > 1:
                 dist.all_reduce(gw)
             ev_side.record(side)
-        gx = _cabi.mvmr(w, go, i, j, seg, None, n, True)
+        gx = _cabi.mvmr(w, go, i, j, seg, None, n, True, engine=engine)
         main.wait_event(ev_side)
         gw.record_stream(main)
         return out, gx, gw
@@ -357,8 +361,10 @@ def run_ours(args, rank, local_rank, world):
     # sampler sees the GPU under load (the scene's working set stays in the L2: no flush)
     sustained = None
     if not args.resident_only:
-        est = max(total_ms / args.steps, 1e-3)
-        n_sus = int(min(max(2000.0 / est, 10), 200000))
+        est = torch.tensor([max(total_ms / args.steps, 1e-3)], dtype=torch.float64, device=dev)
+        if world > 1:   # every rank must run the same number of steps (each holds an all-reduce)
+            dist.all_reduce(est, op=dist.ReduceOp.MAX)
+        n_sus = int(min(max(2000.0 / float(est[0]), 10), 200000))
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         s0.record()
@@ -529,6 +535,7 @@ def run_ours(args, rank, local_rank, world):
             "config": {"workload": WORKLOAD, "points_per_rank": n, "triplets_rank0": T,
                        "triplets_per_point": T / n, "l2": "flushed between steps (256 MiB write)",
                        "collective": "all-reduce of dW per step" if world > 1 else "none",
+                       "mvmr_engine": args.engine,
                        "geometry_ms": geometry_ms},
             "tflops": 6.0 * T_all * C * M / (per_step_ms * 1e-3) / 1e12,
             "roofline": roofline,
@@ -559,6 +566,52 @@ def run_ours(args, rank, local_rank, world):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_geometry(args, local_rank):
+    """Secondary workload: the geometry stage alone on the scene of the headline run -- the
+    tap-segmented radius search (``build_triplets_segmented``) and the stride-2 centre-nearest
+    down-sampling -- as wall-clock milliseconds per call (each call ends with a host hand-over of a
+    count), points per second, and algorithmic bytes over time against the measured HBM bandwidth.
+    Algorithmic bytes: search 16(P+Q) coordinates and sample ids + 8P sorted key / index + 64Q cell
+    ranges + 8T edges + 8Q counts; down-sampling 32N in + 20S out."""
+    import torch
+
+    from pointelligence_b200 import _cabi
+    from pointelligence_b200.layers.downsample import downsample
+    from pointelligence_b200.layers.triplets import build_triplets_segmented
+    from pointelligence_b200.synthetic import indoor_scene
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    pts = torch.from_numpy(indoor_scene(args.points, 0)).to(dev)
+    n = pts.shape[0]
+    sample = torch.zeros(n, dtype=torch.int64, device=dev)
+    sizes = torch.tensor([n], device=dev)
+    build = lambda: build_triplets_segmented(pts, sample, sizes, RADIUS, KERNEL, radius_scaler=RADIUS / TAP_GRID)
+    down = lambda: downsample(pts, sample, 0.02, 2)
+    T, S = int(build()[0].numel()), int(down()[0].shape[0])
+    hbm, peak_kind = _peaks()
+    out = {}
+    for name, fn, nbytes in (("build_triplets_segmented", build, 16 * 2 * n + 8 * n + 64 * n + 8 * T + 8 * n),
+                             ("downsample_stride2", down, 32 * n + 20 * S)):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        _cabi.launch_count(reset=True)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            fn()
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) / args.steps * 1e3
+        out[name] = {"ms": ms, "mpoints_per_s": n / (ms * 1e-3) / 1e6, "algorithmic_bytes": nbytes,
+                     "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / hbm,
+                     "library_kernels_per_call": _cabi.launch_count() / args.steps}
+    print(json.dumps({"metric": "geometry_stage", "unit": "ms", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "data": "synthetic",
+                      "config": {"workload": f"indoor{n} geometry: radius 5 cm, 27 taps; stride-2 down-sampling at 2 cm",
+                                 "points": n, "triplets": T, "downsampled_points": S},
+                      "peak": hbm, "peak_source": peak_kind, "stages": out}), flush=True)
 
 
 def run_block_ops(args, local_rank):
@@ -796,7 +849,8 @@ def run_backbone(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: ranks that fall out of step fail within minutes instead of hanging
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     clocks = ClockSampler(local_rank, enabled=(rank == 0))
     clocks.start()
     _cabi.launch_count(reset=True)
@@ -830,7 +884,7 @@ def main():
     ap.add_argument("--overlap-grads", action="store_true",
                     help="run the weight gradient on a second stream beside the input gradient "
                          "(kernel timings then include the contention)")
-    ap.add_argument("--workload", default="conv", choices=["conv", "block_ops", "backbone"],
+    ap.add_argument("--workload", default="conv", choices=["conv", "block_ops", "backbone", "geometry"],
                     help="conv: the headline convolution step; block_ops: norm / pooling passes of a residual "
                          "block; backbone: one training step of the residual U-Net (weak scaling over ranks)")
     ap.add_argument("--scene", default="indoor", choices=["indoor", "lidar"],
@@ -840,6 +894,9 @@ def main():
     ap.add_argument("--scene-max", type=int, default=200000, help="backbone workload: largest scene")
     ap.add_argument("--allreduce", default="overlap", choices=["serial", "overlap"],
                     help="N > 1: all-reduce of dW after the input gradient (serial) or beside it (overlap)")
+    ap.add_argument("--engine", default="auto", choices=["auto", "scatter", "planned"],
+                    help="conv workload: MVMR engine of the resident step (auto: the library's own choice; scatter: "
+                         "tap-major tensor kernel with fp32 reductions; planned: output-stationary kernel)")
     ap.add_argument("--no-backbone", action="store_true",
                     help="conv workload: leave the backbone training step out of the run")
     ap.add_argument("--resident-only", action="store_true",
@@ -857,6 +914,10 @@ def main():
     if args.workload == "block_ops":
         if rank == 0:
             run_block_ops(args, local_rank)
+        return
+    if args.workload == "geometry":
+        if rank == 0:
+            run_geometry(args, local_rank)
         return
     run_ours(args, rank, local_rank, world)
 
