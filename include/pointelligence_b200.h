@@ -11,7 +11,8 @@
  *     aligned.
  *   - all work is enqueued on `stream` (a cudaStream_t passed as void*).
  *     Calls that have to return a data-dependent count to the host
- *     (pcx_radius_count, pcx_grid_sample_count) synchronise that stream once.
+ *     (pcx_radius_count, pcx_radius_taps_fill, pcx_grid_sample_count) synchronise
+ *     that stream once.
  *   - every function returns PCX_OK (0) or a negative pcx_status; it never
  *     throws and never terminates the process.  pcx_last_error_string() gives
  *     the message of the last failure on the calling thread.
@@ -358,6 +359,44 @@ int pcx_radius_fill(const float *d_points, const float *d_queries, int64_t P,
                     float *d_distances, int32_t *d_out_i, int32_t *d_out_j,
                     int32_t *d_out_k, void *d_ws, size_t ws_bytes, void *d_ws2,
                     size_t ws2_bytes, void *stream);
+
+/* The tap-segmented search (kernel_size 3 or 5) in one enqueue and ONE host
+ * hand-over; same outputs, bit for bit, as pcx_radius_count + pcx_radius_fill
+ * with kernel_size > 0 (same reference interface: internals/neighbors.py:919-955
+ * followed by the stable sort by tap of layers/triplets.py:431-520).
+ *
+ *   pcx_radius_taps_count  enqueues the binning, the count pass and the tap
+ *       segment offsets (d_num_neighbors (Q) int64, d_seg_offs (k^3+1) int64)
+ *       and returns without synchronising.
+ *   pcx_radius_taps_total  (optional) hands the number of pairs to the host
+ *       (one synchronisation) for a caller that has no capacity estimate.
+ *   pcx_radius_taps_fill   writes d_out_i / d_out_j (/ d_out_k when not NULL),
+ *       buffers of `capacity` int32 each, synchronises once and returns the
+ *       number of pairs in *h_total.  When the pairs do not fit it writes
+ *       nothing and returns PCX_E_CAPACITY with *h_total set: call it again
+ *       with buffers of that size (the state is kept in d_ws, which must stay
+ *       untouched between the calls).
+ *   h_total points at TWO int64: [0] the number of pairs, [1] the number of
+ *   queries that have no neighbour (the reference asserts there is none,
+ *   layers/triplets.py:431-520; the count saves the caller a pass and a
+ *   hand-over of its own).
+ *   pcx_radius_taps_supported  1 when kernel_size is served by this path. */
+int pcx_radius_taps_supported(int kernel_size);
+size_t pcx_radius_taps_workspace_bytes(int64_t P, int64_t Q, int kernel_size);
+int pcx_radius_taps_count(const float *d_points, const float *d_queries,
+                          const int32_t *d_point_sample, const int32_t *d_query_sample,
+                          int64_t P, int64_t Q, double radius, int distance_type,
+                          int kernel_size, double kernel_grid_size,
+                          int64_t *d_num_neighbors, int64_t *d_seg_offs, void *d_ws,
+                          size_t ws_bytes, void *stream);
+int pcx_radius_taps_total(int64_t P, int64_t Q, int kernel_size, int64_t *h_total,
+                          void *d_ws, size_t ws_bytes, void *stream);
+int pcx_radius_taps_fill(const float *d_queries, const int32_t *d_point_sample,
+                         const int32_t *d_query_sample, int64_t P, int64_t Q,
+                         double radius, int distance_type, int kernel_size,
+                         double kernel_grid_size, int64_t capacity, int32_t *d_out_i,
+                         int32_t *d_out_j, int32_t *d_out_k, int64_t *h_total,
+                         void *d_ws, size_t ws_bytes, void *stream);
 
 /* ------------------------------------------------------------------------
  * Centre-nearest grid down-sampling: one observed point per occupied cell of

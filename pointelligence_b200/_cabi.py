@@ -20,6 +20,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libpointelligence_b200.so")
 
 PCX_F32, PCX_F16, PCX_BF16 = 0, 1, 2
 ENGINE_AUTO, ENGINE_CUDA_CORE, ENGINE_TENSOR = 0, 1, 2
+PCX_E_CAPACITY = -4
 
 _DTYPES = {torch.float32: PCX_F32, torch.float16: PCX_F16, torch.bfloat16: PCX_BF16}
 
@@ -87,6 +88,13 @@ SIGNATURES = {
                          + [c_void_p] * 3 + [c_void_p, c_size_t, c_void_p]),
     "pcx_radius_fill": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_int, c_double,
                                 c_int64] + [c_void_p] * 5 + [c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
+    "pcx_radius_taps_supported": (c_int, [c_int]),
+    "pcx_radius_taps_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),
+    "pcx_radius_taps_count": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_double, c_int, c_int, c_double]
+                              + [c_void_p] * 2 + [c_void_p, c_size_t, c_void_p]),
+    "pcx_radius_taps_total": (c_int, [c_int64, c_int64, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "pcx_radius_taps_fill": (c_int, [c_void_p] * 3 + [c_int64, c_int64, c_double, c_int, c_int, c_double, c_int64]
+                             + [c_void_p] * 4 + [c_void_p, c_size_t, c_void_p]),
     "pcx_grid_sample_workspace_bytes": (c_size_t, [c_int64]),
     "pcx_grid_sample_count": (c_int, [c_void_p, c_void_p, c_int64, c_double, c_void_p, c_void_p, c_size_t,
                                       c_void_p]),
@@ -606,10 +614,13 @@ def radius_search(points, queries, radius, point_sample, query_sample, distance_
     require_cuda(points, queries, point_sample, query_sample)
     dev = points.device
     points, queries = points.contiguous(), queries.contiguous()
-    ps, qs = as_i32(point_sample), as_i32(query_sample)
+    ps = as_i32(point_sample)
+    qs = ps if query_sample is point_sample else as_i32(query_sample)
     P, Q = points.shape[0], queries.shape[0]
     L = lib()
     k3 = kernel_size ** 3
+    if kernel_size > 0 and L.pcx_radius_taps_supported(kernel_size) and os.environ.get("PCX_RADIUS_TAPS", "1") != "0":
+        return _radius_taps(points, queries, radius, ps, qs, distance_type, kernel_size, kernel_grid_size, want_k)
     with torch.cuda.device(dev):
         ws = workspace(L.pcx_radius_workspace_bytes(P, Q, kernel_size), dev)
         num_neighbors = torch.empty(Q, dtype=torch.int64, device=dev)
@@ -638,6 +649,52 @@ def radius_search(points, queries, radius, point_sample, query_sample, distance_
                                 float(kernel_grid_size), total, None, None, ptr(out_i), ptr(out_j), ptr(out_k),
                                 ptr(ws), ws.numel(), ptr(ws2), ws2.numel(), stream_ptr()))
     return out_i, out_j, out_k, seg, num_neighbors
+
+
+# Largest pairs-per-query ratio seen per (kernel_size, distance_type): sizes the edge buffers of the
+# next tap-segmented search so that it needs one host hand-over instead of two.
+_TAPS_RATIO = {}
+
+
+def _radius_taps(points, queries, radius, ps, qs, distance_type, kernel_size, kernel_grid_size, want_k):
+    """Tap-segmented search through ``pcx_radius_taps_*``: the pairs are written into buffers sized
+    from the density of earlier searches (exactly sized after a counted first call or when the
+    estimate turns out too small) and returned as views of the first ``total`` entries."""
+    dev = points.device
+    P, Q = points.shape[0], queries.shape[0]
+    L = lib()
+    k3 = kernel_size ** 3
+    with torch.cuda.device(dev):
+        ws = workspace(L.pcx_radius_taps_workspace_bytes(P, Q, kernel_size), dev)
+        num_neighbors = torch.empty(Q, dtype=torch.int64, device=dev)
+        seg = torch.empty(k3 + 1, dtype=torch.int64, device=dev)
+        check(L.pcx_radius_taps_count(ptr(points), ptr(queries), ptr(ps), ptr(qs), P, Q, float(radius),
+                                      distance_type, kernel_size, float(kernel_grid_size), ptr(num_neighbors),
+                                      ptr(seg), ptr(ws), ws.numel(), stream_ptr()))
+        total = (c_int64 * 2)()
+        ratio = _TAPS_RATIO.get((kernel_size, distance_type))
+        if ratio is None:
+            check(L.pcx_radius_taps_total(P, Q, kernel_size, total, ptr(ws), ws.numel(), stream_ptr()))
+            capacity = int(total[0])
+        else:
+            capacity = min(int(ratio * Q * 1.25) + 4096, 2 ** 31 - 1)
+        for attempt in range(2):
+            out_i = torch.empty(capacity, dtype=torch.int32, device=dev)
+            out_j = torch.empty(capacity, dtype=torch.int32, device=dev)
+            out_k = torch.empty(capacity, dtype=torch.int32, device=dev) if want_k else None
+            rc = L.pcx_radius_taps_fill(ptr(queries), ptr(ps), ptr(qs), P, Q, float(radius), distance_type,
+                                        kernel_size, float(kernel_grid_size), capacity, ptr(out_i), ptr(out_j),
+                                        ptr(out_k), total, ptr(ws), ws.numel(), stream_ptr())
+            if rc == PCX_E_CAPACITY and attempt == 0 and int(total[0]) > capacity:
+                capacity = int(total[0])   # the estimate was too small: exact size, fill pass only
+                continue
+            check(rc)
+            break
+        raise_if_device_reported()   # the fill above ended with a host hand-over: the stream is idle
+        n = int(total[0])
+        _TAPS_RATIO[(kernel_size, distance_type)] = max(ratio or 0.0, n / Q)
+        num_neighbors.pcx_queries_without_neighbor = int(total[1])   # spares the caller a pass over the counts
+    return out_i[:n], out_j[:n], (out_k[:n] if want_k else None), seg, num_neighbors
 
 
 def grid_sample_center_nearest(points, cell, sample, return_mapping):

@@ -20,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "lib", "obj")
 LIB = os.path.join(HERE, "lib", "libpointelligence_b200.so")
 SOURCES = ("status.cu", "geometry.cu", "sparse_generic.cu", "sparse_tc.cu", "sparse_api.cu",
-           "sparse_noalloc.cu", "segment_reduce.cu", "ragged_norm.cu", "mvmr_os.cu", "rnet.cu")
+           "sparse_noalloc.cu", "segment_reduce.cu", "ragged_norm.cu", "mvmr_os.cu", "rnet.cu", "radius_taps.cu")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xptxas", "-v"] + os.environ.get("PCX_NVCC_EXTRA", "").split()

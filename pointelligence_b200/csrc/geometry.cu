@@ -21,9 +21,10 @@
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 
-#include "common.cuh"
+#include "geometry.cuh"
 
 namespace pcx {
+using namespace geo;
 namespace {
 
 constexpr int kWarpsPerBlock = 8;
@@ -82,11 +83,6 @@ size_t carve_radius(void *ws, int64_t P, int64_t Q, int kernel_size, RadiusWs *o
     w.cub_tmp = c.take<char>(w.cub_bytes);
     if (out) *out = w;
     return c.off;
-}
-
-__device__ __forceinline__ int cell_of(float v, float inv) { return (int)floorf(__fmul_rn(v, inv)); }
-__device__ __forceinline__ int corner_of(float v, float r32, float inv) {
-    return (int)floorf(__fmul_rn(__fsub_rn(v, r32), inv));
 }
 
 // Running min / max of a thread's cells; folded per warp, then per block in shared memory, and
@@ -162,14 +158,6 @@ __global__ void radius_key_kernel(const float *__restrict__ pts, const int32_t *
 // Cell table: key -> [start, end) of the cell's points in the sorted order.  Heads of
 // runs insert (key, start); tails look their slot up and add the end.  Keys are >= 0.
 constexpr int64_t CELL_EMPTY = -1;
-__device__ __forceinline__ uint64_t mix64(uint64_t x) {
-    x ^= x >> 33;
-    x *= 0xff51afd7ed558ccdULL;
-    x ^= x >> 33;
-    x *= 0xc4ceb9fe1a85ec53ULL;
-    x ^= x >> 33;
-    return x;
-}
 __global__ void cell_table_heads_kernel(const int64_t *__restrict__ keys, int64_t P, int64_t *tkeys, int2 *tranges,
                                         uint64_t mask) {
     int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -211,47 +199,6 @@ __global__ void radius_gather_kernel(const float *__restrict__ pts, const int32_
     int32_t p = perm[s];
     sorted_pts[s] = make_float4(pts[3 * (int64_t)p], pts[3 * (int64_t)p + 1], pts[3 * (int64_t)p + 2],
                                 __int_as_float(p));
-}
-
-// Radius predicate  sqrt(dx*dx + dy*dy + dz*dz) <= R  in fp32.
-//   variant 0  the expression as written: one rounding per operation (what the
-//              reference computes under Triton's CPU interpreter and in numpy)
-//   variant 1  the sum of squares contracted into fma(dz,dz, fma(dx,dx, dy*dy)),
-//              which is what Triton compiles the expression to on a B200: on
-//              1,048,576 pairs placed within 3 ulp of R the accepted sets were
-//              identical, while variant 0 changed the neighbour count of 214 of the 4096 queries
-//   variant 2  variant 1 with the approximate square root (same sets as 1 in
-//              that measurement)
-// Pairs farther than an ulp or two from R are classified identically by all.
-__device__ __forceinline__ bool radius_accept(float qx, float qy, float qz, float4 p, float r32,
-                                              int distance_type, int variant, float *dist_out) {
-    float dx = __fsub_rn(qx, p.x), dy = __fsub_rn(qy, p.y), dz = __fsub_rn(qz, p.z);
-    float d;
-    if (distance_type == 0) {
-        float s;
-        if (variant == 0) {
-            s = __fadd_rn(__fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy)), __fmul_rn(dz, dz));
-            d = __fsqrt_rn(s);
-        } else {
-            s = __fmaf_rn(dz, dz, __fmaf_rn(dx, dx, __fmul_rn(dy, dy)));
-            if (variant == 1) d = __fsqrt_rn(s);
-            else asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(d) : "f"(s));
-        }
-    } else {
-        d = fmaxf(fmaxf(fabsf(dx), fabsf(dy)), fabsf(dz));
-    }
-    *dist_out = d;
-    return d <= r32;
-}
-
-__device__ __forceinline__ int tap_of(float qx, float qy, float qz, float4 p, float g32, int K) {
-    int half = K >> 1;
-    int dx = __float2int_rn(__fdiv_rn(__fsub_rn(p.x, qx), g32));
-    int dy = __float2int_rn(__fdiv_rn(__fsub_rn(p.y, qy), g32));
-    int dz = __float2int_rn(__fdiv_rn(__fsub_rn(p.z, qz), g32));
-    int kx = min(max(dx + half, 0), K - 1), ky = min(max(dy + half, 0), K - 1),
-        kz = min(max(dz + half, 0), K - 1);
-    return (kx * K + ky) * K + kz;
 }
 
 struct ScanArgs {
@@ -542,10 +489,18 @@ __global__ void grid_select_kernel(const float *__restrict__ pts, const int32_t 
     if (out_sample) out_sample[seg] = sample ? sample[best_idx] : 0;
 }
 
+int bits_for(int64_t n) {
+    int b = 1;
+    while (((int64_t)1 << b) < n) ++b;
+    return b;
+}
+
+}  // namespace
+
 // Predicate arithmetic in use (see radius_accept): 1 by default -- the FMA
 // chain the reference's Triton kernels compile to on sm_100, measured on a B200
 // -- overridable by the environment (PCX_RADIUS_PREDICATE) and at run time.
-std::atomic<int> g_radius_variant{-1};
+static std::atomic<int> g_radius_variant{-1};
 
 int radius_variant() {
     int v = g_radius_variant.load();
@@ -558,13 +513,6 @@ int radius_variant() {
     return v;
 }
 
-int bits_for(int64_t n) {
-    int b = 1;
-    while (((int64_t)1 << b) < n) ++b;
-    return b;
-}
-
-}  // namespace
 }  // namespace pcx
 
 using namespace pcx;
@@ -771,8 +719,26 @@ int pcx_grid_sample_count(const float *d_points, const int32_t *d_sample, int64_
     unsigned nb = (unsigned)((N + 255) / 256);
     grid_key_kernel<<<nb, 256, 0, stream>>>(d_points, d_sample, N, c32, w.ext, w.keys_a, w.vals_a);
     PCX_LAUNCH_CHECK();
+    // The sort only has to look at the bits the largest key can use: the extents come to the host
+    // (32 bytes; the call ends with a hand-over of the cell count anyway).
+    int32_t h_ext[8];
+    PCX_CUDA(cudaMemcpyAsync(h_ext, w.ext, sizeof(h_ext), cudaMemcpyDeviceToHost, stream));
+    PCX_CUDA(cudaStreamSynchronize(stream));
+    int key_bits = 64;
+    {
+        uint64_t span = 1;
+        bool fits = true;
+        for (int a = 0; a < 4 && fits; ++a) {
+            const int64_t e = (int64_t)h_ext[4 + a] - h_ext[a] + 1;
+            fits = e > 0 && !__builtin_mul_overflow(span, (uint64_t)e, &span);
+        }
+        if (fits) {
+            key_bits = 1;
+            while (key_bits < 64 && ((span - 1) >> key_bits)) ++key_bits;
+        }
+    }
     size_t tmp = w.cub_bytes;
-    PCX_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, tmp, w.keys_a, w.keys_b, w.vals_a, w.vals_b, N, 0, 64, stream));
+    PCX_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, tmp, w.keys_a, w.keys_b, w.vals_a, w.vals_b, N, 0, key_bits, stream));
     grid_flag_kernel<<<nb, 256, 0, stream>>>(w.keys_b, N, w.flags);
     PCX_LAUNCH_CHECK();
     tmp = w.cub_bytes;

@@ -131,7 +131,10 @@ def radius_search_sorted_grid8_segments(points, queries, radius, kernel_size, ke
     i, j, k, seg, counts = _cabi.radius_search(_f32(points), _f32(queries), float(radius), sample_inds,
                                                query_sample_inds, code, kernel_size=kernel_size,
                                                kernel_grid_size=float(kernel_grid_size), want_k=return_k)
-    out = (i, j, seg, counts.to(dtype_num_neighbors))
+    cast = counts.to(dtype_num_neighbors)
+    if hasattr(counts, "pcx_queries_without_neighbor"):
+        cast.pcx_queries_without_neighbor = counts.pcx_queries_without_neighbor
+    out = (i, j, seg, cast)
     return out + (k,) if return_k else out
 
 

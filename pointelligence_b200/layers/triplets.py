@@ -105,7 +105,10 @@ def build_triplets_segmented(points, sample_inds, sample_sizes, neighbor_radius,
             kernel_grid_size=kernel_grid_size, sample_inds=sample_inds,
             query_sample_inds=query_sample_inds, dtype_num_neighbors=torch.int64,
             distance_type="ball", tap_stripes=tap_stripes, return_k=True)
-        if num_neighbors.numel() and bool((num_neighbors == 0).any().item()):
+        lonely = getattr(num_neighbors, "pcx_queries_without_neighbor", None)   # counted by the search itself
+        if lonely is None:
+            lonely = int((num_neighbors == 0).sum().item()) if num_neighbors.numel() else 0
+        if lonely:
             raise AssertionError(_NO_NEIGHBOR_MSG)
         out = (i, j, k, seg_offs, (num_neighbors if return_num_neighbors else None))
         cache_put(key, out, points)
