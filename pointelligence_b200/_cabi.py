@@ -391,6 +391,23 @@ def mvmr(weight, feat, gather, scatter, seg_offs, tap_idx, n_out, transpose, eng
     return out
 
 
+def prepare_mvmr(weight, gather, scatter, seg_offs, n_out, transpose=False):
+    """Build (and cache) now what ``mvmr`` with the automatic engine would build on its first call
+    for this rulebook -- the plan of the output-stationary kernel, whose construction ends with a
+    host hand-over -- so that the feature pass itself is kernels only.  Returns True when a plan
+    was prepared, False when the policy keeps the scatter engines (which need no preparation)."""
+    K, G, C, M = weight.shape
+    n_out = int(n_out)
+    outw = C if transpose else M
+    if not (gather is not None and gather.is_cuda and planned_supported(weight, weight, gather, scatter, seg_offs,
+                                                                        n_out, transpose)):
+        return False
+    if not _planned_pays(gather.numel(), n_out, outw, K):
+        return False
+    cached_mvmr_plan(scatter, gather, seg_offs, K, n_out, plan_group_blocks(outw))
+    return True
+
+
 def vvor(a, a_idx, b, b_idx, seg_offs, o_idx, n_o, engine=ENGINE_AUTO):
     """``out[o[t], g, m, c] += a[a_idx[t], g, m] * b[b_idx[t], g, c]``.
 
@@ -651,8 +668,8 @@ def radius_search(points, queries, radius, point_sample, query_sample, distance_
     return out_i, out_j, out_k, seg, num_neighbors
 
 
-# Largest pairs-per-query ratio seen per (kernel_size, distance_type): sizes the edge buffers of the
-# next tap-segmented search so that it needs one host hand-over instead of two.
+# Largest pairs-per-query ratio seen per (kernel_size, distance_type, radius) -- one entry per level of a
+# network: sizes the edge buffers of the next such search so that it needs one host hand-over, not two.
 _TAPS_RATIO = {}
 
 
@@ -672,7 +689,8 @@ def _radius_taps(points, queries, radius, ps, qs, distance_type, kernel_size, ke
                                       distance_type, kernel_size, float(kernel_grid_size), ptr(num_neighbors),
                                       ptr(seg), ptr(ws), ws.numel(), stream_ptr()))
         total = (c_int64 * 2)()
-        ratio = _TAPS_RATIO.get((kernel_size, distance_type))
+        ratio_key = (kernel_size, distance_type, float(radius))
+        ratio = _TAPS_RATIO.get(ratio_key)
         if ratio is None:
             check(L.pcx_radius_taps_total(P, Q, kernel_size, total, ptr(ws), ws.numel(), stream_ptr()))
             capacity = int(total[0])
@@ -692,7 +710,9 @@ def _radius_taps(points, queries, radius, ps, qs, distance_type, kernel_size, ke
             break
         raise_if_device_reported()   # the fill above ended with a host hand-over: the stream is idle
         n = int(total[0])
-        _TAPS_RATIO[(kernel_size, distance_type)] = max(ratio or 0.0, n / Q)
+        if len(_TAPS_RATIO) > 256:
+            _TAPS_RATIO.clear()
+        _TAPS_RATIO[ratio_key] = max(ratio or 0.0, n / Q)
         num_neighbors.pcx_queries_without_neighbor = int(total[1])   # spares the caller a pass over the counts
     return out_i[:n], out_j[:n], (out_k[:n] if want_k else None), seg, num_neighbors
 

@@ -78,9 +78,9 @@ def test_batched_samples_separate_queries_and_capacity_retry():
     _assert_same(ref, got)
     assert bool((smp3[got[0].long()] == smp3[got[1].long()]).all())
     # an estimate that is far too small: the wrapper retries the fill pass with the exact size
-    _cabi._TAPS_RATIO[(3, 0)] = 0.01
+    _cabi._TAPS_RATIO[(3, 0, 0.05)] = 0.01
     _assert_same(*_both(pts, qry, smp, qs, 0.05, 3, 0.02))
-    assert _cabi._TAPS_RATIO[(3, 0)] > 1.0
+    assert _cabi._TAPS_RATIO[(3, 0, 0.05)] > 1.0
 
 
 def test_long_runs_and_negative_coordinates():
