@@ -300,6 +300,28 @@ int pcx_ragged_layer_norm_backward(const void *d_grad_y, const void *d_x,
                                    int C, int relu, int dtype, void *d_ws,
                                    size_t ws_bytes, void *stream);
 
+/* Group and instance normalisation over a ragged batch:
+ *   y = (x - mean_{s,g}) * rstd_{s,g} * weight + bias
+ * with the statistics over the rows of sample s and the W = C / G consecutive
+ * channels of group g (instance norm: G = C), two-pass, as RaggedGroupNorm /
+ * RaggedInstanceNorm compose them (layers/norm.py:86-116 of the reference).
+ * d_mean / d_rstd (fp32, S * G, index s * G + g) are outputs kept for the
+ * backward; d_weight / d_bias (fp32, C) may both be null; workspace of
+ * pcx_ragged_group_norm_workspace_bytes(S, G).  G <= 8192 (4096 backward). */
+size_t pcx_ragged_group_norm_workspace_bytes(int64_t S, int G);
+int pcx_ragged_group_norm(const void *d_x, const int64_t *d_lengths,
+                          const float *d_weight, const float *d_bias, void *d_y,
+                          float *d_mean, float *d_rstd, int64_t N, int64_t S, int C,
+                          int G, double eps, int dtype, void *d_ws, size_t ws_bytes,
+                          void *stream);
+int pcx_ragged_group_norm_backward(const void *d_grad_y, const void *d_x,
+                                   const int64_t *d_lengths, const float *d_weight,
+                                   const float *d_mean, const float *d_rstd,
+                                   void *d_grad_x, float *d_grad_weight,
+                                   float *d_grad_bias, int64_t N, int64_t S, int C,
+                                   int G, int dtype, void *d_ws, size_t ws_bytes,
+                                   void *stream);
+
 /* ------------------------------------------------------------------------
  * Tap bookkeeping.
  * pcx_seg_offs: seg[k] = first position with value >= k in a sorted int32

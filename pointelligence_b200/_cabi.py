@@ -74,6 +74,11 @@ SIGNATURES = {
                                                       c_size_t, c_void_p]),
     "pcx_ragged_layer_norm_backward": (c_int, [c_void_p] * 11 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
                                                                 c_size_t, c_void_p]),
+    "pcx_ragged_group_norm_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "pcx_ragged_group_norm": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_double, c_int, c_void_p,
+                                                      c_size_t, c_void_p]),
+    "pcx_ragged_group_norm_backward": (c_int, [c_void_p] * 9 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
+                                                               c_size_t, c_void_p]),
     "pcx_rnet_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "pcx_rnet_far": (c_int, [c_void_p] * 3 + [c_int64, c_void_p, c_void_p]),
     "pcx_rnet_rounds": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_void_p, c_void_p, ctypes.POINTER(ctypes.c_int32),
@@ -567,6 +572,46 @@ def ragged_layer_norm_backward(grad_y, x, y, lengths, weight, mean, rstd, relu, 
                                                int(bool(relu)), dtype_code(x.dtype), ptr(ws), ws.numel(),
                                                stream_ptr()))
     return grad_x, gw, gb, gres
+
+
+def ragged_group_norm(x, lengths, weight, bias, groups, eps):
+    """Group norm per sample (``groups`` blocks of consecutive channels; ``groups == C`` is the
+    instance norm); returns ``(y, mean, rstd)`` with the statistics as (S * groups,) fp32."""
+    require_cuda(x, lengths, weight, bias)
+    x = x.contiguous()
+    lengths = lengths.to(torch.int64).contiguous()
+    weight, bias = _f32_or_none(weight), _f32_or_none(bias)
+    N, C = x.shape
+    S, G = lengths.numel(), int(groups)
+    y = torch.empty_like(x)
+    mean = torch.empty(S * G, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(S * G, dtype=torch.float32, device=x.device)
+    L = lib()
+    with torch.cuda.device(x.device):
+        ws = workspace(L.pcx_ragged_group_norm_workspace_bytes(S, G), x.device)
+        check(L.pcx_ragged_group_norm(ptr(x), ptr(lengths), ptr(weight), ptr(bias), ptr(y), ptr(mean), ptr(rstd),
+                                      N, S, C, G, float(eps), dtype_code(x.dtype), ptr(ws), ws.numel(), stream_ptr()))
+    return y, mean, rstd
+
+
+def ragged_group_norm_backward(grad_y, x, lengths, weight, mean, rstd, groups, want_affine):
+    """Returns ``(grad_x, grad_weight|None, grad_bias|None)`` (affine gradients in fp32)."""
+    require_cuda(grad_y, x, lengths)
+    grad_y, x = grad_y.contiguous(), x.contiguous()
+    lengths = lengths.to(torch.int64).contiguous()
+    weight = _f32_or_none(weight)
+    N, C = x.shape
+    S, G = lengths.numel(), int(groups)
+    grad_x = torch.empty_like(x)
+    gw = torch.empty(C, dtype=torch.float32, device=x.device) if want_affine else None
+    gb = torch.empty(C, dtype=torch.float32, device=x.device) if want_affine else None
+    L = lib()
+    with torch.cuda.device(x.device):
+        ws = workspace(L.pcx_ragged_group_norm_workspace_bytes(S, G), x.device)
+        check(L.pcx_ragged_group_norm_backward(ptr(grad_y), ptr(x), ptr(lengths), ptr(weight), ptr(mean), ptr(rstd),
+                                               ptr(grad_x), ptr(gw), ptr(gb), N, S, C, G, dtype_code(x.dtype), ptr(ws),
+                                               ws.numel(), stream_ptr()))
+    return grad_x, gw, gb
 
 
 def seg_offs_from_sorted(idx_sorted, K):

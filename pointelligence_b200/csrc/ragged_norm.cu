@@ -264,6 +264,253 @@ __global__ void ln_bwd_apply_kernel(const T *__restrict__ g, const T *__restrict
     }
 }
 
+// ---------------------------------------------------------------- grouped statistics ----
+// Group and instance normalisation: the statistics of sample s are kept per channel group g
+// (G groups of W = C / G consecutive channels; instance norm is W = 1) in arrays indexed
+// s * G + g.  Same block shape as above; a thread's VN channels may fall into different groups,
+// so every channel keeps its own running sum.  Blocks inside one sample fold their sums per
+// group in shared memory (G floats) and issue one atomic per group; blocks that straddle a
+// sample boundary use per-thread atomics.
+struct GroupStats {
+    float mu[8], rs[8];
+    int64_t at = -1;
+    template <int VN>
+    __device__ __forceinline__ void load(const float *__restrict__ mean, const float *__restrict__ rstd, int64_t s,
+                                         int G, const int *g) {
+        if (s == at) return;
+        at = s;
+#pragma unroll
+        for (int i = 0; i < VN; ++i) {
+            mu[i] = mean ? mean[s * G + g[i]] : 0.f;
+            rs[i] = rstd ? rstd[s * G + g[i]] : 1.f;
+        }
+    }
+};
+
+template <int VN>
+__device__ __forceinline__ void flush_groups(float *dst, const int *g, float *v) {
+#pragma unroll
+    for (int i = 0; i < VN; ++i) {
+        if (v[i] != 0.f) atomicAdd(dst + g[i], v[i]);
+        v[i] = 0.f;
+    }
+}
+
+// sums[s * G + g] += sum of x (mean == null) or of (x - mean)^2
+template <typename T, int VN>
+__global__ void gn_sum_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets,
+                              const float *__restrict__ mean, float *sums, int64_t N, int64_t S, int C, int G) {
+    extern __shared__ float s_grp[];
+    const BlockRows B(offsets, N, S);
+    const RowLayout L(C, VN);
+    const int W = C / G;
+    if (B.uniform) {
+        for (int t = threadIdx.x; t < G; t += blockDim.x) s_grp[t] = 0.f;
+        __syncthreads();
+    }
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        if (vcol >= L.vc_total || L.lane >= L.lanes) continue;
+        int g[VN];
+        float acc[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) g[i] = (vcol * VN + i) / W, acc[i] = 0.f;
+        GroupStats st;
+        int64_t cur = B.s_first;
+#pragma unroll 2
+        for (int64_t r = B.row0 + L.lane; r < B.row1; r += L.lanes) {
+            const int64_t s = B.uniform ? B.s_first : segment_of_row(offsets, S, r);
+            if (s != cur) {
+                flush_groups<VN>(sums + cur * G, g, acc);
+                cur = s;
+            }
+            st.load<VN>(mean, nullptr, s, G, g);
+            float v[VN];
+            load_vec<T, VN>(x + r * C + (int64_t)vcol * VN, v);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                const float d = v[i] - st.mu[i];
+                acc[i] += mean ? d * d : d;
+            }
+        }
+        flush_groups<VN>(B.uniform ? s_grp : sums + cur * G, g, acc);
+    }
+    if (B.uniform) {
+        __syncthreads();
+        for (int t = threadIdx.x; t < G; t += blockDim.x)
+            if (s_grp[t] != 0.f) atomicAdd(sums + B.s_first * G + t, s_grp[t]);
+    }
+}
+
+__global__ void gn_stats_kernel(const float *__restrict__ sums, const int64_t *__restrict__ offsets, float *mean,
+                                float *rstd, int64_t S, int G, int W, float eps, int second) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= S * G) return;
+    const int64_t s = t / G, len = offsets[s + 1] - offsets[s];
+    const float n = (float)(len > 0 ? len : 1) * (float)W;
+    if (!second) mean[t] = sums[t] / n;
+    else rstd[t] = 1.f / sqrtf(sums[t] / n + eps);
+}
+
+template <typename T, int VN>
+__global__ void gn_apply_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets,
+                                const float *__restrict__ mean, const float *__restrict__ rstd,
+                                const float *__restrict__ weight, const float *__restrict__ bias, T *y, int64_t N,
+                                int64_t S, int C, int G) {
+    const BlockRows B(offsets, N, S);
+    const RowLayout L(C, VN);
+    const int W = C / G;
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        if (vcol >= L.vc_total || L.lane >= L.lanes) continue;
+        int g[VN];
+        float w[VN], b[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) {
+            g[i] = (vcol * VN + i) / W;
+            w[i] = weight ? weight[vcol * VN + i] : 1.f;
+            b[i] = weight ? bias[vcol * VN + i] : 0.f;
+        }
+        GroupStats st;
+#pragma unroll 2
+        for (int64_t r = B.row0 + L.lane; r < B.row1; r += L.lanes) {
+            const int64_t s = B.uniform ? B.s_first : segment_of_row(offsets, S, r);
+            st.load<VN>(mean, rstd, s, G, g);
+            const int64_t at = r * C + (int64_t)vcol * VN;
+            float v[VN];
+            load_vec<T, VN>(x + at, v);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) v[i] = (v[i] - st.mu[i]) * st.rs[i] * w[i] + b[i];
+            store_vec<T, VN>(y + at, v);
+        }
+    }
+}
+
+// Backward of the grouped norms, with gh = g * weight, xh = (x - mean) * rstd, n = rows_s * W:
+//   dx = rstd * (gh - sum_{s,g}(gh) / n - xh * sum_{s,g}(gh * xh) / n),
+//   dweight[c] = sum over rows of g * xh, dbias[c] = sum over rows of g.
+template <typename T, int VN>
+__global__ void gn_bwd_sums_kernel(const T *__restrict__ g_out, const T *__restrict__ x,
+                                   const int64_t *__restrict__ offsets, const float *__restrict__ mean,
+                                   const float *__restrict__ rstd, const float *__restrict__ weight, float *s1,
+                                   float *s2, float *dweight, float *dbias, int64_t N, int64_t S, int C, int G) {
+    extern __shared__ float s_grp[];   // 2 G: sums of gh, sums of gh * xh
+    __shared__ float col_w[LN_THREADS * VN], col_b[LN_THREADS * VN];
+    const BlockRows B(offsets, N, S);
+    const RowLayout L(C, VN);
+    const int W = C / G;
+    if (B.uniform) {
+        for (int t = threadIdx.x; t < 2 * G; t += blockDim.x) s_grp[t] = 0.f;
+        __syncthreads();
+    }
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        const bool active = vcol < L.vc_total && L.lane < L.lanes;
+        int g[VN];
+        float w[VN], a[VN], b[VN], dw[VN], db[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) {
+            g[i] = active ? (vcol * VN + i) / W : 0;
+            w[i] = (weight && active) ? weight[vcol * VN + i] : 1.f;
+            a[i] = b[i] = dw[i] = db[i] = 0.f;
+        }
+        GroupStats st;
+        int64_t cur = B.s_first;
+#pragma unroll 2
+        for (int64_t r = B.row0 + L.lane; active && r < B.row1; r += L.lanes) {
+            const int64_t s = B.uniform ? B.s_first : segment_of_row(offsets, S, r);
+            if (s != cur) {
+                flush_groups<VN>(s1 + cur * G, g, a);
+                flush_groups<VN>(s2 + cur * G, g, b);
+                cur = s;
+            }
+            st.load<VN>(mean, rstd, s, G, g);
+            const int64_t at = r * C + (int64_t)vcol * VN;
+            float gv[VN], xv[VN];
+            load_vec<T, VN>(g_out + at, gv);
+            load_vec<T, VN>(x + at, xv);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                const float xh = (xv[i] - st.mu[i]) * st.rs[i];
+                a[i] += gv[i] * w[i];
+                b[i] += gv[i] * w[i] * xh;
+                dw[i] += gv[i] * xh;
+                db[i] += gv[i];
+            }
+        }
+        flush_groups<VN>(B.uniform ? s_grp : s1 + cur * G, g, a);
+        flush_groups<VN>(B.uniform ? s_grp + G : s2 + cur * G, g, b);
+        if (dweight) {   // fold the row lanes in shared memory, then one atomic per channel and block
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                col_w[(L.lane * L.vcb + L.vc) * VN + i] = dw[i];
+                col_b[(L.lane * L.vcb + L.vc) * VN + i] = db[i];
+            }
+            __syncthreads();
+            const int cols = L.vcb * VN;
+            for (int t = threadIdx.x; t < cols; t += LN_THREADS) {
+                const int c = cp * cols + t;
+                if (c < C) {
+                    float tw = 0.f, tb = 0.f;
+                    for (int q = 0; q < L.lanes; ++q) tw += col_w[q * cols + t], tb += col_b[q * cols + t];
+                    atomicAdd(dweight + c, tw);
+                    atomicAdd(dbias + c, tb);
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (B.uniform) {
+        __syncthreads();
+        for (int t = threadIdx.x; t < G; t += blockDim.x) {
+            if (s_grp[t] != 0.f) atomicAdd(s1 + B.s_first * G + t, s_grp[t]);
+            if (s_grp[G + t] != 0.f) atomicAdd(s2 + B.s_first * G + t, s_grp[G + t]);
+        }
+    }
+}
+
+template <typename T, int VN>
+__global__ void gn_bwd_apply_kernel(const T *__restrict__ g_out, const T *__restrict__ x,
+                                    const int64_t *__restrict__ offsets, const float *__restrict__ mean,
+                                    const float *__restrict__ rstd, const float *__restrict__ weight,
+                                    const float *__restrict__ s1, const float *__restrict__ s2, T *dx, int64_t N,
+                                    int64_t S, int C, int G) {
+    const BlockRows B(offsets, N, S);
+    const RowLayout L(C, VN);
+    const int W = C / G;
+    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+        const int vcol = cp * L.vcb + L.vc;
+        if (vcol >= L.vc_total || L.lane >= L.lanes) continue;
+        int g[VN];
+        float w[VN], m1[VN], m2[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) g[i] = (vcol * VN + i) / W, w[i] = weight ? weight[vcol * VN + i] : 1.f;
+        GroupStats st;
+        int64_t have = -1;
+#pragma unroll 2
+        for (int64_t r = B.row0 + L.lane; r < B.row1; r += L.lanes) {
+            const int64_t s = B.uniform ? B.s_first : segment_of_row(offsets, S, r);
+            st.load<VN>(mean, rstd, s, G, g);
+            if (s != have) {
+                have = s;
+                const float inv_n = 1.f / ((float)(offsets[s + 1] - offsets[s]) * (float)W);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) m1[i] = s1[s * G + g[i]] * inv_n, m2[i] = s2[s * G + g[i]] * inv_n;
+            }
+            const int64_t at = r * C + (int64_t)vcol * VN;
+            float gv[VN], xv[VN];
+            load_vec<T, VN>(g_out + at, gv);
+            load_vec<T, VN>(x + at, xv);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                const float xh = (xv[i] - st.mu[i]) * st.rs[i];
+                gv[i] = st.rs[i] * (gv[i] * w[i] - m1[i] - xh * m2[i]);
+            }
+            store_vec<T, VN>(dx + at, gv);
+        }
+    }
+}
+
 struct LnWs {
     int64_t *offsets;
     float *sums;   // 2 * S
@@ -380,6 +627,83 @@ int pcx_ragged_layer_norm_backward(const void *d_grad_y, const void *d_x, const 
     PCX_LN_DISPATCH(dtype, vec, (ln_bwd_apply_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>(
                                (const T *)d_grad_y, (const T *)d_x, (const T *)d_y, w.offsets, d_mean, d_rstd, d_weight,
                                w.sums, w.sums + S, (T *)d_grad_x, N, S, C, relu)));
+    PCX_LAUNCH_CHECK();
+    return PCX_OK;
+}
+
+size_t pcx_ragged_group_norm_workspace_bytes(int64_t S, int G) {
+    return (S <= 0 || G <= 0 || S * (int64_t)G > INT32_MAX) ? 0 : carve_ln(nullptr, S * G, nullptr);
+}
+
+int pcx_ragged_group_norm(const void *d_x, const int64_t *d_lengths, const float *d_weight, const float *d_bias,
+                          void *d_y, float *d_mean, float *d_rstd, int64_t N, int64_t S, int C, int G, double eps,
+                          int dtype, void *d_ws, size_t ws_bytes, void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!ln_sizes_ok(N, S, C, dtype) || G <= 0 || C % G || S * (int64_t)G > INT32_MAX || G > 8192)
+        PCX_FAIL(PCX_E_ARG, "pcx_ragged_group_norm: bad sizes or dtype (C must be a multiple of G <= 8192)");
+    if (!d_lengths || !d_mean || !d_rstd || !d_ws || (N > 0 && (!d_x || !d_y)) || ((d_weight == nullptr) != (d_bias == nullptr)))
+        PCX_FAIL(PCX_E_ARG, "pcx_ragged_group_norm: null pointer (weight and bias come together)");
+    if ((uintptr_t)d_ws % 256) PCX_FAIL(PCX_E_ALIGN, "pcx_ragged_group_norm: workspace must be 256-byte aligned");
+    const int64_t SG = S * G;
+    LnWs w;
+    size_t need = carve_ln(d_ws, SG, &w);
+    if (ws_bytes < need) PCX_FAIL(PCX_E_CAPACITY, "pcx_ragged_group_norm: workspace %zu < %zu bytes", ws_bytes, need);
+    if (int rc = ln_offsets(d_lengths, S, N, w, stream)) return rc;
+    PCX_CUDA(cudaMemsetAsync(w.sums, 0, (size_t)2 * SG * sizeof(float), stream));
+    const unsigned grid = (unsigned)((N + LN_ROWS - 1) / LN_ROWS), sgrid = (unsigned)((SG + 127) / 128);
+    const bool vec = vec_ok(C, dtype, {d_x, d_y});
+    const size_t smem = (size_t)G * sizeof(float);
+    const int W = C / G;
+    for (int second = 0; second < 2; ++second) {
+        if (N > 0) {
+            PCX_LN_DISPATCH(dtype, vec, (gn_sum_kernel<T, VN><<<grid, LN_THREADS, smem, stream>>>(
+                                       (const T *)d_x, w.offsets, second ? d_mean : nullptr, w.sums + second * SG, N, S, C, G)));
+            PCX_LAUNCH_CHECK();
+        }
+        gn_stats_kernel<<<sgrid, 128, 0, stream>>>(w.sums + second * SG, w.offsets, d_mean, d_rstd, S, G, W, (float)eps, second);
+        PCX_LAUNCH_CHECK();
+    }
+    if (N > 0) {
+        prof_begin("gn_apply_kernel", stream);
+        PCX_LN_DISPATCH(dtype, vec, (gn_apply_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>(
+                                   (const T *)d_x, w.offsets, d_mean, d_rstd, d_weight, d_bias, (T *)d_y, N, S, C, G)));
+        prof_end(stream);
+        PCX_LAUNCH_CHECK();
+    }
+    return PCX_OK;
+}
+
+int pcx_ragged_group_norm_backward(const void *d_grad_y, const void *d_x, const int64_t *d_lengths,
+                                   const float *d_weight, const float *d_mean, const float *d_rstd, void *d_grad_x,
+                                   float *d_grad_weight, float *d_grad_bias, int64_t N, int64_t S, int C, int G,
+                                   int dtype, void *d_ws, size_t ws_bytes, void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!ln_sizes_ok(N, S, C, dtype) || G <= 0 || C % G || S * (int64_t)G > INT32_MAX || G > 4096)
+        PCX_FAIL(PCX_E_ARG, "pcx_ragged_group_norm_backward: bad sizes or dtype (C must be a multiple of G <= 4096)");
+    if (!d_lengths || !d_mean || !d_rstd || !d_ws || (N > 0 && (!d_grad_y || !d_x || !d_grad_x)) ||
+        ((d_grad_weight == nullptr) != (d_grad_bias == nullptr)))
+        PCX_FAIL(PCX_E_ARG, "pcx_ragged_group_norm_backward: null pointer");
+    if ((uintptr_t)d_ws % 256) PCX_FAIL(PCX_E_ALIGN, "pcx_ragged_group_norm_backward: workspace must be 256-byte aligned");
+    const int64_t SG = S * G;
+    LnWs w;
+    size_t need = carve_ln(d_ws, SG, &w);
+    if (ws_bytes < need) PCX_FAIL(PCX_E_CAPACITY, "pcx_ragged_group_norm_backward: workspace %zu < %zu bytes", ws_bytes, need);
+    if (int rc = ln_offsets(d_lengths, S, N, w, stream)) return rc;
+    PCX_CUDA(cudaMemsetAsync(w.sums, 0, (size_t)2 * SG * sizeof(float), stream));
+    if (d_grad_weight) {
+        PCX_CUDA(cudaMemsetAsync(d_grad_weight, 0, (size_t)C * sizeof(float), stream));
+        PCX_CUDA(cudaMemsetAsync(d_grad_bias, 0, (size_t)C * sizeof(float), stream));
+    }
+    if (N == 0) return PCX_OK;
+    const unsigned grid = (unsigned)((N + LN_ROWS - 1) / LN_ROWS);
+    const bool vec = vec_ok(C, dtype, {d_grad_y, d_x, d_grad_x});
+    PCX_LN_DISPATCH(dtype, vec, (gn_bwd_sums_kernel<T, VN><<<grid, LN_THREADS, (size_t)2 * G * sizeof(float), stream>>>(
+                               (const T *)d_grad_y, (const T *)d_x, w.offsets, d_mean, d_rstd, d_weight, w.sums, w.sums + SG,
+                               d_grad_weight, d_grad_bias, N, S, C, G)));
+    PCX_LAUNCH_CHECK();
+    PCX_LN_DISPATCH(dtype, vec, (gn_bwd_apply_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>(
+                               (const T *)d_grad_y, (const T *)d_x, w.offsets, d_mean, d_rstd, d_weight, w.sums, w.sums + SG,
+                               (T *)d_grad_x, N, S, C, G)));
     PCX_LAUNCH_CHECK();
     return PCX_OK;
 }

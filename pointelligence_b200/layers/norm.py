@@ -3,12 +3,14 @@ back to back).
 
 Stand in for the reference's ``layers/norm.py:12-172``: ``RaggedNorm`` and its four wrappers
 with the same constructor arguments and the same arithmetic (fp32, mean first, then the variance
-of the centred values, cast back to the input type).  Layer norm on CUDA runs as the library's
-fused kernels; the other per-sample norms share one code path that treats layer / group /
-instance as the same computation over (groups, width) views, with the per-sample sums done by
-the library's segment reduction (the reference defaults to ``torch.segment_reduce`` and lets a
-caller plug ``large_segment_reduce`` in as ``reduce_fn``, :22-57; ``reduce_fn`` still overrides
-the library kernel here, and is called with ``reduce="sum"``).
+of the centred values, cast back to the input type).  On CUDA the three per-sample norms run as
+the library's fused kernels (layer norm with its residual / ReLU tail, group and instance norm as
+one kernel family over (sample, channel group) statistics).  With a ``reduce_fn`` plugged in, or on
+the CPU, they share one code path that treats layer / group / instance as the same computation
+over (groups, width) views, with the per-sample sums done by the library's segment reduction
+(the reference defaults to ``torch.segment_reduce`` and lets a caller plug ``large_segment_reduce``
+in as ``reduce_fn``, :22-57; ``reduce_fn`` still overrides the library kernel here, and is called
+with ``reduce="sum"``).
 """
 from __future__ import annotations
 
@@ -19,7 +21,7 @@ from .. import _cabi
 from ..sparse_engines.segment_reduce import large_segment_reduce
 
 __all__ = ["RaggedNorm", "RaggedBatchNorm", "RaggedInstanceNorm", "RaggedLayerNorm", "RaggedGroupNorm",
-           "fused_layer_norm"]
+           "fused_layer_norm", "fused_group_norm"]
 
 
 class _FusedLayerNorm(torch.autograd.Function):
@@ -47,6 +49,34 @@ class _FusedLayerNorm(torch.autograd.Function):
         if gres is not None:
             gres = gres.to(ctx.residual_dtype)
         return gx, None, gw, gb, gres, None, None
+
+
+class _FusedGroupNorm(torch.autograd.Function):
+    """Group / instance norm over the library's kernels (``pcx_ragged_group_norm`` and its backward)."""
+
+    @staticmethod
+    def forward(ctx, x, lengths, weight, bias, groups, eps):
+        y, mean, rstd = _cabi.ragged_group_norm(x, lengths, weight, bias, groups, eps)
+        ctx.save_for_backward(x, lengths, weight, mean, rstd)
+        ctx.groups = int(groups)
+        ctx.param_dtypes = (None if weight is None else weight.dtype, None if bias is None else bias.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, lengths, weight, mean, rstd = ctx.saved_tensors
+        want_affine = weight is not None and (ctx.needs_input_grad[2] or ctx.needs_input_grad[3])
+        gx, gw, gb = _cabi.ragged_group_norm_backward(grad_y, x, lengths, weight, mean, rstd, ctx.groups, want_affine)
+        if gw is not None:
+            gw, gb = gw.to(ctx.param_dtypes[0]), gb.to(ctx.param_dtypes[1])
+        return gx, None, gw, gb, None, None
+
+
+def fused_group_norm(x, lengths, groups, weight=None, bias=None, eps=1e-5):
+    """``RaggedGroupNorm`` (``groups == x.shape[1]``: ``RaggedInstanceNorm``) as two statistics passes and
+    one normalising pass of the library (layers/norm.py:86-116 of the reference composes it from a dozen
+    torch launches); CUDA tensors only."""
+    return _FusedGroupNorm.apply(x, lengths, weight, bias, groups, eps)
 
 
 def fused_layer_norm(x, lengths, weight=None, bias=None, eps=1e-5, residual=None, relu=False):
@@ -97,8 +127,11 @@ class RaggedNorm(nn.Module):
         groups = self._groups()
         if lengths is None:
             raise ValueError(f"lengths argument is required for {self.norm_type} norm")
-        if self.norm_type == "layer" and self.reduce_fn is None and x.is_cuda:
-            return fused_layer_norm(x, lengths, self.weight, self.bias, self.eps)
+        if self.reduce_fn is None and x.is_cuda:
+            if self.norm_type == "layer":
+                return fused_layer_norm(x, lengths, self.weight, self.bias, self.eps)
+            if groups <= 4096 and self.num_features % groups == 0:
+                return fused_group_norm(x, lengths, groups, self.weight, self.bias, self.eps)
         # fp32, two passes (mean, then variance of the centred values) as layers/norm.py:86-130 of
         # the reference; one code path for the three norms: rows are viewed as (groups, width),
         # every pass is a per-row sum over the width followed by one segment sum over the sample

@@ -229,3 +229,62 @@ def test_fused_layer_norm_residual_relu_matches_composition(dtype):
     for name, a, b in zip(("y", "dx", "dresidual", "dweight", "dbias"), *results):
         scale = max(1.0, np.abs(b).max())
         assert np.abs(a - b).max() <= tol * scale, (name, np.abs(a - b).max(), scale)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind,C,G", [("group", 64, 8), ("group", 48, 16), ("group", 50, 5), ("instance", 48, 48),
+                                      ("instance", 7, 7)])
+def test_fused_group_and_instance_norm_match_composition(dtype, kind, C, G):
+    """``pcx_ragged_group_norm`` (forward and backward) against the same layer composed from torch
+    operators: samples spanning many row blocks, a one-row sample, boundaries inside a block, vector
+    and scalar channel layouts, groups narrower and wider than one 16-byte access, with and without
+    the affine parameters."""
+    from pointelligence_b200 import _cabi
+    from pointelligence_b200.layers import RaggedGroupNorm, RaggedInstanceNorm
+
+    def torch_reduce(v, reduce, lengths):
+        return torch.segment_reduce(v, reduce=reduce, lengths=lengths, axis=0)
+
+    rng = np.random.default_rng(C * 131 + G)
+    lengths = _t(np.array([3000, 1, 5000, 300, 0, 17]))
+    n = int(lengths.sum())
+    x0 = _t(rng.standard_normal((n, C)) * 2 + 0.5, dtype)
+    go = _t(rng.standard_normal((n, C)), dtype)
+    for affine in (True, False):
+        make = (lambda **kw: RaggedGroupNorm(G, C, affine=affine, **kw)) if kind == "group" else \
+               (lambda **kw: RaggedInstanceNorm(C, affine=affine, **kw))
+        fused, composed = make().to("cuda:0"), make(reduce_fn=torch_reduce).to("cuda:0")
+        if affine:
+            w, b = rng.standard_normal(C).astype(np.float32), rng.standard_normal(C).astype(np.float32)
+            for layer in (fused, composed):
+                layer.weight.data, layer.bias.data = _t(w), _t(b)
+        results = []
+        for layer in (fused, composed):
+            x = x0.clone().requires_grad_(True)
+            _cabi.profile_enable(True)
+            y = layer(x, lengths)
+            names = [name for name, _ in _cabi.profile_records()]
+            _cabi.profile_enable(False)
+            assert ("gn_apply_kernel" in names) == (layer is fused), names
+            assert y.dtype == dtype
+            y.backward(go)
+            got = [y, x.grad] + ([layer.weight.grad, layer.bias.grad] if affine else [])
+            results.append([t.detach().float().cpu().numpy() for t in got])
+        tol = 3e-5 if dtype == torch.float32 else 2e-2
+        for name, a, b in zip(("y", "dx", "dweight", "dbias"), *results):
+            scale = max(1.0, np.abs(b).max())
+            assert np.abs(a - b).max() <= tol * scale, (kind, affine, name, np.abs(a - b).max(), scale)
+
+
+def test_group_norm_rejects_bad_arguments():
+    from pointelligence_b200 import _cabi
+
+    x = torch.zeros((10, 24), device="cuda:0")
+    lengths = torch.tensor([10], device="cuda:0")
+    with pytest.raises(ValueError):
+        _cabi.ragged_group_norm(x, lengths, None, None, 5, 1e-5)          # 24 channels, 5 groups
+    with pytest.raises(ValueError):
+        _cabi.ragged_group_norm(x, lengths, torch.ones(24, device="cuda:0"), None, 4, 1e-5)   # weight without bias
+    y, mean, rstd = _cabi.ragged_group_norm(torch.zeros((0, 24), device="cuda:0"),
+                                            torch.zeros(2, dtype=torch.int64, device="cuda:0"), None, None, 4, 1e-5)
+    assert y.shape == (0, 24) and mean.shape == (8,)
