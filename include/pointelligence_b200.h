@@ -284,7 +284,7 @@ int pcx_indexed_segment_reduce_backward(const void *d_grad_y, const void *d_x,
  * backward.  _backward: d_y is read only when relu != 0; d_grad_weight /
  * d_grad_bias (fp32, C) and d_grad_residual may be null.
  */
-size_t pcx_ragged_layer_norm_workspace_bytes(int64_t S);
+size_t pcx_ragged_layer_norm_workspace_bytes(int64_t N, int64_t S);
 int pcx_ragged_layer_norm(const void *d_x, const int64_t *d_lengths,
                           const float *d_weight, const float *d_bias,
                           const void *d_residual, void *d_y, float *d_mean,

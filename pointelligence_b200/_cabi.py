@@ -69,7 +69,7 @@ SIGNATURES = {
                                                                                          c_void_p]),
     "pcx_indexed_segment_reduce_backward": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int] * 3
                                             + [c_void_p, c_size_t, c_void_p]),
-    "pcx_ragged_layer_norm_workspace_bytes": (c_size_t, [c_int64]),
+    "pcx_ragged_layer_norm_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "pcx_ragged_layer_norm": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_double, c_int, c_int, c_void_p,
                                                       c_size_t, c_void_p]),
     "pcx_ragged_layer_norm_backward": (c_int, [c_void_p] * 11 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
@@ -545,7 +545,7 @@ def ragged_layer_norm(x, lengths, weight, bias, residual, eps, relu):
     rstd = torch.empty(S, dtype=torch.float32, device=x.device)
     L = lib()
     with torch.cuda.device(x.device):
-        ws = workspace(L.pcx_ragged_layer_norm_workspace_bytes(S), x.device)
+        ws = workspace(L.pcx_ragged_layer_norm_workspace_bytes(N, S), x.device)
         check(L.pcx_ragged_layer_norm(ptr(x), ptr(lengths), ptr(weight), ptr(bias), ptr(residual), ptr(y), ptr(mean),
                                       ptr(rstd), N, S, C, float(eps), int(bool(relu)), dtype_code(x.dtype), ptr(ws),
                                       ws.numel(), stream_ptr()))
@@ -566,7 +566,7 @@ def ragged_layer_norm_backward(grad_y, x, y, lengths, weight, mean, rstd, relu, 
     gres = torch.empty_like(x) if want_residual else None
     L = lib()
     with torch.cuda.device(x.device):
-        ws = workspace(L.pcx_ragged_layer_norm_workspace_bytes(S), x.device)
+        ws = workspace(L.pcx_ragged_layer_norm_workspace_bytes(N, S), x.device)
         check(L.pcx_ragged_layer_norm_backward(ptr(grad_y), ptr(x), ptr(y), ptr(lengths), ptr(weight), ptr(mean),
                                                ptr(rstd), ptr(grad_x), ptr(gw), ptr(gb), ptr(gres), N, S, C,
                                                int(bool(relu)), dtype_code(x.dtype), ptr(ws), ws.numel(),

@@ -7,8 +7,10 @@
 // sample s, computed in two passes exactly as the reference composes them
 // (layers/norm.py:118-130: mean first, then the variance of the centred values,
 // rstd = 1 / sqrt(var + eps)); the reference spends about a dozen elementwise
-// and reduction launches on it, this file three passes over x forward and two
-// backward.  HBM-bound: bytes are what counts, the arithmetic is fp32.
+// and reduction launches on it, this file two reads of x from HBM forward (the
+// statistics pass centres on block means while a block's rows are still cached
+// and merges the blocks exactly) and two passes backward.  HBM-bound: bytes are
+// what counts, the arithmetic is fp32.
 //
 // Backward, with g' = g masked by the ReLU, gh = g' * weight, xh = (x - mean) * rstd,
 // n = rows_s * C:
@@ -42,6 +44,24 @@ __global__ void ln_tail_kernel(int64_t *offsets, int64_t S, int64_t total) {
     if (threadIdx.x == 0 && blockIdx.x == 0) offsets[S] = total;
 }
 
+// Row offsets of a batch of a few samples in one small launch: one warp scans 32 lengths at a time.
+__global__ void ln_small_offsets_kernel(const int64_t *__restrict__ lengths, int64_t *offsets, int64_t S, int64_t total) {
+    const int lane = threadIdx.x;
+    int64_t carry = 0;
+    for (int64_t base = 0; base < S; base += 32) {
+        const int64_t v = base + lane < S ? lengths[base + lane] : 0;
+        int64_t incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int64_t up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (base + lane < S) offsets[base + lane] = carry + incl - v;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) offsets[S] = total;
+}
+
 // The kernels below share one shape: a block owns LN_ROWS consecutive rows, a thread
 // keeps one vector column (VN channels, one 16-byte access when VN > 1) and walks the
 // rows of its row lane.  `uniform` blocks lie inside one sample (all but S - 1 of them).
@@ -56,54 +76,77 @@ struct BlockRows {
     }
 };
 
-// sums[s] += sum of x (mean == null) or of (x - mean_s)^2 over the block's rows: one
-// atomic per uniform block, per-thread atomics in the blocks that straddle a boundary.
+// Statistics of the layer norm with ONE read of x from HBM.  A block first sums its rows (block
+// mean), then sums the squares centred on that mean while its rows are still in the caches, and
+// leaves (count, mean, M2) per (block, sample) piece; ln_combine_kernel merges the pieces of a
+// sample exactly (M2 = sum M2_p + n_p (mean_p - mean)^2), which keeps the accuracy of the
+// two-pass formula.  The piece of sample s in block b is record b + s (pieces are ordered, and
+// going to the next piece advances b or s by one), so a sample's pieces are consecutive records.
+struct Moments { float n, mean, m2, pad; };
+
 template <typename T, int VN>
-__global__ void ln_sum_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets,
-                              const float *__restrict__ mean, float *sums, int64_t N, int64_t S, int C) {
+__global__ void ln_moments_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets, Moments *rec,
+                                  int64_t N, int64_t S, int C) {
     __shared__ float scratch[LN_THREADS / 32];
     const BlockRows B(offsets, N, S);
     const RowLayout L(C, VN);
-    float acc = 0.f;
-    int64_t cur = B.s_first;
-    for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
-        const int vcol = cp * L.vcb + L.vc;
-        if (vcol >= L.vc_total || L.lane >= L.lanes) continue;
-#pragma unroll 4
-        for (int64_t r = B.row0 + L.lane; r < B.row1; r += L.lanes) {
-            const int64_t s = B.uniform ? B.s_first : segment_of_row(offsets, S, r);
-            if (s != cur) {
-                atomicAdd(sums + cur, acc);
-                acc = 0.f;
-                cur = s;
-            }
-            const float mu = mean ? mean[s] : 0.f;
-            float v[VN];
-            load_vec<T, VN>(x + r * C + (int64_t)vcol * VN, v);
+    const int64_t s_last = B.uniform ? B.s_first : segment_of_row(offsets, S, B.row1 - 1);
+    for (int64_t s = B.s_first; s <= s_last; ++s) {
+        const int64_t lo = max(B.row0, offsets[s]), hi = min(B.row1, offsets[s + 1]);
+        if (hi <= lo) continue;   // an empty sample inside the block (same decision in every thread)
+        float mu = 0.f;
+        float result[2];
 #pragma unroll
-            for (int i = 0; i < VN; ++i) {
-                const float d = v[i] - mu;
-                acc += mean ? d * d : d;
+        for (int pass = 0; pass < 2; ++pass) {
+            float acc = 0.f;
+            for (int cp = 0; cp * L.vcb < L.vc_total; ++cp) {
+                const int vcol = cp * L.vcb + L.vc;
+                if (vcol >= L.vc_total || L.lane >= L.lanes) continue;
+#pragma unroll 4
+                for (int64_t r = lo + L.lane; r < hi; r += L.lanes) {
+                    float v[VN];
+                    load_vec<T, VN>(x + r * C + (int64_t)vcol * VN, v);
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) {
+                        const float d = v[i] - mu;
+                        acc += pass ? d * d : d;
+                    }
+                }
             }
+            result[pass] = block_sum(acc, scratch);
+            if (pass == 0) mu = result[0] / ((float)(hi - lo) * (float)C);
         }
-    }
-    if (B.uniform) {
-        acc = block_sum(acc, scratch);
-        if (threadIdx.x == 0) atomicAdd(sums + B.s_first, acc);
-    } else {
-        atomicAdd(sums + cur, acc);
+        if (threadIdx.x == 0) rec[blockIdx.x + s] = Moments{(float)(hi - lo) * (float)C, mu, result[1], 0.f};
     }
 }
 
-// pass 1 -> mean; pass 2 -> rstd
-__global__ void ln_stats_kernel(const float *__restrict__ sums, const int64_t *__restrict__ offsets, float *mean,
-                                float *rstd, int64_t S, int C, float eps, int second) {
-    int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= S) return;
-    const int64_t len = offsets[s + 1] - offsets[s];
-    const float n = (float)(len > 0 ? len : 1) * (float)C;
-    if (!second) mean[s] = sums[s] / n;
-    else rstd[s] = 1.f / sqrtf(sums[s] / n + eps);
+__global__ void ln_combine_kernel(const Moments *__restrict__ rec, const int64_t *__restrict__ offsets, float *mean,
+                                  float *rstd, int64_t S, float eps) {
+    const int64_t s = blockIdx.x;
+    const int lane = threadIdx.x;   // one warp per sample
+    const int64_t lo = offsets[s], hi = offsets[s + 1];
+    if (hi <= lo) {
+        if (lane == 0) mean[s] = 0.f, rstd[s] = 1.f / sqrtf(eps);
+        return;
+    }
+    const int64_t b0 = lo / LN_ROWS, b1 = (hi - 1) / LN_ROWS;
+    double n = 0.0, sum = 0.0;
+    for (int64_t b = b0 + lane; b <= b1; b += 32) {
+        const Moments m = rec[b + s];
+        n += m.n, sum += (double)m.n * m.mean;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o), sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const double mu = sum / n;
+    double m2 = 0.0;
+    for (int64_t b = b0 + lane; b <= b1; b += 32) {
+        const Moments m = rec[b + s];
+        const double d = (double)m.mean - mu;
+        m2 += (double)m.m2 + (double)m.n * d * d;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m2 += __shfl_xor_sync(0xffffffffu, m2, o);
+    if (lane == 0) mean[s] = (float)mu, rstd[s] = 1.f / sqrtf((float)(m2 / n) + eps);
 }
 
 template <typename T, int VN>
@@ -513,15 +556,17 @@ __global__ void gn_bwd_apply_kernel(const T *__restrict__ g_out, const T *__rest
 
 struct LnWs {
     int64_t *offsets;
+    Moments *rec;  // per (block, sample) piece of the forward statistics (layer norm only)
     float *sums;   // 2 * S
     void *cub_tmp;
     size_t cub_bytes;
 };
 
-size_t carve_ln(void *ws, int64_t S, LnWs *out) {
+size_t carve_ln(void *ws, int64_t S, LnWs *out, int64_t pieces = 0) {
     Carver c(ws);
     LnWs w;
     w.offsets = c.take<int64_t>((size_t)S + 1);
+    w.rec = c.take<Moments>((size_t)pieces);
     w.sums = c.take<float>((size_t)2 * S + 1);
     size_t bytes = 0;
     cub::DeviceScan::ExclusiveSum(nullptr, bytes, (const int64_t *)nullptr, (int64_t *)nullptr, (int)std::max<int64_t>(S, 1));
@@ -532,12 +577,20 @@ size_t carve_ln(void *ws, int64_t S, LnWs *out) {
 }
 
 int ln_offsets(const int64_t *d_lengths, int64_t S, int64_t N, const LnWs &w, cudaStream_t stream) {
+    if (S <= 4096) {
+        ln_small_offsets_kernel<<<1, 32, 0, stream>>>(d_lengths, w.offsets, S, N);
+        PCX_LAUNCH_CHECK();
+        return PCX_OK;
+    }
     size_t bytes = w.cub_bytes;
     PCX_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, bytes, d_lengths, w.offsets, (int)S, stream));
     ln_tail_kernel<<<1, 32, 0, stream>>>(w.offsets, S, N);
     PCX_LAUNCH_CHECK();
     return PCX_OK;
 }
+
+// (block, sample) pieces of N rows in S samples: record b + s, b < blocks, s < S
+int64_t ln_pieces(int64_t N, int64_t S) { return (N + LN_ROWS - 1) / LN_ROWS + S; }
 
 bool ln_sizes_ok(int64_t N, int64_t S, int C, int dtype) {
     return N >= 0 && S > 0 && S <= INT32_MAX && C > 0 && (dtype == PCX_F32 || dtype == PCX_F16 || dtype == PCX_BF16);
@@ -558,7 +611,9 @@ using namespace pcx;
 
 extern "C" {
 
-size_t pcx_ragged_layer_norm_workspace_bytes(int64_t S) { return S <= 0 ? 0 : carve_ln(nullptr, S, nullptr); }
+size_t pcx_ragged_layer_norm_workspace_bytes(int64_t N, int64_t S) {
+    return (S <= 0 || N < 0) ? 0 : carve_ln(nullptr, S, nullptr, ln_pieces(N, S));
+}
 
 int pcx_ragged_layer_norm(const void *d_x, const int64_t *d_lengths, const float *d_weight, const float *d_bias,
                           const void *d_residual, void *d_y, float *d_mean, float *d_rstd, int64_t N, int64_t S, int C,
@@ -569,23 +624,16 @@ int pcx_ragged_layer_norm(const void *d_x, const int64_t *d_lengths, const float
         PCX_FAIL(PCX_E_ARG, "pcx_ragged_layer_norm: null pointer (weight and bias come together)");
     if ((uintptr_t)d_ws % 256) PCX_FAIL(PCX_E_ALIGN, "pcx_ragged_layer_norm: workspace must be 256-byte aligned");
     LnWs w;
-    size_t need = carve_ln(d_ws, S, &w);
+    size_t need = carve_ln(d_ws, S, &w, ln_pieces(N, S));
     if (ws_bytes < need) PCX_FAIL(PCX_E_CAPACITY, "pcx_ragged_layer_norm: workspace %zu < %zu bytes", ws_bytes, need);
     if (int rc = ln_offsets(d_lengths, S, N, w, stream)) return rc;
-    PCX_CUDA(cudaMemsetAsync(w.sums, 0, (size_t)2 * S * sizeof(float), stream));
-    const unsigned grid = (unsigned)((N + LN_ROWS - 1) / LN_ROWS), sgrid = (unsigned)((S + 127) / 128);
+    const unsigned grid = (unsigned)((N + LN_ROWS - 1) / LN_ROWS);
     const bool vec = vec_ok(C, dtype, {d_x, d_y, d_residual});
     if (N > 0) {
-        PCX_LN_DISPATCH(dtype, vec, (ln_sum_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, nullptr, w.sums, N, S, C)));
+        PCX_LN_DISPATCH(dtype, vec, (ln_moments_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, w.rec, N, S, C)));
         PCX_LAUNCH_CHECK();
     }
-    ln_stats_kernel<<<sgrid, 128, 0, stream>>>(w.sums, w.offsets, d_mean, d_rstd, S, C, (float)eps, 0);
-    PCX_LAUNCH_CHECK();
-    if (N > 0) {
-        PCX_LN_DISPATCH(dtype, vec, (ln_sum_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, d_mean, w.sums + S, N, S, C)));
-        PCX_LAUNCH_CHECK();
-    }
-    ln_stats_kernel<<<sgrid, 128, 0, stream>>>(w.sums + S, w.offsets, d_mean, d_rstd, S, C, (float)eps, 1);
+    ln_combine_kernel<<<(unsigned)S, 32, 0, stream>>>(w.rec, w.offsets, d_mean, d_rstd, S, (float)eps);
     PCX_LAUNCH_CHECK();
     if (N > 0) {
         prof_begin("ln_apply_kernel", stream);

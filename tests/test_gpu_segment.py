@@ -288,3 +288,28 @@ def test_group_norm_rejects_bad_arguments():
     y, mean, rstd = _cabi.ragged_group_norm(torch.zeros((0, 24), device="cuda:0"),
                                             torch.zeros(2, dtype=torch.int64, device="cuda:0"), None, None, 4, 1e-5)
     assert y.shape == (0, 24) and mean.shape == (8,)
+
+
+@pytest.mark.parametrize("samples", [100, 5000])
+def test_norms_with_many_short_samples(samples):
+    """Hundreds and thousands of samples of 0 to 6 rows: many sample boundaries inside every row
+    block, both row-offset paths (one small launch up to 4096 samples, the library scan above)."""
+    from pointelligence_b200.layers import RaggedGroupNorm, RaggedLayerNorm
+
+    def torch_reduce(v, reduce, lengths):
+        return torch.segment_reduce(v, reduce=reduce, lengths=lengths, axis=0)
+
+    rng = np.random.default_rng(samples)
+    lens = rng.integers(1, 7, samples)          # torch.segment_reduce gives NaN means for empty samples
+    lengths = _t(lens)
+    x0 = _t(rng.standard_normal((int(lens.sum()), 32)).astype(np.float32))
+    for make in (lambda **kw: RaggedLayerNorm(32, **kw), lambda **kw: RaggedGroupNorm(4, 32, **kw)):
+        out = []
+        for reduce_fn in (None, torch_reduce):
+            layer = make(reduce_fn=reduce_fn).to("cuda:0")
+            x = x0.clone().requires_grad_(True)
+            y = layer(x, lengths)
+            y.square().sum().backward()
+            out.append((y.detach().cpu().numpy(), x.grad.cpu().numpy()))
+        for a, b in zip(*out):
+            assert np.abs(a - b).max() <= 2e-4 * max(1.0, np.abs(b).max())
