@@ -290,3 +290,35 @@ def grid_sample_center_nearest(points, grid_size, sample_inds=None,
     indices = order[first].astype(np.int64)
     si = None if sample_inds is None else np.asarray(sample_inds)[indices]
     return pts[indices], si, indices, (inverse.astype(np.int64) if return_mapping else None)
+
+
+# --------------------------------------------------------------------------
+# grid partition (patchify) rulebook
+# --------------------------------------------------------------------------
+def partition_triplets(points, grid_size, stride, kernel_size, sample_inds=None):
+    """Rulebook of the disjoint strided convolution: one triplet per input point.
+
+    layers/triplets.py:1042-1167 (``handle_stride_disjoint_and_build_triplets``): the token of a
+    point is its cell of side ``stride * grid_size`` (cells in the order of
+    ``grid_sample_center_nearest``, token coordinate = cell centre ``(g + 0.5) * cell``), the tap is
+    ``floor(frac * K)`` per axis with ``frac = p / cell - floor_div(p, cell)`` in fp32, clamped to
+    ``[0, K)``, x most significant; triplets grouped by tap (stable, point order inside a tap).
+    Returns ``(i int64, j int64, k int64, centres fp32 (S, 3), slack)`` where ``slack`` is, per
+    point, the distance of ``frac * K`` (evaluated in float64) from the nearest integer: a device
+    that divides by multiplying with the reciprocal may move points with a slack of a few ulp into
+    the neighbouring slot.
+    """
+    pts = _as_f32(points)
+    K = int(kernel_size)
+    cell = F32(float(stride) * float(grid_size))
+    _, _, indices, token_of = grid_sample_center_nearest(pts, cell, sample_inds, return_mapping=True)
+    g = grid_cell_indices(pts, cell)
+    centres = ((g[indices].astype(F32) + F32(0.5)).astype(F32) * cell).astype(F32)
+    frac = ((pts / cell).astype(F32) - g.astype(F32)).astype(F32)
+    sub = np.clip(np.floor((frac * F32(K)).astype(F32)).astype(np.int64), 0, K - 1)
+    slot = (sub[:, 0] * K + sub[:, 1]) * K + sub[:, 2]
+    exact = pts.astype(np.float64) / float(cell)
+    scaled = (exact - np.floor(exact)) * K
+    slack = np.abs(scaled - np.round(scaled)).min(axis=1)
+    order = np.argsort(slot, kind="stable")
+    return token_of[order].astype(np.int64), order.astype(np.int64), slot[order], centres, slack[order]

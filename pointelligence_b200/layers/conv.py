@@ -23,7 +23,8 @@ from ..sparse_engines.ops import sparse_matrix_vector_multiplication_reduction
 from ..sparse_engines.tig import TigIndex, tig_mvmr
 from .contract import TripletContract
 from .metadata import MetaData
-from .triplets import build_full_cover_strided_rulebook, handle_stride_and_build_triplets
+from .triplets import (build_full_cover_strided_rulebook, handle_stride_and_build_triplets,
+                       handle_stride_disjoint_and_build_triplets)
 
 
 class GeneralConv(Module):
@@ -145,6 +146,17 @@ def conv_with_stride(conv_op: Callable, x: Tensor, m: MetaData, stride: float,
     from the parent cloud to the down-sampled cloud, convolve."""
     m = handle_stride_and_build_triplets(m, stride, conv_op.kernel_size_3, receptive_field_scaler,
                                          distance_type=distance_type)
+    x = conv_op(x, m.i, m.j, m.k, m.num_points(), contract=m.contract, seg_offs=m.seg_offs)
+    return x, m
+
+
+def conv_with_stride_disjoint(conv_op: Callable, x: Tensor, m: MetaData, stride: float) -> Tuple[Tensor, MetaData]:
+    """Strided convolution as a grid partition, the patchify operator (``layers/conv.py:636-700`` of
+    the reference): every input point contributes to exactly one token, the cell centre of side
+    ``stride * grid_size`` it lies in, through the weight of its sub-voxel slot (``K**3`` slots for
+    ``conv_op``'s cubic kernel).  ``Upsample(straight_recover=True, recompute_k=False)`` on the
+    returned geometry is the matching unpatchify."""
+    m = handle_stride_disjoint_and_build_triplets(m, stride, conv_op.kernel_size_3)
     x = conv_op(x, m.i, m.j, m.k, m.num_points(), contract=m.contract, seg_offs=m.seg_offs)
     return x, m
 

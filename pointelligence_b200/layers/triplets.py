@@ -218,6 +218,74 @@ def handle_stride_and_build_triplets(m: MetaData, stride, kernel_size=_triple(3)
     return m
 
 
+def _own_parent(m: MetaData) -> MetaData:
+    """The geometry of ``m`` before a strided layer changes it, linked as ``m.parent`` (reused when
+    the existing parent already is that cloud)."""
+    if _same_cloud(m.parent, m):
+        return m.parent
+    parent = MetaData(points=m.points, sample_inds=m.sample_inds, sample_sizes=m.sample_sizes,
+                      grid_size=m.grid_size, parent=m.parent)
+    m.parent = parent
+    return parent
+
+
+def partition_slots(points, cell_size, slots_per_axis):
+    """Sub-voxel slot of every point inside its cell of side ``cell_size``: the cell is the floor
+    division the grid sampler uses, the slot ``floor(frac * K)`` per axis (clamped to ``[0, K)`` against
+    rounding at the upper face), x most significant (``layers/triplets.py:1130-1134`` of the reference;
+    the same torch expressions, so that both run the same device arithmetic)."""
+    K = int(slots_per_axis)
+    cell = torch.div(points, cell_size, rounding_mode="floor")
+    sub = torch.floor((points / cell_size - cell) * K).to(torch.long).clamp_(0, K - 1)
+    return (sub[:, 0] * K + sub[:, 1]) * K + sub[:, 2]
+
+
+@torch.compiler.disable
+def handle_stride_disjoint_and_build_triplets(m: MetaData, stride, kernel_size=_triple(3), sort_by="k") -> MetaData:
+    """Strided convolution as a grid partition (``layers/triplets.py:1042-1167`` of the reference):
+    no search.  Every input point belongs to exactly one cell of side ``stride * grid_size``; the
+    output token is the cell centre, the tap is the point's sub-voxel slot in its cell (cubic
+    kernel, ``K**3`` slots), so the rulebook has one triplet per input point.  The mirrored edges
+    cached on the parent make ``Upsample(straight_recover=True, recompute_k=False)`` the exact inverse.
+
+    With ``sort_by="k"`` the triplets are grouped by slot with a stable sort (inside a slot in point
+    order; the reference's ``argsort`` leaves that order open)."""
+    if stride <= 1:
+        raise ValueError(f"handle_stride_disjoint_and_build_triplets requires stride > 1 (downsample case); "
+                         f"got stride={stride}.")
+    ks = _triple(kernel_size)
+    if not (ks[0] == ks[1] == ks[2]):
+        raise ValueError(f"partition disjoint conv requires a cubic kernel; got kernel_size={ks}")
+    K = int(ks[0])
+    with torch.no_grad():
+        parent = _own_parent(m)
+        pts, cell_size = parent.points, stride * parent.grid_size
+        centres, sample_c, kept, token_of = grid_sample_filter(points=pts, grid_size=cell_size,
+                                                               sample_inds=parent.sample_inds, reduction="center",
+                                                               return_mapping=True)
+        m.points, m.sample_inds, m.grid_size = centres.contiguous(), sample_c, cell_size
+        m.sample_sizes = torch.bincount(sample_c)
+        m.downsample_indices = kept
+        slot = partition_slots(pts, cell_size, K)
+        point = torch.arange(pts.shape[0], device=pts.device)
+        if sort_by == "k":
+            slot, order = torch.sort(slot, stable=True)
+            point = point[order]
+        m.i, m.j, m.k = token_of.to(torch.long)[point], point, slot
+        m.seg_offs = kernel_offset_segments(m.k, K ** 3)
+        m.num_neighbors = None
+        parent.i_upsample, parent.j_upsample = m.j, m.i
+        parent.k_upsample, parent.seg_offs_upsample = m.k, m.seg_offs
+    # one triplet per input point by construction: the fan-out-1 contract holds whenever the
+    # partition actually merges points (as many tokens as points would be the identity case,
+    # which the reference leaves to the submanifold contract)
+    n_in, n_out = pts.shape[0], m.points.shape[0]
+    covers = m.k.numel() == n_in and n_in != n_out and n_in > 0
+    m.contract = TripletContract(k_sorted=True, exact_cover_out=False, exact_cover_in=bool(covers),
+                                 uniform_seg_len=None)
+    return m
+
+
 # --------------------------------------------------------------------------
 # Full-cover strided rulebook (mirror of ``layers/triplets.py:36-465``)
 # --------------------------------------------------------------------------
