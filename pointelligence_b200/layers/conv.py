@@ -150,6 +150,33 @@ def conv_with_stride(conv_op: Callable, x: Tensor, m: MetaData, stride: float,
     return x, m
 
 
+class GenerativePointConv3d(GeneralConv):
+    """Convolution onto an invented, denser point set (``layers/conv.py:687-755`` of the reference):
+    ``forward(input, m)`` returns the features of the generated points and their ``MetaData``
+    (parent = ``m``).  The point set and its rulebook come from a ``CoordinateGenerator`` (default
+    ``KernelStampGenerator(kernel_size, expansion)``; its tap count sizes the weight); ``sites`` lets
+    sibling layers share one generated set."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size=3, expansion: float = 2.0, generator=None,
+                 groups: int = 1, bias: bool = True, device=None, dtype=None) -> None:
+        from .generative import KernelStampGenerator
+
+        self.kernel_size_3 = _triple(kernel_size)
+        self.expansion = expansion
+        if generator is None:
+            generator = KernelStampGenerator(self.kernel_size_3, expansion)
+        super().__init__(in_channels, out_channels, generator.kernel_taps, groups, bias, device=device, dtype=dtype)
+        self.generator = generator
+
+    def forward(self, input: Tensor, m: MetaData, sites=None) -> Tuple[Tensor, MetaData]:
+        if sites is None:
+            sites = self.generator(m)
+        sites.validate()
+        x = self._conv_forward(input, sites.i, sites.j, sites.k, sites.n_out, self.weight, self.bias,
+                               contract=sites.to_contract())
+        return x, sites.to_metadata(parent=m)
+
+
 def conv_with_stride_disjoint(conv_op: Callable, x: Tensor, m: MetaData, stride: float) -> Tuple[Tensor, MetaData]:
     """Strided convolution as a grid partition, the patchify operator (``layers/conv.py:636-700`` of
     the reference): every input point contributes to exactly one token, the cell centre of side
