@@ -690,7 +690,7 @@ def backbone_setup(args, rank, world, dev):
     import torch.nn.functional as F
 
     from pointelligence_b200.backbone import ResUNet
-    from pointelligence_b200.dist import allreduce_gradients
+    from pointelligence_b200.dist import OverlappedGradientReducer
     from pointelligence_b200.synthetic import indoor_scene, ragged_batch
 
     if args.scene == "lidar":
@@ -721,14 +721,19 @@ def backbone_setup(args, rank, world, dev):
     model = ResUNet(in_channels=3, num_classes=20).to(dev)
     params = [p for p in model.parameters()]
 
+    # gradients are summed bucket by bucket while the backward pass still runs
+    reducer = OverlappedGradientReducer(params) if world > 1 else None
+
     def step(reduce=True):
         for p in params:
             p.grad = None
+        if reducer is not None:
+            reducer.enabled = bool(reduce)
         logits = model(feat, pts, inds, lens, grid)
         loss = F.cross_entropy(logits.float(), labels)
         loss.backward()
-        if world > 1 and reduce:
-            allreduce_gradients(params)
+        if reducer is not None and reduce:
+            reducer.finish()
         return loss
 
     return step, params, n, scene_desc

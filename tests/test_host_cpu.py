@@ -154,6 +154,29 @@ assert torch.allclose(params[1].grad, torch.arange(8.0) * 1.5)
 assert torch.allclose(params[2].grad, torch.full((3, 3), 0.5))
 owned = partition_scenes([5, 9, 7, 3], 2)
 assert sorted(owned[0] + owned[1]) == [0, 1, 2, 3]
+# the reducer that overlaps with backward: a small network whose ranks see different data, one
+# parameter unused on rank 1, two steps through the same reducer, against a plain all-reduce
+from pointelligence_b200.dist import OverlappedGradientReducer
+torch.manual_seed(1)
+net = torch.nn.Sequential(torch.nn.Linear(6, 16), torch.nn.ReLU(), torch.nn.Linear(16, 16), torch.nn.ReLU(),
+                          torch.nn.Linear(16, 3))
+extra = torch.nn.Parameter(torch.ones(4))
+params = list(net.parameters()) + [extra]
+reducer = OverlappedGradientReducer(params, average=True, bucket_bytes=600)
+assert len(reducer.buckets) >= 3
+for step in range(2):
+    for p in params:
+        p.grad = None
+    x = torch.randn(5, 6, generator=torch.Generator().manual_seed(10 * step + rank))
+    loss = net(x).square().sum() + (extra.sum() * (rank == 0))
+    loss.backward()
+    local = [None if p.grad is None else p.grad.clone() for p in params]
+    reducer.finish()
+    for p, g in zip(params, local):
+        want = torch.zeros_like(p) if g is None else g
+        dist.all_reduce(want)
+        assert torch.allclose(p.grad, want / 2, atol=1e-6), (step, p.shape)
+reducer.remove()
 dist.barrier()
 dist.destroy_process_group()
 print("rank", rank, "ok")
