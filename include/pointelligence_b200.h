@@ -398,10 +398,11 @@ int pcx_radius_fill(const float *d_points, const float *d_queries, int64_t P,
  *       nothing and returns PCX_E_CAPACITY with *h_total set: call it again
  *       with buffers of that size (the state is kept in d_ws, which must stay
  *       untouched between the calls).
- *   h_total points at TWO int64: [0] the number of pairs, [1] the number of
+ *   h_total points at THREE int64: [0] the number of pairs, [1] the number of
  *   queries that have no neighbour (the reference asserts there is none,
  *   layers/triplets.py:431-520; the count saves the caller a pass and a
- *   hand-over of its own).
+ *   hand-over of its own), [2] the device status word of pcx_device_status as
+ *   it stood at this hand-over (not cleared).
  *   pcx_radius_taps_supported  1 when kernel_size is served by this path. */
 int pcx_radius_taps_supported(int kernel_size);
 size_t pcx_radius_taps_workspace_bytes(int64_t P, int64_t Q, int kernel_size);

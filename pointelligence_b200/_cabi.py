@@ -733,7 +733,7 @@ def _radius_taps(points, queries, radius, ps, qs, distance_type, kernel_size, ke
         check(L.pcx_radius_taps_count(ptr(points), ptr(queries), ptr(ps), ptr(qs), P, Q, float(radius),
                                       distance_type, kernel_size, float(kernel_grid_size), ptr(num_neighbors),
                                       ptr(seg), ptr(ws), ws.numel(), stream_ptr()))
-        total = (c_int64 * 2)()
+        total = (c_int64 * 3)()
         ratio_key = (kernel_size, distance_type, float(radius))
         ratio = _TAPS_RATIO.get(ratio_key)
         if ratio is None:
@@ -753,7 +753,8 @@ def _radius_taps(points, queries, radius, ps, qs, distance_type, kernel_size, ke
                 continue
             check(rc)
             break
-        raise_if_device_reported()   # the fill above ended with a host hand-over: the stream is idle
+        if total[2]:                 # the hand-over of the fill pass brought the status word along
+            raise_if_device_reported()
         n = int(total[0])
         if len(_TAPS_RATIO) > 256:
             _TAPS_RATIO.clear()

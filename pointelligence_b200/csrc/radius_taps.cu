@@ -32,6 +32,7 @@
 #include "geometry.cuh"
 
 namespace pcx {
+int device_status_address(unsigned int **d_status);   // status word of the bounded waits (sparse_tc.cu)
 using namespace geo;
 namespace {
 
@@ -455,9 +456,12 @@ int pcx_radius_taps_total(int64_t P, int64_t Q, int kernel_size, int64_t *h_tota
     TapsWs w;
     if (ws_bytes < carve_taps(d_ws, P, Q, kernel_size * kernel_size * kernel_size, &w)) PCX_FAIL(PCX_E_CAPACITY, "pcx_radius_taps_total: workspace too small");
     int64_t h[4] = {0, 0, 0, 0};
+    unsigned int status = 0, *d_status = nullptr;
+    if (int rc = device_status_address(&d_status)) return rc;
     PCX_CUDA(cudaMemcpyAsync(h, w.ctrl, sizeof(h), cudaMemcpyDeviceToHost, stream));
+    PCX_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(status), cudaMemcpyDeviceToHost, stream));
     PCX_CUDA(cudaStreamSynchronize(stream));
-    h_total[0] = h[0], h_total[1] = h[3];
+    h_total[0] = h[0], h_total[1] = h[3], h_total[2] = (int64_t)status;
     if (h[1] || h[0] > INT32_MAX) PCX_FAIL(PCX_E_UNSUPPORTED, "prepared kernel-segment output currently requires fewer than 2^31 edges; got %lld", (long long)h[0]);
     return PCX_OK;
 }
@@ -484,9 +488,12 @@ int pcx_radius_taps_fill(const float *d_queries, const int32_t *d_point_sample, 
         PCX_LAUNCH_CHECK();
     }
     int64_t h[4] = {0, 0, 0, 0};
+    unsigned int status = 0, *d_status = nullptr;
+    if (int rc = device_status_address(&d_status)) return rc;
     PCX_CUDA(cudaMemcpyAsync(h, w.ctrl, sizeof(h), cudaMemcpyDeviceToHost, stream));
+    PCX_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(status), cudaMemcpyDeviceToHost, stream));
     PCX_CUDA(cudaStreamSynchronize(stream));
-    h_total[0] = h[0], h_total[1] = h[3];
+    h_total[0] = h[0], h_total[1] = h[3], h_total[2] = (int64_t)status;
     if (h[1] || h[0] > INT32_MAX) PCX_FAIL(PCX_E_UNSUPPORTED, "prepared kernel-segment output currently requires fewer than 2^31 edges; got %lld", (long long)h[0]);
     if (h[0] > capacity) PCX_FAIL(PCX_E_CAPACITY, "pcx_radius_taps_fill: %lld pairs do not fit the capacity of %lld; nothing was written", (long long)h[0], (long long)capacity);
     return PCX_OK;

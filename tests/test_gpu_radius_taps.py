@@ -145,12 +145,12 @@ def test_c_abi_capacity_protocol_and_argument_errors():
     assert L.pcx_radius_taps_count(ptr(pts), ptr(pts), None, None, n, n, 0.05, 0, 7, 0.02, ptr(nn), ptr(seg),
                                    ptr(ws), ws.numel(), stream_ptr()) == -6                    # PCX_E_UNSUPPORTED
     _cabi.check(L.pcx_radius_taps_count(*args, ptr(ws), ws.numel(), stream_ptr()))
-    total = (c_int64 * 2)()
+    total = (c_int64 * 3)()
     _cabi.check(L.pcx_radius_taps_total(n, n, 3, total, ptr(ws), ws.numel(), stream_ptr()))
     t = int(total[0])
     assert t == int(nn.sum()) and int(seg[-1]) == t and int(total[1]) == 0
     small = torch.full((t - 1,), -7, dtype=torch.int32, device=dev)
-    got = (c_int64 * 2)()
+    got = (c_int64 * 3)()
     rc = L.pcx_radius_taps_fill(ptr(pts), None, None, n, n, 0.05, 0, 3, 0.02, t - 1, ptr(small), ptr(small), None,
                                 got, ptr(ws), ws.numel(), stream_ptr())
     assert rc == _cabi.PCX_E_CAPACITY and int(got[0]) == t
