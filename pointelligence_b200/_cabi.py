@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 from ctypes import c_double, c_int, c_int64, c_size_t, c_void_p
 
 import torch
@@ -161,6 +162,108 @@ def workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
 
+# ---------------------------------------------------- geometry beside the features ----
+_SIDE_STREAMS = {}
+_overlap = threading.local()
+
+
+def _side_stream(device):
+    """The high-priority stream geometry runs on inside a ``geometry_overlap`` scope, else None."""
+    active = getattr(_overlap, "devices", None)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if not active or index not in active:
+        return None
+    return _SIDE_STREAMS[index]
+
+
+class geometry_overlap:
+    """Scope in which the index-building calls of this module (radius search, grid sampling, plan
+    building) run on a stream of their own, so that their host hand-overs wait for the geometry
+    kernels only and the feature kernels already queued on the caller's stream keep the GPU busy
+    meanwhile.  Results are handed to the caller's stream with an event, never with a host wait.
+
+    Contract: inside the scope, every tensor handed to those calls was either complete before the
+    scope was entered or is itself the result of one of them (point clouds, sample ids, index
+    arrays) -- true for a network that derives its geometry from the input cloud alone.  The side
+    stream waits for the caller's stream once, on entry; the caller's stream waits for the side
+    stream on exit.  Not re-entrant across devices; nested use on one device is a no-op."""
+
+    def __init__(self, device=None):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.owner = False
+
+    def __enter__(self):
+        if self.device.type != "cuda" or os.environ.get("PCX_GEOMETRY_OVERLAP", "1") == "0":
+            return self
+        index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        active = getattr(_overlap, "devices", None)
+        if active is None:
+            active = _overlap.devices = set()
+        if index in active:
+            return self
+        if index not in _SIDE_STREAMS:
+            _SIDE_STREAMS[index] = torch.cuda.Stream(device=index, priority=-1)
+        _SIDE_STREAMS[index].wait_stream(torch.cuda.current_stream(index))
+        active.add(index)
+        self.owner, self.index = True, index
+        return self
+
+    def __exit__(self, *exc):
+        if self.owner:
+            _overlap.devices.discard(self.index)
+            torch.cuda.current_stream(self.index).wait_stream(_SIDE_STREAMS[self.index])
+            self.owner = False
+        return False
+
+
+def on_geometry_stream(fn):
+    """Decorator of an index-building function (no feature arithmetic inside): when its device is
+    inside a ``geometry_overlap`` scope the whole body runs on the side stream, and every tensor it
+    returns -- also inside tuples and geometry records such as ``MetaData`` and its parents -- is
+    made known to the caller's stream (event wait, allocator bookkeeping)."""
+    import functools
+
+    def device_of(values):
+        for v in values:
+            if isinstance(v, torch.Tensor):
+                if v.is_cuda:
+                    return v.device
+            elif hasattr(v, "points") and isinstance(getattr(v, "points"), torch.Tensor) and v.points.is_cuda:
+                return v.points.device
+        return None
+
+    def hand_over(value, main, depth=0):
+        if isinstance(value, torch.Tensor):
+            if value.is_cuda:
+                value.record_stream(main)
+        elif isinstance(value, (tuple, list)):
+            for v in value:
+                hand_over(v, main, depth)
+        elif isinstance(value, MvmrPlan):
+            value.buffer.record_stream(main)
+        elif hasattr(value, "__dataclass_fields__") and depth < 8:
+            for v in vars(value).values():
+                if isinstance(v, (torch.Tensor, tuple, list)) or hasattr(v, "__dataclass_fields__"):
+                    hand_over(v, main, depth + 1)
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        dev = device_of(list(args) + list(kwargs.values()))
+        side = _side_stream(dev) if dev is not None else None
+        if side is None:
+            return fn(*args, **kwargs)
+        main = torch.cuda.current_stream(dev)
+        if main == side:
+            return fn(*args, **kwargs)
+        with torch.cuda.stream(side):
+            out = fn(*args, **kwargs)
+        main.wait_stream(side)
+        hand_over(out, main)
+        return out
+
+    return wrapper
+
+
 def as_i32(t):
     if t is None:
         return None
@@ -287,6 +390,7 @@ def planned_supported(weight, feat, gather, scatter, seg_offs, n_out, transpose)
     return T < 2 ** 31 and nblocks * K * 128 <= 2 ** 32
 
 
+@on_geometry_stream
 def mvmr_plan(scatter, gather, seg_offs, K, n_out, group_blocks):
     """Build the plan of a tap-sorted rulebook: ``scatter`` indexes the rows that are summed
     into (n_out of them), ``gather`` the rows that are read."""
@@ -665,6 +769,7 @@ def rnet_select(points, centres, centre_of, neighbors, offsets, source, rounds_p
 
 
 # -------------------------------------------------------------- geometry ----
+@on_geometry_stream
 def radius_search(points, queries, radius, point_sample, query_sample, distance_type,
                   kernel_size=0, kernel_grid_size=0.0, return_distances=False, want_k=False):
     """Sorted-grid fixed-radius search.
@@ -763,6 +868,7 @@ def _radius_taps(points, queries, radius, ps, qs, distance_type, kernel_size, ke
     return out_i[:n], out_j[:n], (out_k[:n] if want_k else None), seg, num_neighbors
 
 
+@on_geometry_stream
 def grid_sample_center_nearest(points, cell, sample, return_mapping):
     """Returns ``(indices int64 (S,), points_f (S,3), sample_f int32 (S,)|None, mapping int64|None)``."""
     require_cuda(points, sample)

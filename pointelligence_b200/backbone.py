@@ -22,6 +22,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch import Tensor
 
+from . import _cabi
 from .internals.triplet_cache import triplet_cache_scope
 from .layers import MetaData, PointConv3d, RaggedLayerNorm, Upsample
 from .layers.norm import fused_layer_norm
@@ -159,7 +160,10 @@ class ResUNet(nn.Module):
                 grid_size: float) -> Tensor:
         # one rulebook per (cloud, radius, kernel size) and forward pass: the decoder levels
         # find the encoder levels' submanifold triplets in the cache
-        with triplet_cache_scope():
+        # and the geometry of a level is built on a stream of its own while the feature kernels of
+        # the level before it are still running (every point cloud of the network derives from
+        # the input cloud through the library's geometry calls alone)
+        with triplet_cache_scope(), _cabi.geometry_overlap(points.device):
             return self._forward(feat, points, sample_inds, sample_sizes, grid_size)
 
     def _forward(self, feat, points, sample_inds, sample_sizes, grid_size):

@@ -13,6 +13,7 @@ import torch
 from .. import _cabi
 
 
+@_cabi.on_geometry_stream
 def grid_sample_filter(points, grid_size, sample_inds=None, reduction="center_nearest",
                        return_mapping=False, center_nearest_impl="auto"):
     """Returns ``(points_f (S,3), sample_inds_f (S,) or None, indices (S,) int64, mapping or None)``.

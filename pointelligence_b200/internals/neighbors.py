@@ -66,6 +66,7 @@ def _f32(x):
 
 
 @torch.no_grad()
+@_cabi.on_geometry_stream
 def radius_search_sorted_grid8(points, queries, radius, sample_inds=None, query_sample_inds=None,
                                return_distances=False, dtype_num_neighbors=torch.int64,
                                distance_type="ball"):
@@ -97,6 +98,7 @@ def radius_search_sorted_grid8(points, queries, radius, sample_inds=None, query_
 
 
 @torch.no_grad()
+@_cabi.on_geometry_stream
 def radius_search_sorted_grid8_segments(points, queries, radius, kernel_size, kernel_grid_size,
                                         sample_inds=None, query_sample_inds=None,
                                         dtype_num_neighbors=torch.int64, distance_type="ball",

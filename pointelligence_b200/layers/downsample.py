@@ -2,10 +2,12 @@
 ``layers/downsample.py:15-42``)."""
 import torch
 
+from .. import _cabi
 from ..internals.grid_sample import grid_sample_filter
 
 
 @torch.compiler.disable
+@_cabi.on_geometry_stream
 def downsample(points, sample_inds, grid_size, stride):
     """Returns ``(points_, sample_inds_, grid_size * stride, indices)``."""
     with torch.no_grad():

@@ -16,6 +16,7 @@ from typing import Callable, Optional
 import torch
 from torch.nn.modules.utils import _triple
 
+from .. import _cabi
 from ..internals.indexing import cumsum_exclusive, repeat_interleave_indices
 from ..internals.neighbors import radius_search, radius_search_sorted_grid8_segments
 from ..internals.triplet_cache import cache_get, cache_put, triplet_key
@@ -76,6 +77,7 @@ def _resolve_queries(points, sample_inds, sample_sizes, query_points, query_samp
 
 
 @torch.compiler.disable
+@_cabi.on_geometry_stream
 def build_triplets_segmented(points, sample_inds, sample_sizes, neighbor_radius, kernel_size,
                              query_points=None, query_sample_inds=None, query_sample_sizes=None,
                              return_num_neighbors=False, radius_scaler=None, tap_stripes=32):
@@ -137,6 +139,7 @@ def _triplets_from_pairs(points, query_points, neighbor_indices, num_neighbors, 
 
 
 @torch.compiler.disable
+@_cabi.on_geometry_stream
 def build_triplets(points, sample_inds, sample_sizes, neighbor_radius, kernel_indexer: Callable,
                    query_points=None, query_sample_inds=None, query_sample_sizes=None, sort_by="k",
                    return_num_neighbors=False, radius_scaler: Optional[float] = None):
@@ -184,6 +187,7 @@ def _build_for(m_points, m_sample_inds, m_sample_sizes, neighbor_radius, kernel_
 
 
 @torch.compiler.disable
+@_cabi.on_geometry_stream
 def handle_stride_and_build_triplets(m: MetaData, stride, kernel_size=_triple(3),
                                      receptive_field_scaler=1.0, sort_by="k",
                                      return_num_neighbors=False, distance_type="ball") -> MetaData:
@@ -241,6 +245,7 @@ def partition_slots(points, cell_size, slots_per_axis):
 
 
 @torch.compiler.disable
+@_cabi.on_geometry_stream
 def handle_stride_disjoint_and_build_triplets(m: MetaData, stride, kernel_size=_triple(3), sort_by="k") -> MetaData:
     """Strided convolution as a grid partition (``layers/triplets.py:1042-1167`` of the reference):
     no search.  Every input point belongs to exactly one cell of side ``stride * grid_size``; the
@@ -365,6 +370,7 @@ def _residual_net(points, sample_inds, c0_points, point_to_c0, uncovered, radius
 
 
 @torch.compiler.disable
+@_cabi.on_geometry_stream
 def build_full_cover_strided_rulebook(points, sample_inds, sample_sizes, *, stride, input_grid_size,
                                       kernel_size, radius_margin=1e-2, radius_backend="auto",
                                       return_num_neighbors=True) -> FullCoverStridedRulebook:

@@ -60,3 +60,58 @@ def test_wide_input_convolution_is_split_and_matches_oracle():
     wn = conv.weight.detach().float().cpu().numpy().astype(np.float64)
     ref = oso.mvmr_f64(wn, k, x.float().cpu().numpy().astype(np.float64)[:, None, :], j, i, n_out)[:, 0]
     assert oso.rel_frobenius(out.detach().float().cpu().numpy(), ref) < 2e-2
+
+
+def test_geometry_on_its_own_stream_gives_the_same_step(monkeypatch):
+    """The backbone builds its geometry on a side stream beside the feature kernels
+    (``_cabi.geometry_overlap``); with the scope switched off the same step must come out: same
+    rulebooks, logits and gradients equal up to the order of the fp32 atomics."""
+    import torch.nn.functional as F
+
+    from pointelligence_b200 import _cabi
+    from pointelligence_b200.backbone import ResUNet
+    from pointelligence_b200.layers.metadata import MetaData
+    from pointelligence_b200.layers.triplets import handle_stride_and_build_triplets
+    from pointelligence_b200.synthetic import indoor_scene, ragged_batch
+
+    pts, inds, sizes = ragged_batch([indoor_scene(20000, 3), indoor_scene(9000, 4), indoor_scene(14000, 5)])
+    dev = torch.device("cuda:0")
+    pts, inds, sizes = (torch.from_numpy(a).to(dev) for a in (pts, inds, sizes))
+    n = pts.shape[0]
+    feat = torch.randn(n, 3, device=dev, generator=torch.Generator(device=dev).manual_seed(0))
+    labels = torch.randint(0, 20, (n,), device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+    torch.manual_seed(0)
+    model = ResUNet(in_channels=3, num_classes=20).to(dev)
+    runs = []
+    for mode in ("0", "0", "1", "1"):
+        monkeypatch.setenv("PCX_GEOMETRY_OVERLAP", mode)
+        model.zero_grad(set_to_none=True)
+        # a long kernel queue in front of the step: the side stream must not run ahead of its inputs
+        busy = torch.randn(4096, 4096, device=dev)
+        for _ in range(20):
+            busy = busy @ busy * 1e-3
+        logits = model(feat + busy[0, 0] * 0, pts, inds, sizes, 0.02)
+        F.cross_entropy(logits.float(), labels).backward()
+        grads = torch.cat([p.grad.flatten().float() for p in model.parameters()])
+        runs.append((logits.detach().float(), grads))
+    # two runs of the same bf16 step differ by the order of their fp32 atomics; a run with the
+    # geometry on its own stream must differ from a plain run by no more than that
+    rel = lambda a, b: float((a - b).norm() / b.norm())
+    for part in (0, 1):
+        noise = rel(runs[1][part], runs[0][part])
+        for overlapped in (runs[2], runs[3]):
+            assert torch.isfinite(overlapped[part]).all()
+            assert rel(overlapped[part], runs[0][part]) <= 3 * noise + 1e-3, (part, noise)
+    # the rulebook of a strided layer, built inside and outside a scope, is bit-identical
+    books = []
+    for scoped in (True, False):
+        m = MetaData(points=pts, sample_inds=inds, sample_sizes=sizes, grid_size=0.02)
+        if scoped:
+            with _cabi.geometry_overlap(dev):
+                m = handle_stride_and_build_triplets(m, 2.0, (3, 3, 3), 1.0)
+        else:
+            m = handle_stride_and_build_triplets(m, 2.0, (3, 3, 3), 1.0)
+        torch.cuda.synchronize()
+        books.append(m)
+    for name in ("i", "j", "k", "seg_offs", "points", "sample_inds", "downsample_indices"):
+        assert torch.equal(getattr(books[0], name), getattr(books[1], name)), name

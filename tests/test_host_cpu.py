@@ -298,6 +298,12 @@ from layers import (MetaData, PointConv3d, TripletContract, build_triplets, buil
 from layers.downsample import downsample
 from internals.neighbors import radius_search, radius_search_sorted_grid8, radius_search_sorted_grid8_segments
 from internals.grid_sample import grid_sample_filter
+from internals.two_phase import ForceFused, GeometryScheduler, TwoPhaseOp
+from layers.two_phase_conv import ConvOp
+from layers.generative import GeneratedSites, KernelStampGenerator, SubdivisionGenerator, build_generative_triplets
+from layers.conv import GenerativePointConv3d, conv_with_stride_disjoint
+from layers.triplets import handle_stride_disjoint_and_build_triplets
+from layers.norm import RaggedGroupNorm, RaggedInstanceNorm, RaggedLayerNorm
 import pointelligence_b200.layers as ours, layers
 assert layers is ours and layers.PointConv3d is ours.PointConv3d
 import sparse_engines.tig, pointelligence_b200.sparse_engines.tig as t
