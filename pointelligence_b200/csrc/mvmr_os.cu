@@ -230,25 +230,37 @@ __global__ void plan_entries_kernel(const uint32_t *__restrict__ key_sorted, con
 // scratch[b] = sum of the feature rows of bucket b (fp32 sum in entry order, one rounding); one thread
 // per 16-byte piece.  The row indices of up to four members are fetched together and their pieces
 // together after that, so that a bucket costs two memory latencies instead of two per member.
-__device__ __forceinline__ void add_piece(float (&acc)[8], uint4 v, int fmt) {
+// The element format and, for the usual row widths, the pieces per row are compile-time values: the
+// first version of this kernel spent most of its instructions on a 64-bit division of the thread
+// index and on per-element format branches (749 M warp instructions for 9 M buckets, issue-bound
+// at 28 % of the DRAM bandwidth).
+template <int FMT>
+__device__ __forceinline__ void add_piece(float (&acc)[8], uint4 v) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         float2 f;
-        if (fmt) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[q]));
+        if (FMT) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[q]));
         else f = __half22float2(*reinterpret_cast<const __half2 *>(&w[q]));
         acc[2 * q] += f.x, acc[2 * q + 1] += f.y;
     }
 }
 
-__global__ void bucket_sum_kernel(const uint16_t *__restrict__ feat, const uint2 *__restrict__ entries,
-                                  const uint2 *__restrict__ buckets, const uint32_t *__restrict__ ctrl, int inw, int fmt,
-                                  uint16_t *scratch) {
-    const int ppr = inw >> 3;
-    const int64_t x = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t b = x / ppr;
-    const int piece = (int)(x - b * ppr);
-    if (b >= (int64_t)ctrl[CTRL_NMULTI]) return;
+constexpr int BUCKET_SUM_THREADS = 256;
+
+// PPR: 16-byte pieces per row when that is a power of two (2 .. 32), else 0 (taken from inw).
+// (Two pieces per thread were tried: fewer instructions per byte, but fewer resident warps, and slower.)
+template <int FMT, int PPR>
+__global__ void __launch_bounds__(BUCKET_SUM_THREADS) bucket_sum_kernel(const uint16_t *__restrict__ feat,
+                                                                        const uint2 *__restrict__ entries,
+                                                                        const uint2 *__restrict__ buckets,
+                                                                        const uint32_t *__restrict__ ctrl, int inw,
+                                                                        uint16_t *scratch) {
+    const unsigned ppr = PPR ? (unsigned)PPR : (unsigned)inw >> 3;
+    const unsigned per_block = BUCKET_SUM_THREADS / ppr;
+    const unsigned local = threadIdx.x / ppr, piece = threadIdx.x - local * ppr;
+    const unsigned b = blockIdx.x * per_block + local;
+    if (local >= per_block || b >= ctrl[CTRL_NMULTI]) return;
     const uint2 bk = __ldg(buckets + b);
     const uint16_t *col = feat + piece * 8;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -259,15 +271,31 @@ __global__ void bucket_sum_kernel(const uint16_t *__restrict__ feat, const uint2
         uint4 v[4];
 #pragma unroll
         for (int m = 0; m < 4; ++m)
-            v[m] = m0 + m < bk.y ? __ldg(reinterpret_cast<const uint4 *>(col + (int64_t)rows[m] * inw)) : make_uint4(0, 0, 0, 0);
+            v[m] = m0 + m < bk.y ? __ldg(reinterpret_cast<const uint4 *>(col + (size_t)rows[m] * (unsigned)inw)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int m = 0; m < 4; ++m)
-            if (m0 + m < bk.y) add_piece(acc, v[m], fmt);
+        for (int m = 0; m < 4; ++m) add_piece<FMT>(acc, v[m]);   // an absent member adds zeros
     }
     uint4 o;
-    o.x = pack2(acc[0], acc[1], fmt), o.y = pack2(acc[2], acc[3], fmt);
-    o.z = pack2(acc[4], acc[5], fmt), o.w = pack2(acc[6], acc[7], fmt);
-    *reinterpret_cast<uint4 *>(scratch + b * inw + piece * 8) = o;
+    o.x = pack2(acc[0], acc[1], FMT), o.y = pack2(acc[2], acc[3], FMT);
+    o.z = pack2(acc[4], acc[5], FMT), o.w = pack2(acc[6], acc[7], FMT);
+    *reinterpret_cast<uint4 *>(scratch + (size_t)b * (unsigned)inw + piece * 8) = o;
+}
+
+template <int FMT>
+void launch_bucket_sum(int64_t multi, int inw, const uint16_t *feat, const uint2 *entries, const uint2 *buckets,
+                       const uint32_t *ctrl, uint16_t *scratch, cudaStream_t stream) {
+    const int ppr = inw >> 3;
+    const unsigned grid = (unsigned)((multi + BUCKET_SUM_THREADS / ppr - 1) / (BUCKET_SUM_THREADS / ppr));
+#define PCX_BS(P) bucket_sum_kernel<FMT, P><<<grid, BUCKET_SUM_THREADS, 0, stream>>>(feat, entries, buckets, ctrl, inw, scratch)
+    switch (ppr) {
+        case 2: PCX_BS(2); break;
+        case 4: PCX_BS(4); break;
+        case 8: PCX_BS(8); break;
+        case 16: PCX_BS(16); break;
+        case 32: PCX_BS(32); break;
+        default: PCX_BS(0); break;
+    }
+#undef PCX_BS
 }
 
 // cost of a group = its non-empty tiles (each is one A tile to gather and multiply)
@@ -954,10 +982,9 @@ int pcx_mvmr_planned(const void *d_weight, const void *d_feat, void *d_plan, siz
     }
     const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(pv.ngroups, (int64_t)ctas * num_sms()));
     if (multi_buckets > 0) {
-        const int64_t threads = multi_buckets * (inw >> 3);
         prof_begin("bucket_sum_kernel", stream);
-        bucket_sum_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(p.feat, pv.entries, pv.buckets, pv.ctrl, inw, p.fmt,
-                                                                               (uint16_t *)d_ws);
+        if (p.fmt) launch_bucket_sum<1>(multi_buckets, inw, p.feat, pv.entries, pv.buckets, pv.ctrl, (uint16_t *)d_ws, stream);
+        else launch_bucket_sum<0>(multi_buckets, inw, p.feat, pv.entries, pv.buckets, pv.ctrl, (uint16_t *)d_ws, stream);
         prof_end(stream);
         PCX_LAUNCH_CHECK();
     }
