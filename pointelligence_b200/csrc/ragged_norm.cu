@@ -120,37 +120,51 @@ __global__ void ln_moments_kernel(const T *__restrict__ x, const int64_t *__rest
     }
 }
 
-__global__ void ln_combine_kernel(const Moments *__restrict__ rec, const int64_t *__restrict__ offsets, float *mean,
-                                  float *rstd, int64_t S, float eps) {
+constexpr int COMBINE_THREADS = 256;
+
+__device__ __forceinline__ double block_sum_f64(double v, double *scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double t = 0.0;
+    for (int w = 0; w < COMBINE_THREADS / 32; ++w) t += scratch[w];
+    return t;
+}
+
+// one block per sample: the sample's pieces are spread over the threads, the sums are folded in fp64
+__global__ void __launch_bounds__(COMBINE_THREADS) ln_combine_kernel(const Moments *__restrict__ rec,
+                                                                     const int64_t *__restrict__ offsets, float *mean,
+                                                                     float *rstd, int64_t S, float eps) {
+    __shared__ double scratch[COMBINE_THREADS / 32];
     const int64_t s = blockIdx.x;
-    const int lane = threadIdx.x;   // one warp per sample
     const int64_t lo = offsets[s], hi = offsets[s + 1];
-    if (hi <= lo) {
-        if (lane == 0) mean[s] = 0.f, rstd[s] = 1.f / sqrtf(eps);
+    if (hi <= lo) {   // the same decision in every thread
+        if (threadIdx.x == 0) mean[s] = 0.f, rstd[s] = 1.f / sqrtf(eps);
         return;
     }
     const int64_t b0 = lo / LN_ROWS, b1 = (hi - 1) / LN_ROWS;
     double n = 0.0, sum = 0.0;
-    for (int64_t b = b0 + lane; b <= b1; b += 32) {
+    for (int64_t b = b0 + threadIdx.x; b <= b1; b += COMBINE_THREADS) {
         const Moments m = rec[b + s];
         n += m.n, sum += (double)m.n * m.mean;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o), sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    n = block_sum_f64(n, scratch);
+    sum = block_sum_f64(sum, scratch);
     const double mu = sum / n;
     double m2 = 0.0;
-    for (int64_t b = b0 + lane; b <= b1; b += 32) {
+    for (int64_t b = b0 + threadIdx.x; b <= b1; b += COMBINE_THREADS) {
         const Moments m = rec[b + s];
         const double d = (double)m.mean - mu;
         m2 += (double)m.m2 + (double)m.n * d * d;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m2 += __shfl_xor_sync(0xffffffffu, m2, o);
-    if (lane == 0) mean[s] = (float)mu, rstd[s] = 1.f / sqrtf((float)(m2 / n) + eps);
+    m2 = block_sum_f64(m2, scratch);
+    if (threadIdx.x == 0) mean[s] = (float)mu, rstd[s] = 1.f / sqrtf((float)(m2 / n) + eps);
 }
 
 template <typename T, int VN>
-__global__ void ln_apply_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets,
+__global__ void __launch_bounds__(LN_THREADS, 5) ln_apply_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets,
                                 const float *__restrict__ mean, const float *__restrict__ rstd,
                                 const float *__restrict__ weight, const float *__restrict__ bias,
                                 const T *__restrict__ residual, T *y, int64_t N, int64_t S, int C, int relu) {
@@ -189,7 +203,7 @@ __global__ void ln_apply_kernel(const T *__restrict__ x, const int64_t *__restri
 // stay in registers while a thread's rows belong to one sample; the per-channel sums of
 // the row lanes are folded in shared memory, one atomic per channel and block.
 template <typename T, int VN>
-__global__ void ln_bwd_sums_kernel(const T *__restrict__ g, const T *__restrict__ x, const T *__restrict__ y,
+__global__ void __launch_bounds__(LN_THREADS, 4) ln_bwd_sums_kernel(const T *__restrict__ g, const T *__restrict__ x, const T *__restrict__ y,
                                    const int64_t *__restrict__ offsets, const float *__restrict__ mean,
                                    const float *__restrict__ rstd, const float *__restrict__ weight, float *s1,
                                    float *s2, float *dweight, float *dbias, T *dresidual, int64_t N, int64_t S,
@@ -293,7 +307,7 @@ __global__ void ln_bwd_apply_kernel(const T *__restrict__ g, const T *__restrict
             const float m1 = s1[s] * inv_n, m2 = s2[s] * inv_n;
             const int64_t at = r * C + (int64_t)vcol * VN;
             float gv[VN], xv[VN], yv[VN];
-            load_vec<T, VN>(g + at, gv);
+            load_vec<T, VN>(g + at, gv);   // with relu == 0 this may be the gradient the sums pass already masked
             load_vec<T, VN>(x + at, xv);
             if (relu) load_vec<T, VN>(y + at, yv);
 #pragma unroll
@@ -633,7 +647,7 @@ int pcx_ragged_layer_norm(const void *d_x, const int64_t *d_lengths, const float
         PCX_LN_DISPATCH(dtype, vec, (ln_moments_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, w.rec, N, S, C)));
         PCX_LAUNCH_CHECK();
     }
-    ln_combine_kernel<<<(unsigned)S, 32, 0, stream>>>(w.rec, w.offsets, d_mean, d_rstd, S, (float)eps);
+    ln_combine_kernel<<<(unsigned)S, COMBINE_THREADS, 0, stream>>>(w.rec, w.offsets, d_mean, d_rstd, S, (float)eps);
     PCX_LAUNCH_CHECK();
     if (N > 0) {
         prof_begin("ln_apply_kernel", stream);
@@ -672,9 +686,12 @@ int pcx_ragged_layer_norm_backward(const void *d_grad_y, const void *d_x, const 
                                (const T *)d_grad_y, (const T *)d_x, (const T *)d_y, w.offsets, d_mean, d_rstd, d_weight,
                                w.sums, w.sums + S, d_grad_weight, d_grad_bias, (T *)d_grad_residual, N, S, C, relu)));
     PCX_LAUNCH_CHECK();
+    // the sums pass wrote the ReLU-masked gradient as the residual's gradient: the second pass reads
+    // that instead of masking again, which spares it the read of y
+    const bool masked = relu && d_grad_residual;
     PCX_LN_DISPATCH(dtype, vec, (ln_bwd_apply_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>(
-                               (const T *)d_grad_y, (const T *)d_x, (const T *)d_y, w.offsets, d_mean, d_rstd, d_weight,
-                               w.sums, w.sums + S, (T *)d_grad_x, N, S, C, relu)));
+                               (const T *)(masked ? d_grad_residual : d_grad_y), (const T *)d_x, (const T *)d_y, w.offsets,
+                               d_mean, d_rstd, d_weight, w.sums, w.sums + S, (T *)d_grad_x, N, S, C, masked ? 0 : relu)));
     PCX_LAUNCH_CHECK();
     return PCX_OK;
 }
