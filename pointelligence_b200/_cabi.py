@@ -414,6 +414,29 @@ def mvmr_plan(scatter, gather, seg_offs, K, n_out, group_blocks):
 
 _PLAN_CACHE = {}
 _PLAN_CACHE_MAX = 64
+_SYMMETRIC = {}
+
+
+def mark_symmetric(i, j):
+    """Record that the rulebook ``(i, j, k)`` these index tensors belong to is its own mirror image:
+    with ``(i, j, k)`` it holds ``(j, i, K - 1 - k)``.  True for a self-search (queries are the points):
+    the distance is symmetric and the tap of the opposite offset is the mirrored tap.  The input
+    gradient of such a layer is then a forward pass over the SAME rulebook with the taps of the
+    weight reversed, so it needs no plan of its own (``tig_grad_input``).  Remembered by tensor
+    identity, like the plans."""
+    import weakref
+
+    for key in [key for key, (refs, _) in _SYMMETRIC.items() if any(r() is None for r in refs)]:
+        _SYMMETRIC.pop(key, None)
+    _SYMMETRIC[(i.data_ptr(), j.data_ptr(), i.numel())] = ((weakref.ref(i), weakref.ref(j)), (i._version, j._version))
+
+
+def is_symmetric(i, j):
+    hit = _SYMMETRIC.get((i.data_ptr(), j.data_ptr(), i.numel()))
+    if hit is None or os.environ.get("PCX_SYMMETRIC_DGRAD", "1") == "0":
+        return False
+    refs, stamp = hit
+    return refs[0]() is i and refs[1]() is j and stamp == (i._version, j._version)
 
 
 def cached_mvmr_plan(scatter, gather, seg_offs, K, n_out, group_blocks):

@@ -112,6 +112,8 @@ def build_triplets_segmented(points, sample_inds, sample_sizes, neighbor_radius,
             lonely = int((num_neighbors == 0).sum().item()) if num_neighbors.numel() else 0
         if lonely:
             raise AssertionError(_NO_NEIGHBOR_MSG)
+        if query_points is points:       # self-search: the rulebook is its own mirror image
+            _cabi.mark_symmetric(i, j)
         out = (i, j, k, seg_offs, (num_neighbors if return_num_neighbors else None))
         cache_put(key, out, points)
         return out

@@ -16,6 +16,7 @@ from typing import Optional
 import torch
 from torch import Tensor
 
+from .. import _cabi
 from ._dispatch_override import current_engine, resolve_input_precision
 from ._ops import mvmr_op, vvor_op
 from ._seg_offs import kernel_offset_segments
@@ -94,6 +95,12 @@ def tig_grad_input(weight, grad_out, index, input_precision=None, flat_cfg=None)
     assert grad_out.size(0) == index.N, f"grad_out rows {grad_out.size(0)} != index.N {index.N}"
     out_dtype = grad_out.dtype
     w, grad_out = _match(w, grad_out)
+    if index.N == index.N_in and _cabi.is_symmetric(index.flat_i, index.flat_j):
+        # a self-search rulebook holds (j, i, K - 1 - k) with every (i, j, k): the input gradient is
+        # the forward schedule over the same rulebook (and the same plan) with the taps reversed
+        out = mvmr_op(w.flip(0), grad_out, index.flat_j, index.flat_i, index.flat_seg, None, index.N_in, True,
+                      current_engine())
+        return out.to(out_dtype)
     out = mvmr_op(w, grad_out, index.flat_i, index.flat_j, index.flat_seg, None, index.N_in, True,
                   current_engine())
     return out.to(out_dtype)

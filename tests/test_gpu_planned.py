@@ -210,3 +210,41 @@ def test_bounded_wait_that_runs_out_is_reported():
     radius_search_sorted_grid8(pts, pts, 0.2)
     with pytest.raises(ValueError):
         _cabi.debug_wait_runs_out(10 ** 12)
+
+
+def test_symmetric_rulebook_input_gradient_reuses_the_forward_plan(monkeypatch):
+    """A self-search rulebook is its own mirror image, so the input gradient runs as a forward
+    schedule over the same rulebook with reversed taps: same result as the separate transposed
+    pass (and as the fp64 oracle), and no second plan is built."""
+    from pointelligence_b200 import _cabi
+    from pointelligence_b200.layers import PointConv3d
+    from pointelligence_b200.layers.triplets import build_triplets_segmented
+    from pointelligence_b200.synthetic import indoor_scene
+
+    dev = torch.device("cuda:0")
+    monkeypatch.setattr(_cabi, "_PLANNED_DENSE_RATIO", 0.0)      # every tap-sorted bf16 layer takes the planned engine
+    pts = torch.from_numpy(indoor_scene(20000, 9)).to(dev)
+    n = pts.shape[0]
+    smp = torch.zeros(n, dtype=torch.int64, device=dev)
+    i, j, k, seg, _ = build_triplets_segmented(pts, smp, torch.tensor([n], device=dev), 0.05, 3, radius_scaler=2.5)
+    assert _cabi.is_symmetric(i, j)
+    key = lambda a, b, c: torch.sort(c.long() * n * n + a.long() * n + b.long()).values
+    assert torch.equal(key(i, j, k), key(j, i, 26 - k))             # the mirror property itself
+    torch.manual_seed(0)
+    conv = PointConv3d(32, 64, kernel_size=3, bias=False).to(dev).to(torch.bfloat16)
+    x0 = torch.randn(n, 32, device=dev).to(torch.bfloat16)
+    go = torch.randn(n, 64, device=dev).to(torch.bfloat16)
+    grads = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("PCX_SYMMETRIC_DGRAD", mode)
+        _cabi._PLAN_CACHE.clear()
+        x = x0.clone().requires_grad_(True)
+        conv(x, i, j, k, n, seg_offs=seg).backward(go)
+        grads[mode] = (x.grad.float(), len(_cabi._PLAN_CACHE))
+    assert grads["1"][1] == 1 and grads["0"][1] == 2                 # one plan against two
+    w = conv.weight.detach().double()[:, 0]
+    want = torch.zeros(n, 32, dtype=torch.float64, device=dev)
+    want.index_add_(0, j.long(), torch.einsum("tm,tcm->tc", go.double()[i.long()], w[k.long()]))
+    for mode in ("1", "0"):
+        err = (grads[mode][0].double() - want).norm() / want.norm()
+        assert float(err) < 1e-2, (mode, float(err))
