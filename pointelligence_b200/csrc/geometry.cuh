@@ -69,6 +69,23 @@ __device__ __forceinline__ int tap_of(float qx, float qy, float qz, float4 p, fl
     return (kx * K + ky) * K + kz;
 }
 
+// The same tap without the three IEEE divisions where that is safe: rint(d / g) equals rint(d * (1 / g))
+// unless the quotient lies within a few ulp of a half-integer, because the product differs from the
+// correctly rounded quotient by at most about two ulp.  A component whose product is farther than
+// 0.49 from its nearest integer (or large) is decided by the exact division, as in tap_of.
+__device__ __forceinline__ int tap_axis_fast(float d, float g32, float inv_g) {
+    const float t = __fmul_rn(d, inv_g);
+    const float r = rintf(t);
+    if (fabsf(t - r) > 0.49f || fabsf(t) > 4096.f) return __float2int_rn(__fdiv_rn(d, g32));
+    return (int)r;
+}
+__device__ __forceinline__ int tap_of_fast(float qx, float qy, float qz, float4 p, float g32, float inv_g, int K) {
+    const int half = K >> 1;
+    const int dx = tap_axis_fast(__fsub_rn(p.x, qx), g32, inv_g), dy = tap_axis_fast(__fsub_rn(p.y, qy), g32, inv_g),
+              dz = tap_axis_fast(__fsub_rn(p.z, qz), g32, inv_g);
+    const int kx = min(max(dx + half, 0), K - 1), ky = min(max(dy + half, 0), K - 1), kz = min(max(dz + half, 0), K - 1);
+    return (kx * K + ky) * K + kz;
+}
 
 }  // namespace geo
 }  // namespace pcx

@@ -134,7 +134,7 @@ struct TapArgs {
     int32_t *out_i, *out_j, *out_k;
     int64_t Q, nblocks, capacity;
     uint32_t mask;
-    float r32, inv, g32, s_max;
+    float r32, inv, g32, inv_g, s_max;
     int distance_type, variant, K, k3, use_s_max;
 };
 
@@ -194,7 +194,7 @@ __device__ __forceinline__ void walk_run(const TapArgs &a, int2 r, float qx, flo
                 keep &= ~(1ULL << t);
                 continue;
             }
-            hit(tap_of(qx, qy, qz, p, a.g32, a.K), j);
+            hit(tap_of_fast(qx, qy, qz, p, a.g32, a.inv_g, a.K), j);
         }
         if (!STORED && first) *first_mask = keep;
     }
@@ -384,6 +384,7 @@ TapArgs make_args(const TapsWs &w, const float *queries, const int32_t *point_sa
     a.lane_counts = w.lane_counts, a.block_hist = w.block_hist, a.seg = w.seg, a.ctrl = w.ctrl, a.ctrl_rw = w.ctrl;
     a.Q = Q, a.nblocks = w.nblocks, a.mask = (uint32_t)(w.buckets - 1);
     a.r32 = (float)radius, a.inv = (float)(1.0 / (2.0 * radius)), a.g32 = (float)grid;
+    a.inv_g = 1.0f / a.g32;
     a.distance_type = distance_type, a.variant = radius_variant(), a.K = kernel_size;
     a.k3 = kernel_size * kernel_size * kernel_size;
     a.use_s_max = distance_type == 0 && a.variant != 2;

@@ -188,3 +188,21 @@ def test_builder_raises_for_a_query_without_neighbour():
         build_triplets_segmented(pts, smp, torch.tensor([3000], device=dev), 0.05, 3, query_points=qry,
                                  query_sample_inds=qsm, query_sample_sizes=torch.tensor([51], device=dev),
                                  radius_scaler=2.5)
+
+
+def test_tap_ties_on_a_half_grid_lattice():
+    """Points on a lattice of half the tap grid: every offset divided by the tap grid is an integer
+    or a half-integer, the round-half-even cases the division-free tap computation must hand to
+    the exact division."""
+    from pointelligence_b200 import _cabi
+
+    dev = torch.device("cuda:0")
+    g = 0.02
+    axis = torch.arange(24, device=dev, dtype=torch.float32) * (g / 2)
+    pts = torch.cartesian_prod(axis, axis, axis).contiguous()
+    pts = pts + torch.tensor([0.3, -0.2, 1.7], device=dev)          # lattice offsets that are not representable exactly
+    for k, radius in ((3, 0.05), (5, 0.045)):
+        _cabi._TAPS_RATIO.clear()
+        ref, got = _both(pts, pts, None, None, radius, k, g)
+        _assert_same(ref, got)
+        assert got[0].numel() > 20 * pts.shape[0]
