@@ -52,6 +52,17 @@ typedef enum {
     PCX_ENGINE_TENSOR = 2   /* tcgen05 path or PCX_E_UNSUPPORTED               */
 } pcx_engine;
 
+/* May be OR-ed into the `engine` argument of pcx_mvmr: the caller guarantees that
+ * every output row occurs in exactly one triplet (T == n_out; the fan-in-1
+ * contract of a subdivision rulebook in the forward direction, or of a grid
+ * partition in the input-gradient direction: layers/contract.py:27-64
+ * exact_cover_out / exact_cover_in, engines of sparse_engines/tig.py:227-291).
+ * The tensor engine then stores each rounded row itself: no accumulator is
+ * cleared, nothing is reduced, no rounding pass follows.  Other engines ignore
+ * the flag.  A rulebook that breaks the guarantee gives an unspecified result
+ * in the rows concerned (no fault). */
+#define PCX_ENGINE_FLAG_FAN_IN_ONE 0x100
+
 int pcx_version(void);
 const char *pcx_last_error_string(void);
 

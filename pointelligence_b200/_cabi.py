@@ -21,6 +21,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libpointelligence_b200.so")
 
 PCX_F32, PCX_F16, PCX_BF16 = 0, 1, 2
 ENGINE_AUTO, ENGINE_CUDA_CORE, ENGINE_TENSOR = 0, 1, 2
+ENGINE_FLAG_FAN_IN_ONE = 0x100   # OR-ed into an engine: every output row occurs in exactly one triplet
 PCX_E_CAPACITY = -4
 
 _DTYPES = {torch.float32: PCX_F32, torch.float16: PCX_F16, torch.bfloat16: PCX_BF16}

@@ -72,7 +72,10 @@ int pcx_mvmr(const void *d_weight, const void *d_feat, const int32_t *d_gather, 
         PCX_FAIL(PCX_E_ARG, "pcx_mvmr: negative or zero size (T=%lld n_feat=%lld n_out=%lld K=%d G=%d C=%d M=%d)",
                  (long long)T, (long long)n_feat, (long long)n_out, K, G, C, M);
     if (dtype != PCX_F32 && dtype != PCX_F16 && dtype != PCX_BF16) PCX_FAIL(PCX_E_DTYPE, "pcx_mvmr: unsupported dtype %d", dtype);
+    const bool fan_in_one = (engine & PCX_ENGINE_FLAG_FAN_IN_ONE) != 0;
+    engine &= ~PCX_ENGINE_FLAG_FAN_IN_ONE;
     if (engine < 0 || engine > 2) PCX_FAIL(PCX_E_ARG, "pcx_mvmr: unknown engine %d", engine);
+    if (fan_in_one && T != n_out) PCX_FAIL(PCX_E_ARG, "pcx_mvmr: fan-in 1 means one triplet per output row (T=%lld, n_out=%lld)", (long long)T, (long long)n_out);
     if (!d_weight || (n_out > 0 && !d_out) || !d_ws) PCX_FAIL(PCX_E_ARG, "pcx_mvmr: null pointer");
     if (T > 0 && (!d_feat || !d_gather || !d_scatter)) PCX_FAIL(PCX_E_ARG, "pcx_mvmr: null pointer");
     if (T > 0 && !d_seg_offs && !d_tap_idx) PCX_FAIL(PCX_E_ARG, "pcx_mvmr: either d_seg_offs or d_tap_idx is required");
@@ -96,9 +99,15 @@ int pcx_mvmr(const void *d_weight, const void *d_feat, const int32_t *d_gather, 
     a.chunk_table = w.chunk_table;
     a.T = T, a.n_feat = n_feat, a.n_out = n_out;
     a.K = K, a.G = G, a.C = C, a.M = M, a.transpose = transpose ? 1 : 0, a.dtype = dtype;
+    if (force_engine()) engine = force_engine();
+    if (fan_in_one && T > 0 && engine != PCX_ENGINE_CUDA_CORE && mvmr_tensor_supported(a) && ((uintptr_t)d_out & 15) == 0) {
+        // every output row has exactly one triplet: the tensor kernel stores the rounded rows
+        // itself -- no accumulator to clear, no reductions, no rounding pass
+        a.out_rows = d_out;
+        return mvmr_tensor(a, stream);
+    }
     PCX_CUDA(cudaMemsetAsync(a.acc, 0, (size_t)out_elems * sizeof(float), stream));
     if (T > 0) {
-        if (force_engine()) engine = force_engine();
         bool tensor_ok = mvmr_tensor_supported(a);
         if (engine == PCX_ENGINE_TENSOR && !tensor_ok)
             PCX_FAIL(PCX_E_UNSUPPORTED, "pcx_mvmr: tensor engine needs fp16/bf16, G=1, tap-sorted triplets and channel counts that are multiples of 16 in [16,256]");

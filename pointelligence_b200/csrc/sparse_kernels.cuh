@@ -12,6 +12,7 @@ struct MvmrArgs {
     const int64_t *seg_offs; // (K+1) or null
     const int32_t *tap_idx;  // (T) when seg_offs is null
     float *acc;              // (n_out, G*outw) fp32, zeroed by the caller
+    void *out_rows;          // tensor engine, fan-in 1: the output itself, written row by row (acc unused)
     int32_t *chunk_table;    // (K+1) scratch of the CUDA-core engine
     int64_t T, n_feat, n_out;
     int K, G, C, M, transpose, dtype;

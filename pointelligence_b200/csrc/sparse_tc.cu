@@ -160,12 +160,22 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 
+__device__ __forceinline__ uint32_t pack_pair(float a, float b, int fmt) {
+    if (fmt) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
 struct MvmrTcParams {
     const uint16_t *weight;  // (K, C, M) as stored
     const uint16_t *feat;
     const int32_t *gather, *scatter;
     const int64_t *seg;
     float *acc;
+    uint16_t *out;           // MODE 2: the output rows themselves (every row occurs in exactly one triplet)
     int K, C, M, transpose, fmt, nbuf, slab;  // slab: columns parked per bulk reduction (32 or 64)
     int prow_log2;                            // a warp parks 2^prow_log2 rows at a time (8, 16 or 32)
     uint32_t park_bytes;                      // size of the parking area (the chunk table follows it)
@@ -177,8 +187,12 @@ struct MvmrTcParams {
 // when the parking area aliases the tile, once the reductions have read it) and the other
 // CTAs resident on the SM cover its latency; the indices of chunk c+2 are already on their
 // way into registers.  nbuf == 2 keeps a ring of two A tiles instead.
-template <bool BULK>
+// MODE 0: sums leave through two-float reductions from registers; 1: one bulk reduction per row
+// (rows of 64 floats); 2: plain 16-byte stores of the rounded row, for rulebooks in which every output
+// row occurs in exactly one triplet (fan-in 1: nothing to accumulate, clear or round afterwards).
+template <int MODE>
 __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
+    constexpr bool BULK = MODE == 1;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t s_bar;
     __shared__ uint32_t s_tmem;
@@ -345,7 +359,27 @@ __global__ void __launch_bounds__(128) mvmr_tc_kernel(MvmrTcParams p) {
                     bulk_commit();
                 }
             }
-        } else if (!BULK && alive && warp * 32 < rows) {
+        } else if (MODE == 2 && alive && warp * 32 < rows) {
+            // one thread per accumulator row: 32 columns at a time, rounded and stored
+            const int row = warp * 32 + lane;
+            const bool row_ok = row < rows;
+            uint16_t *dst_row = p.out + (int64_t)(row_ok ? s_scatter[b][row] : 0) * outw;
+            for (int col0 = 0; col0 < outw; col0 += 32) {
+                float v[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)col0, v);
+                if (row_ok) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (col0 + 8 * q < outw) {
+                            uint4 o;
+                            o.x = pack_pair(v[8 * q], v[8 * q + 1], p.fmt), o.y = pack_pair(v[8 * q + 2], v[8 * q + 3], p.fmt);
+                            o.z = pack_pair(v[8 * q + 4], v[8 * q + 5], p.fmt), o.w = pack_pair(v[8 * q + 6], v[8 * q + 7], p.fmt);
+                            *reinterpret_cast<uint4 *>(dst_row + col0 + 8 * q) = o;
+                        }
+                    }
+                }
+            }
+        } else if (MODE == 0 && alive && warp * 32 < rows) {
             // wide rows: scatter from registers (two-float vector reductions); with several
             // 64-column blocks per row the single parking area would serialise the bulk reductions
             const int32_t *sc = s_scatter[b];
@@ -621,6 +655,7 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     MvmrTcParams p;
     p.weight = (const uint16_t *)a.weight, p.feat = (const uint16_t *)a.feat;
     p.gather = a.gather, p.scatter = a.scatter, p.seg = a.seg_offs, p.acc = a.acc;
+    p.out = (uint16_t *)a.out_rows;
     p.K = a.K, p.C = a.C, p.M = a.M, p.transpose = a.transpose, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
     p.ncols = pow2_cols((outw + 63) / 64 * 64);  // the epilogue reads blocks of up to 64 columns
     // Measured on B200: rows of exactly 64 floats leave fastest through one bulk reduction
@@ -629,6 +664,8 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     // with equal destinations in shared memory first was tried and cost more than it saved.
     bool bulk = outw == 64;
     if (const char *e = getenv("PCX_MVMR_SCATTER")) bulk = atoi(e) != 0;
+    const bool store = a.out_rows != nullptr;
+    if (store) bulk = false;
     const int kb = (inw + 63) / 64, wb = (a.M + 63) / 64;
     const size_t static_smem = 2176;  // index rings, barrier
     const size_t table = align_up((size_t)(a.K + 1) * 4, 16);
@@ -653,21 +690,25 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     size_t smem = rest + std::max((size_t)p.nbuf * kb * BLK_BYTES, p.alias ? (size_t)p.park_bytes : (size_t)0);
     smem = pad_for_tmem(smem, p.ncols);
     if (smem + static_smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "mvmr tensor kernel does not fit (smem %zu)", smem);
-    static int granted_mvmr[2][64] = {};   // per scatter mode and device
+    static int granted_mvmr[3][64] = {};   // per output mode and device
     int dev = 0;
     PCX_CUDA(cudaGetDevice(&dev));
-    if (int rc = bulk ? ensure_dynamic_smem(mvmr_tc_kernel<true>, smem, &granted_mvmr[1][dev & 63])
-                      : ensure_dynamic_smem(mvmr_tc_kernel<false>, smem, &granted_mvmr[0][dev & 63]))
+    if (int rc = store ? ensure_dynamic_smem(mvmr_tc_kernel<2>, smem, &granted_mvmr[2][dev & 63])
+                 : bulk ? ensure_dynamic_smem(mvmr_tc_kernel<1>, smem, &granted_mvmr[1][dev & 63])
+                        : ensure_dynamic_smem(mvmr_tc_kernel<0>, smem, &granted_mvmr[0][dev & 63]))
         return rc;
-    static int regs_mvmr[2] = {0, 0};
-    const int regs = bulk ? kernel_registers(mvmr_tc_kernel<true>, &regs_mvmr[1])
-                          : kernel_registers(mvmr_tc_kernel<false>, &regs_mvmr[0]);
+    static int regs_mvmr[3] = {0, 0, 0};
+    const int regs = store ? kernel_registers(mvmr_tc_kernel<2>, &regs_mvmr[2])
+                     : bulk ? kernel_registers(mvmr_tc_kernel<1>, &regs_mvmr[1])
+                            : kernel_registers(mvmr_tc_kernel<0>, &regs_mvmr[0]);
     const int occ = ctas_per_sm(smem + static_smem, p.ncols, regs);
     int64_t upper = a.T / CH + a.K + 1;
     int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
-    prof_begin(a.transpose ? "mvmr_tc_kernel(dgrad)" : "mvmr_tc_kernel(fwd)", stream);
-    if (bulk) mvmr_tc_kernel<true><<<(unsigned)grid, 128, smem, stream>>>(p);
-    else mvmr_tc_kernel<false><<<(unsigned)grid, 128, smem, stream>>>(p);
+    prof_begin(store ? (a.transpose ? "mvmr_tc_kernel(dgrad, store)" : "mvmr_tc_kernel(fwd, store)")
+                     : (a.transpose ? "mvmr_tc_kernel(dgrad)" : "mvmr_tc_kernel(fwd)"), stream);
+    if (store) mvmr_tc_kernel<2><<<(unsigned)grid, 128, smem, stream>>>(p);
+    else if (bulk) mvmr_tc_kernel<1><<<(unsigned)grid, 128, smem, stream>>>(p);
+    else mvmr_tc_kernel<0><<<(unsigned)grid, 128, smem, stream>>>(p);
     prof_end(stream);
     PCX_LAUNCH_CHECK();
     return PCX_OK;

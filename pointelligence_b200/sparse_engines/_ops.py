@@ -48,7 +48,7 @@ def _(a, a_idx, b, b_idx, seg_offs, o_idx, n_o, engine):
 def _mvmr_setup(ctx, inputs, output):
     weight, feat, gather, scatter, seg_offs, tap_idx, n_out, transpose, engine = inputs
     ctx.save_for_backward(weight, feat, gather, scatter, seg_offs, tap_idx)
-    ctx.transpose, ctx.engine = transpose, engine
+    ctx.transpose, ctx.engine = transpose, engine & 0xff   # a fan-in-1 promise holds for this direction only
 
 
 def _mvmr_backward(ctx, grad):

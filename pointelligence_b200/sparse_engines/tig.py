@@ -84,8 +84,10 @@ def tig_forward(weight, feat, index, mode="auto", input_precision=None, flat_cfg
     assert feat.size(0) == index.N_in, f"feat rows {feat.size(0)} != index.N_in {index.N_in}"
     out_dtype = feat.dtype
     w, feat = _match(w, feat)
-    out = mvmr_op(w, feat, index.flat_j, index.flat_i, index.flat_seg, None, index.N, False,
-                  current_engine())
+    engine = current_engine()
+    if index.exact_cover_out and index.T == index.N:
+        engine |= _cabi.ENGINE_FLAG_FAN_IN_ONE    # every output row has one triplet: rows are stored, not reduced
+    out = mvmr_op(w, feat, index.flat_j, index.flat_i, index.flat_seg, None, index.N, False, engine)
     return out.to(out_dtype)
 
 
@@ -101,8 +103,10 @@ def tig_grad_input(weight, grad_out, index, input_precision=None, flat_cfg=None)
         out = mvmr_op(w.flip(0), grad_out, index.flat_j, index.flat_i, index.flat_seg, None, index.N_in, True,
                       current_engine())
         return out.to(out_dtype)
-    out = mvmr_op(w, grad_out, index.flat_i, index.flat_j, index.flat_seg, None, index.N_in, True,
-                  current_engine())
+    engine = current_engine()
+    if index.exact_cover_in and index.T == index.N_in:
+        engine |= _cabi.ENGINE_FLAG_FAN_IN_ONE    # every input row has one triplet: its gradient row is stored
+    out = mvmr_op(w, grad_out, index.flat_i, index.flat_j, index.flat_seg, None, index.N_in, True, engine)
     return out.to(out_dtype)
 
 

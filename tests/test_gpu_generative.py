@@ -33,7 +33,14 @@ def test_generative_convolution_matches_dense_evaluation(dtype, generator):
     for name in ("points", "sample_inds", "sample_sizes", "i", "j", "k"):
         assert torch.equal(getattr(sites, name).cpu(), getattr(sites_cpu, name)), name
     x = torch.randn(n, cin, device="cuda").to(dtype).requires_grad_(True)
+    from pointelligence_b200 import _cabi
+
+    _cabi.profile_enable(True)
     y, m_out = conv(x, m, sites=sites)
+    labels = [name for name, _ in _cabi.profile_records()]
+    _cabi.profile_enable(False)
+    if dtype == torch.bfloat16:   # fan-in 1 (nothing merged): rows are stored by the tensor kernel, not reduced
+        assert ("mvmr_tc_kernel(fwd, store)" in labels) == sites.exact_cover_out, labels
     assert y.shape == (sites.n_out, cout) and m_out.parent is m and m_out.points.shape[0] == sites.n_out
     w = conv.weight.detach().double()[:, 0]
     i, j, k = sites.i.long(), sites.j.long(), sites.k.long()
@@ -48,3 +55,27 @@ def test_generative_convolution_matches_dense_evaluation(dtype, generator):
     assert (x.grad.double() - want_dx).abs().max() <= tol * max(1.0, float(want_dx.abs().max()))
     y2, _ = conv(x.detach(), m)                       # the generator runs inside forward as well
     assert torch.allclose(y2.float(), y.detach().float(), atol=tol, rtol=tol)
+
+
+def test_fan_in_one_flag_through_the_c_abi():
+    """``PCX_ENGINE_FLAG_FAN_IN_ONE``: a permutation rulebook (one triplet per output row) stored by
+    the tensor kernel equals the reduced result bit for bit; the flag with T != n_out is refused;
+    the CUDA-core engine ignores it."""
+    from pointelligence_b200 import _cabi
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    K, C, M, n = 8, 32, 48, 5000
+    w = torch.randn(K, 1, C, M, device=dev).to(torch.bfloat16)
+    x = torch.randn(n, C, device=dev).to(torch.bfloat16)
+    tap = torch.sort(torch.randint(0, K, (n,), device=dev)).values
+    seg = torch.searchsorted(tap, torch.arange(K + 1, device=dev)).to(torch.int64)
+    scatter = torch.randperm(n, device=dev).to(torch.int32)          # every output row exactly once
+    gather = torch.randint(0, n, (n,), device=dev).to(torch.int32)
+    reduced = _cabi.mvmr(w, x, gather, scatter, seg, None, n, False, _cabi.ENGINE_TENSOR)
+    stored = _cabi.mvmr(w, x, gather, scatter, seg, None, n, False, _cabi.ENGINE_TENSOR | _cabi.ENGINE_FLAG_FAN_IN_ONE)
+    assert torch.equal(stored, reduced)
+    core = _cabi.mvmr(w, x, gather, scatter, seg, None, n, False, _cabi.ENGINE_CUDA_CORE | _cabi.ENGINE_FLAG_FAN_IN_ONE)
+    assert torch.allclose(core.float(), reduced.float(), atol=2e-2, rtol=2e-2)
+    with pytest.raises(ValueError):
+        _cabi.mvmr(w, x, gather, scatter, seg, None, n + 1, False, _cabi.ENGINE_TENSOR | _cabi.ENGINE_FLAG_FAN_IN_ONE)

@@ -88,7 +88,14 @@ def test_patchify_convolution_and_unpatchify(dtype, cin):
     tol = 1e-4 if dtype == torch.float32 else 3e-2
     assert (y.detach().double() - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
     go = torch.randn_like(y)
+    from pointelligence_b200 import _cabi
+
+    _cabi.profile_enable(True)
     y.backward(go)
+    labels = [name for name, _ in _cabi.profile_records()]
+    _cabi.profile_enable(False)
+    if dtype == torch.bfloat16:   # one triplet per input point: the input gradient is stored row by row
+        assert m2.contract.exact_cover_in and "mvmr_tc_kernel(dgrad, store)" in labels, labels
     want_dx = torch.zeros(n, cin, dtype=torch.float64, device="cuda")
     want_dx.index_add_(0, m2.j, torch.einsum("tm,tcm->tc", go.double()[m2.i], w[m2.k]))
     assert (x.grad.double() - want_dx).abs().max() <= tol * max(1.0, float(want_dx.abs().max()))
