@@ -120,6 +120,55 @@ __global__ void ln_moments_kernel(const T *__restrict__ x, const int64_t *__rest
     }
 }
 
+// The same statistics with the block's rows held in registers (rows of at most 256 sixteen-byte
+// columns): a thread loads MOM_R rows of its column once, and both sweeps -- the sum, then the squares
+// centred on the block mean -- run over those registers.  A block covers MOM_R * (256 / columns) rows.
+constexpr int MOM_R = 4;
+
+template <typename T, int VN>
+__global__ void __launch_bounds__(LN_THREADS) ln_moments_reg_kernel(const T *__restrict__ x, const int64_t *__restrict__ offsets,
+                                                                    Moments *rec, int64_t N, int64_t S, int C, int mom_rows) {
+    __shared__ float scratch[LN_THREADS / 32];
+    const RowLayout L(C, VN);   // one pass: vc_total <= blockDim
+    const int64_t row0 = (int64_t)blockIdx.x * mom_rows, row1 = min(N, row0 + mom_rows);
+    const int64_t s_first = segment_of_row(offsets, S, row0), s_last = segment_of_row(offsets, S, row1 - 1);
+    float v[MOM_R][VN];
+    int64_t rows[MOM_R];
+#pragma unroll
+    for (int k = 0; k < MOM_R; ++k) {
+        rows[k] = row0 + L.lane + (int64_t)k * L.lanes;
+        if (L.lane < L.lanes && rows[k] < row1) {
+            load_vec<T, VN>(x + rows[k] * C + (int64_t)L.vc * VN, v[k]);
+        } else {
+            rows[k] = -1;
+#pragma unroll
+            for (int i = 0; i < VN; ++i) v[k][i] = 0.f;
+        }
+    }
+    for (int64_t s = s_first; s <= s_last; ++s) {
+        const int64_t lo = max(row0, offsets[s]), hi = min(row1, offsets[s + 1]);
+        if (hi <= lo) continue;   // an empty sample inside the block (same decision in every thread)
+        float mu = 0.f, result[2];
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < MOM_R; ++k) {
+                if (rows[k] >= lo && rows[k] < hi) {
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) {
+                        const float d = v[k][i] - mu;
+                        acc += pass ? d * d : d;
+                    }
+                }
+            }
+            result[pass] = block_sum(acc, scratch);
+            if (pass == 0) mu = result[0] / ((float)(hi - lo) * (float)C);
+        }
+        if (threadIdx.x == 0) rec[blockIdx.x + s] = Moments{(float)(hi - lo) * (float)C, mu, result[1], 0.f};
+    }
+}
+
 constexpr int COMBINE_THREADS = 256;
 
 __device__ __forceinline__ double block_sum_f64(double v, double *scratch) {
@@ -136,7 +185,7 @@ __device__ __forceinline__ double block_sum_f64(double v, double *scratch) {
 // one block per sample: the sample's pieces are spread over the threads, the sums are folded in fp64
 __global__ void __launch_bounds__(COMBINE_THREADS) ln_combine_kernel(const Moments *__restrict__ rec,
                                                                      const int64_t *__restrict__ offsets, float *mean,
-                                                                     float *rstd, int64_t S, float eps) {
+                                                                     float *rstd, int64_t S, float eps, int mom_rows) {
     __shared__ double scratch[COMBINE_THREADS / 32];
     const int64_t s = blockIdx.x;
     const int64_t lo = offsets[s], hi = offsets[s + 1];
@@ -144,7 +193,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS) ln_combine_kernel(const Momen
         if (threadIdx.x == 0) mean[s] = 0.f, rstd[s] = 1.f / sqrtf(eps);
         return;
     }
-    const int64_t b0 = lo / LN_ROWS, b1 = (hi - 1) / LN_ROWS;
+    const int64_t b0 = lo / mom_rows, b1 = (hi - 1) / mom_rows;
     double n = 0.0, sum = 0.0;
     for (int64_t b = b0 + threadIdx.x; b <= b1; b += COMBINE_THREADS) {
         const Moments m = rec[b + s];
@@ -604,7 +653,8 @@ int ln_offsets(const int64_t *d_lengths, int64_t S, int64_t N, const LnWs &w, cu
 }
 
 // (block, sample) pieces of N rows in S samples: record b + s, b < blocks, s < S
-int64_t ln_pieces(int64_t N, int64_t S) { return (N + LN_ROWS - 1) / LN_ROWS + S; }
+// an upper bound for every block height the statistics pass may choose (at least MOM_R rows per block)
+int64_t ln_pieces(int64_t N, int64_t S) { return (N + MOM_R - 1) / MOM_R + S; }
 
 bool ln_sizes_ok(int64_t N, int64_t S, int C, int dtype) {
     return N >= 0 && S > 0 && S <= INT32_MAX && C > 0 && (dtype == PCX_F32 || dtype == PCX_F16 || dtype == PCX_BF16);
@@ -643,11 +693,19 @@ int pcx_ragged_layer_norm(const void *d_x, const int64_t *d_lengths, const float
     if (int rc = ln_offsets(d_lengths, S, N, w, stream)) return rc;
     const unsigned grid = (unsigned)((N + LN_ROWS - 1) / LN_ROWS);
     const bool vec = vec_ok(C, dtype, {d_x, d_y, d_residual});
+    int mom_rows = LN_ROWS;
+    const int vcols = C / (16 / (int)elem_size(dtype));   // sixteen-byte columns of a row (when vectorised)
+    if (vec && vcols <= LN_THREADS) mom_rows = MOM_R * (LN_THREADS / vcols);   // rows held in registers
     if (N > 0) {
-        PCX_LN_DISPATCH(dtype, vec, (ln_moments_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, w.rec, N, S, C)));
+        if (mom_rows != LN_ROWS) {
+            const unsigned mgrid = (unsigned)((N + mom_rows - 1) / mom_rows);
+            PCX_LN_DISPATCH(dtype, true, (ln_moments_reg_kernel<T, VN><<<mgrid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, w.rec, N, S, C, mom_rows)));
+        } else {
+            PCX_LN_DISPATCH(dtype, vec, (ln_moments_kernel<T, VN><<<grid, LN_THREADS, 0, stream>>>((const T *)d_x, w.offsets, w.rec, N, S, C)));
+        }
         PCX_LAUNCH_CHECK();
     }
-    ln_combine_kernel<<<(unsigned)S, COMBINE_THREADS, 0, stream>>>(w.rec, w.offsets, d_mean, d_rstd, S, (float)eps);
+    ln_combine_kernel<<<(unsigned)S, COMBINE_THREADS, 0, stream>>>(w.rec, w.offsets, d_mean, d_rstd, S, (float)eps, mom_rows);
     PCX_LAUNCH_CHECK();
     if (N > 0) {
         prof_begin("ln_apply_kernel", stream);
