@@ -63,6 +63,35 @@ WORKLOAD = ("indoor150k_c64_bf16: PointConv3d fwd+dgrad+wgrad, 150000-point synt
             "R=5cm, 27 taps, C_in=C_out=64 bf16, fp32 accumulate")
 
 
+def bind_to_gpu_numa_node(local_rank):
+    """Keep this rank's threads -- and with them the pinned host buffers they allocate and touch -- on the
+    NUMA node of its GPU when the box has more than one node.  Returns what was done, for the JSON line."""
+    import glob
+
+    import torch
+
+    info = {"nodes": len(glob.glob("/sys/devices/system/node/node[0-9]*")), "bound_node": None}
+    try:
+        prop = torch.cuda.get_device_properties(local_rank)
+        bus = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        info["gpu_node"] = node
+        if info["nodes"] > 1 and node >= 0:
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+                cpus = set()
+                for part in f.read().strip().split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            allowed = cpus & os.sched_getaffinity(0)
+            if allowed:
+                os.sched_setaffinity(0, allowed)
+                info["bound_node"] = node
+    except (OSError, ValueError, AttributeError) as exc:   # no sysfs entry, no such property: leave the affinity alone
+        info["note"] = type(exc).__name__
+    return info
+
+
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -251,6 +280,7 @@ def run_ours(args, rank, local_rank, world):
         raise RuntimeError("bench.py needs a CUDA device (the operators have no CPU fallback)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa = bind_to_gpu_numa_node(local_rank)
     if world > 1:
         # a short collective timeout: ranks that fall out of step fail within minutes instead of hanging
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
@@ -534,7 +564,7 @@ def run_ours(args, rank, local_rank, world):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "points_per_rank": n, "triplets_rank0": T,
                        "triplets_per_point": T / n, "l2": "flushed between steps (256 MiB write)",
-                       "collective": "all-reduce of dW per step" if world > 1 else "none",
+                       "collective": "all-reduce of dW per step" if world > 1 else "none", "numa_rank0": numa,
                        "mvmr_engine": args.engine,
                        "geometry_ms": geometry_ms},
             "tflops": 6.0 * T_all * C * M / (per_step_ms * 1e-3) / 1e12,
