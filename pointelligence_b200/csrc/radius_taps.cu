@@ -48,6 +48,7 @@ struct TapsWs {
     float4 *sorted_pts;     // xyz + original index (bit pattern) in bucket order
     int2 *table;            // bucket -> [start, end) in the sorted order; (0,0) = empty
     uint4 *lanes;           // Q x 8: candidate run [start, end) and the accept mask of its first 64 points
+    unsigned long long *lanes_more;   // Q x 8: accept mask of points 64 .. 127 of a run longer than 64
     uint32_t *lane_counts;  // Q x 8 accepted pairs per (query, cell)
     uint32_t *block_hist;   // [tap][block] accepted pairs; exclusive prefix over blocks after the scan
     unsigned long long *tap_total;  // k3
@@ -83,6 +84,7 @@ size_t carve_taps(void *ws, int64_t P, int64_t Q, int k3, TapsWs *out) {
     w.sorted_pts = c.take<float4>(P);
     w.table = c.take<int2>(w.buckets);
     w.lanes = c.take<uint4>(Q * 8);
+    w.lanes_more = c.take<unsigned long long>(Q * 8);
     w.lane_counts = c.take<uint32_t>(Q * 8);
     w.block_hist = c.take<uint32_t>(w.nblocks * k3);
     w.cub_bytes = 0;
@@ -127,6 +129,7 @@ struct TapArgs {
     const float4 *sorted_pts;
     const int2 *table;
     uint4 *lanes;
+    unsigned long long *lanes_more;
     uint32_t *lane_counts, *block_hist;
     int64_t *num_neighbors;
     const int64_t *seg, *ctrl;
@@ -157,16 +160,18 @@ __device__ __forceinline__ bool accept_fast(const TapArgs &a, float qx, float qy
 // time: first the predicate alone over the chunk (two loads in flight, no divergent work), giving
 // a 64-bit mask, then hit(tap, j) for the set bits in run order.  The mask of the first chunk is
 // stored by the count pass (after the sample check) and read back by the fill pass, which then
-// touches accepted points only; later chunks of a long run are evaluated again.
+// touches accepted points only; later chunks of a long run are evaluated again.  `masks` holds the
+// masks of the first two chunks (128 candidates), which covers the runs of dense scenes.
 template <bool STORED, typename Hit>
 __device__ __forceinline__ void walk_run(const TapArgs &a, int2 r, float qx, float qy, float qz, int b,
-                                         unsigned long long *first_mask, Hit hit) {
+                                         unsigned long long (&masks)[2], Hit hit) {
     for (int s0 = r.x; s0 < r.y; s0 += 64) {
-        const bool first = s0 == r.x;
+        const int chunk = (s0 - r.x) >> 6;
+        const bool first = chunk < 2;   // a chunk whose mask is kept
         const int len = min(64, r.y - s0);
         unsigned long long m = 0;
         if (STORED && first) {
-            m = *first_mask;
+            m = masks[chunk & 1];
         } else {
             uint32_t half[2] = {0u, 0u};
 #pragma unroll
@@ -196,7 +201,7 @@ __device__ __forceinline__ void walk_run(const TapArgs &a, int2 r, float qx, flo
             }
             hit(tap_of_fast(qx, qy, qz, p, a.g32, a.inv_g, a.K), j);
         }
-        if (!STORED && first) *first_mask = keep;
+        if (!STORED && first) masks[chunk & 1] = keep;
     }
 }
 
@@ -214,12 +219,13 @@ __global__ void __launch_bounds__(THREADS) taps_count_kernel(TapArgs a) {
         const int cy = corner_of(qy, a.r32, a.inv) + ((c >> 1) & 1);
         const int cz = corner_of(qz, a.r32, a.inv) + (c & 1);
         const int2 r = a.table[cell_bucket(b, cx, cy, cz, a.mask)];
-        unsigned long long first_mask = 0;
-        walk_run<false>(a, r, qx, qy, qz, b, &first_mask, [&](int tap, int) {
+        unsigned long long masks[2] = {0ULL, 0ULL};
+        walk_run<false>(a, r, qx, qy, qz, b, masks, [&](int tap, int) {
             ++n;
             atomicAdd(&s_hist[tap], 1u);
         });
-        a.lanes[q * 8 + c] = make_uint4((uint32_t)r.x, (uint32_t)r.y, (uint32_t)first_mask, (uint32_t)(first_mask >> 32));
+        a.lanes[q * 8 + c] = make_uint4((uint32_t)r.x, (uint32_t)r.y, (uint32_t)masks[0], (uint32_t)(masks[0] >> 32));
+        if (r.y - r.x > 64) a.lanes_more[q * 8 + c] = masks[1];
         a.lane_counts[q * 8 + c] = n;
     }
     uint32_t tot = n;
@@ -305,13 +311,14 @@ __global__ void __launch_bounds__(THREADS) taps_fill_kernel(TapArgs a) {
     float qx = 0.f, qy = 0.f, qz = 0.f;
     int b = 0;
     int2 r = make_int2(0, 0);
-    unsigned long long first_mask = 0;
+    unsigned long long masks[2] = {0ULL, 0ULL};
     if (n) {
         qx = a.queries[3 * q], qy = a.queries[3 * q + 1], qz = a.queries[3 * q + 2];
         b = a.query_sample ? a.query_sample[q] : 0;
         const uint4 l = a.lanes[q * 8 + c];
         r = make_int2((int)l.x, (int)l.y);
-        first_mask = (unsigned long long)l.z | ((unsigned long long)l.w << 32);
+        masks[0] = (unsigned long long)l.z | ((unsigned long long)l.w << 32);
+        if (r.y - r.x > 64) masks[1] = a.lanes_more[q * 8 + c];
     }
     __syncthreads();
     for (uint32_t lo = 0; lo < block_total; lo += REC_MAX) {
@@ -320,7 +327,7 @@ __global__ void __launch_bounds__(THREADS) taps_fill_kernel(TapArgs a) {
         for (int t = threadIdx.x; t < groups * kpad; t += THREADS) s_gcnt[t] = 0;
         if (n && my_off < hi && my_off + n > lo) {
             uint32_t pos = my_off;
-            walk_run<true>(a, r, qx, qy, qz, b, &first_mask, [&](int tap, int j) {
+            walk_run<true>(a, r, qx, qy, qz, b, masks, [&](int tap, int j) {
                 if (pos >= lo && pos < hi)
                     s_rec[pos - lo] = ((unsigned long long)tap << 40) | ((unsigned long long)ql << 32) | (uint32_t)j;
                 ++pos;
@@ -380,7 +387,7 @@ TapArgs make_args(const TapsWs &w, const float *queries, const int32_t *point_sa
                   int64_t Q, double radius, int distance_type, int kernel_size, double grid) {
     TapArgs a = {};
     a.queries = queries, a.query_sample = query_sample, a.point_sample = point_sample;
-    a.sorted_pts = w.sorted_pts, a.table = w.table, a.lanes = w.lanes;
+    a.sorted_pts = w.sorted_pts, a.table = w.table, a.lanes = w.lanes, a.lanes_more = w.lanes_more;
     a.lane_counts = w.lane_counts, a.block_hist = w.block_hist, a.seg = w.seg, a.ctrl = w.ctrl, a.ctrl_rw = w.ctrl;
     a.Q = Q, a.nblocks = w.nblocks, a.mask = (uint32_t)(w.buckets - 1);
     a.r32 = (float)radius, a.inv = (float)(1.0 / (2.0 * radius)), a.g32 = (float)grid;
