@@ -50,7 +50,8 @@ using namespace tc;
 // kept in registers and reloaded only when the chunk index leaves the tap.
 // The cumulative chunk table lives in shared memory (built by every CTA from
 // the segment offsets), so no separate kernel and no global table are needed.
-struct ChunkCursor {
+template <int CHR>
+struct ChunkCursorT {
     int tap;
     int cum_lo, cum_hi;
     int64_t seg_lo, seg_hi;
@@ -72,24 +73,26 @@ struct ChunkCursor {
         while (tap + 1 < K && cum[tap + 1] <= chunk) ++tap;
         load(cum, seg);
     }
-    __device__ __forceinline__ int64_t first(int chunk) const { return seg_lo + (int64_t)(chunk - cum_lo) * CH; }
+    __device__ __forceinline__ int64_t first(int chunk) const { return seg_lo + (int64_t)(chunk - cum_lo) * CHR; }
     __device__ __forceinline__ int rows(int chunk) const {
         int64_t left = seg_hi - first(chunk);
-        return (int)(left < CH ? left : CH);
+        return (int)(left < CHR ? left : CHR);
     }
     __device__ __forceinline__ bool last_of_tap(int chunk) const { return chunk + 1 >= cum_hi; }
 };
+using ChunkCursor = ChunkCursorT<CH>;
 
 constexpr int MAX_TAPS_SMEM = 1024;  // taps whose chunk table fits the shared-memory copy
 
-// cum[k] = chunks of CH triplets in the taps before k; all threads of the CTA call this.
+// cum[k] = chunks of CHR triplets in the taps before k; all threads of the CTA call this.
+template <int CHR = CH>
 __device__ __forceinline__ void build_chunk_table(const int64_t *__restrict__ seg, int K, int32_t *cum,
                                                   int32_t *warp_sums) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     int32_t carry = 0;
     for (int base = 0; base < K; base += blockDim.x) {
         int k = base + tid;
-        int32_t v = k < K ? (int32_t)((seg[k + 1] - seg[k] + CH - 1) / CH) : 0;
+        int32_t v = k < K ? (int32_t)((seg[k + 1] - seg[k] + CHR - 1) / CHR) : 0;
         int32_t inc = v;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -115,16 +118,17 @@ __device__ __forceinline__ void build_chunk_table(const int64_t *__restrict__ se
 // indices were staged in shared memory beforehand so that the copy loop issues
 // cp.async back to back.  Rows past `rows` are zero-filled when ZERO_TAIL
 // (needed when the row index is the contraction index), untouched otherwise.
-template <bool ZERO_TAIL>
+template <bool ZERO_TAIL, int CHR = CH>
 __device__ __forceinline__ void gather_tile(uint32_t tile, const uint16_t *__restrict__ src,
                                             const int32_t *s_idx, int rows, int width, int tid, int nthreads) {
     const int cpr = width >> 3;  // 16-byte pieces per row
-    const int rmax = ZERO_TAIL ? CH : rows;
+    constexpr uint32_t BLK = CHR * 128;   // one 64-channel block of the tile
+    const int rmax = ZERO_TAIL ? CHR : rows;
     if ((cpr & (cpr - 1)) == 0) {
         // power-of-two row length: a thread keeps its 16-byte column and walks down the rows
         const int sh = __ffs(cpr) - 1;
         const int ch = tid & (cpr - 1), rpp = nthreads >> sh;
-        const uint32_t dcol = tile + (uint32_t)(ch >> 3) * BLK_BYTES;
+        const uint32_t dcol = tile + (uint32_t)(ch >> 3) * BLK;
         const uint16_t *scol = src + ch * 8;
 #pragma unroll 4
         for (int r = tid >> sh; r < rmax; r += rpp) {
@@ -137,9 +141,11 @@ __device__ __forceinline__ void gather_tile(uint32_t tile, const uint16_t *__res
         }
         return;
     }
+    // (keeping a thread on one column with a single division up front was tried for these row
+    // lengths and for the loop above: 96 channels unchanged, 128 and 256 channels 13 % slower)
     for (int e = tid; e < rmax * cpr; e += nthreads) {
         int r = e / cpr, ch = e - r * cpr;
-        uint32_t dst = tile + (uint32_t)(ch >> 3) * BLK_BYTES + (uint32_t)r * 128 + (uint32_t)(((ch & 7) ^ (r & 7)) << 4);
+        uint32_t dst = tile + (uint32_t)(ch >> 3) * BLK + (uint32_t)r * 128 + (uint32_t)(((ch & 7) ^ (r & 7)) << 4);
         if (r < rows) {
             cp_async16(dst, src + (int64_t)s_idx[r] * width + ch * 8);
         } else if (ZERO_TAIL) {
@@ -427,33 +433,44 @@ struct VvorTcParams {
 
 constexpr int MAX_STAGES = 4;
 
-// Ring of `stages` operand buffers: the gathers of the next stages-1 chunks are
-// in flight while the tensor core contracts the current one (a single stage,
-// for the widest channel counts, degenerates to gather-then-multiply).
-__global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
+// Chunks of CHR triplets (the contraction length of one group of MMAs) through a ring of
+// `stages` operand buffers.  NT threads.
+//  * one stage, 128 threads: gather, multiply, gather ...; several CTAs per SM overlap each
+//    other (narrow operands, where three and more CTAs fit).
+//  * wide operands leave room for one or two CTAs per SM: more warps issue the copies of a
+//    chunk, and with two or more stages the multiply of chunk n is issued BEFORE the CTA waits
+//    for the multiply of chunk n-1 and refills its buffer, so the tensor core always has the
+//    next group queued and the copies of the following chunks are in flight meanwhile.
+template <int NT, int CHR, bool RING>
+__global__ void __launch_bounds__(NT) vvor_tc_kernel(VvorTcParams p) {
+    constexpr uint32_t BLK = CHR * 128;   // one 64-channel block of a CHR-row tile
+    using Cursor = ChunkCursorT<CHR>;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t s_bar;
+    __shared__ uint64_t s_bar[2];
     __shared__ uint32_t s_tmem;
-    __shared__ int32_t s_warp_sums[4];
+    __shared__ int32_t s_warp_sums[NT / 32];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int row_tiles = (p.Ma + 127) >> 7;
     const int ablk = (p.Ma + 63) >> 6;  // blocks actually filled; an odd count borrows the next block as padding
     const int bblk = (p.Cb + 63) >> 6;
-    const uint32_t buf_bytes = (uint32_t)(ablk + bblk) * BLK_BYTES;
-    const int NS = p.stages;
+    const uint32_t buf_bytes = (uint32_t)(ablk + bblk) * BLK;
+    const int NS = RING ? p.stages : 1;   // RING: two to four stages
     // behind the operand stages: the index rings of both operands, then the chunk table
-    int32_t(*s_ia)[CH] = reinterpret_cast<int32_t(*)[CH]>(smem_raw + (base - smem_u32(smem_raw)) + (size_t)NS * buf_bytes);
-    int32_t(*s_ib)[CH] = s_ia + NS;
-    int32_t *s_cum = reinterpret_cast<int32_t *>(s_ib + NS);
-    const uint32_t bar = smem_u32(&s_bar);
+    // (the ring keeps the index rows of 2 NS chunks: they are fetched NS-1 iterations before the copies that use them)
+    const int IR = RING ? 2 * NS : 1;
+    int32_t(*s_ia)[CHR] = reinterpret_cast<int32_t(*)[CHR]>(smem_raw + (base - smem_u32(smem_raw)) + (size_t)NS * buf_bytes);
+    int32_t(*s_ib)[CHR] = s_ia + IR;
+    int32_t *s_cum = reinterpret_cast<int32_t *>(s_ib + IR);
+    const uint32_t bar0 = smem_u32(&s_bar[0]), bar1 = smem_u32(&s_bar[1]);
 
     if (tid == 0) {
-        mbar_init(bar, 1);
+        mbar_init(bar0, 1);
+        mbar_init(bar1, 1);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(&s_tmem), p.ncols);
-    build_chunk_table(p.seg, p.n_o, s_cum, s_warp_sums);
+    build_chunk_table<CHR>(p.seg, p.n_o, s_cum, s_warp_sums);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -463,116 +480,219 @@ __global__ void __launch_bounds__(128) vvor_tc_kernel(VvorTcParams p) {
     const int per = (total + gridDim.x - 1) / gridDim.x;
     const int lo = blockIdx.x * per, hi = min(total, lo + per);
     const uint32_t idesc = instr_desc(p.fmt, 128, p.Cb, 1, 1);
-    uint32_t phase = 0;
     bool alive = true;
     bool fresh = true;  // next MMA starts a new accumulation
 
-    ChunkCursor cur, pre;  // chunk being multiplied; chunk whose indices are being fetched
+    Cursor cur, pre;  // chunk being multiplied; chunk whose indices are being fetched
     int pre_a = 0, pre_b = 0;
-    auto issue_gather = [&](const ChunkCursor &cc, int chunk, int slot, bool from_regs) {
+    auto stage_indices = [&](const Cursor &cc, int chunk, int slot, bool from_regs) {
         const int rows = cc.rows(chunk);
         if (tid < rows) {
             s_ia[slot][tid] = from_regs ? pre_a : p.a_idx[cc.first(chunk) + tid];
             s_ib[slot][tid] = from_regs ? pre_b : p.b_idx[cc.first(chunk) + tid];
         }
+        return rows;
+    };
+    auto copy_rows = [&](int slot, int rows) {
         __syncthreads();
         const uint32_t a_tile = base + (uint32_t)slot * buf_bytes;
-        gather_tile<true>(a_tile, p.a, s_ia[slot], rows, p.Ma, tid, 128);
-        gather_tile<true>(a_tile + (uint32_t)ablk * BLK_BYTES, p.b, s_ib[slot], rows, p.Cb, tid, 128);
+        gather_tile<true, CHR>(a_tile, p.a, s_ia[slot], rows, p.Ma, tid, NT);
+        gather_tile<true, CHR>(a_tile + (uint32_t)ablk * BLK, p.b, s_ib[slot], rows, p.Cb, tid, NT);
     };
-    auto flush_tap = [&](int o) {
-        float *dst_o = p.acc + (int64_t)o * p.Ma * p.Cb;
-        for (int rt = 0; rt < row_tiles; ++rt) {
-#pragma unroll 1
-            for (int half = 0; half < 2; ++half) {
-                const int m0 = rt * 128 + warp * 32 + half * 16;
-                if (m0 >= p.Ma) break;
-                const int ma = m0 + (lane >> 2), mb = ma + 8;
-                const int64_t da = ma < p.Ma ? ma : -1, db = mb < p.Ma ? mb : -1;
-                for (int c0 = 0; c0 < p.Cb; c0 += 64) {
-                    float v[32];
-                    tmem_ld_16x64(tmem + ((uint32_t)(warp * 32 + half * 16) << 16) + (uint32_t)(rt * p.Cb + c0), v);
-                    scatter_block(dst_o, da, db, p.Cb, c0, lane, v);
-                }
+    auto issue_gather = [&](const Cursor &cc, int chunk, int slot, bool from_regs) {
+        copy_rows(slot, stage_indices(cc, chunk, slot, from_regs));
+    };
+    auto prefetch_indices = [&](int chunk) {
+        if (chunk < hi) {
+            pre.advance(s_cum, p.seg, p.n_o, chunk);
+            if (tid < pre.rows(chunk)) {
+                pre_a = p.a_idx[pre.first(chunk) + tid];
+                pre_b = p.b_idx[pre.first(chunk) + tid];
             }
         }
     };
-
-    if (lo < hi) {
-        cur.seek(s_cum, p.seg, p.n_o, lo);
-        pre = cur;
-        for (int s = 0; s < NS - 1; ++s) {  // prologue: chunks lo .. lo+NS-2
-            if (lo + s < hi) {
-                pre.advance(s_cum, p.seg, p.n_o, lo + s);
-                issue_gather(pre, lo + s, s, false);
-            }
-            cp_async_commit();
-        }
-        if (lo + NS - 1 < hi) {
-            pre.advance(s_cum, p.seg, p.n_o, lo + NS - 1);
-            if (tid < pre.rows(lo + NS - 1)) {
-                pre_a = p.a_idx[pre.first(lo + NS - 1) + tid];
-                pre_b = p.b_idx[pre.first(lo + NS - 1) + tid];
-            }
-        }
-    }
-    int pending_tap = -1;  // tap whose last MMA has been issued but whose sums are still in TMEM
-
-    for (int chunk = lo; chunk < hi && alive; ++chunk) {
-        const int n = chunk - lo;
-        // the MMA of the previous chunk must be done before its buffer is refilled
-        if (n > 0) {
-            alive = __syncthreads_and(mbar_wait(bar, phase, 2u, &g_device_status));
-            phase ^= 1u;
-            tc_fence_after();
-            if (alive && pending_tap >= 0) {
-                flush_tap(pending_tap);
-                pending_tap = -1;
-                fresh = true;
-                tc_fence_before();
-            }
-        }
-        const int refill = chunk + NS - 1;
-        if (refill < hi) issue_gather(pre, refill, (n + NS - 1) % NS, true);
-        cp_async_commit();
-        if (refill + 1 < hi) {
-            pre.advance(s_cum, p.seg, p.n_o, refill + 1);
-            if (tid < pre.rows(refill + 1)) {
-                pre_a = p.a_idx[pre.first(refill + 1) + tid];
-                pre_b = p.b_idx[pre.first(refill + 1) + tid];
-            }
-        }
-        // chunk `chunk` has landed once at most NS-1 newer groups are pending
+    auto wait_landed = [&]() {  // the oldest chunk in the ring has landed once NS-1 newer groups are pending
         if (NS == 1) cp_async_wait<0>();
         else if (NS == 2) cp_async_wait<1>();
         else if (NS == 3) cp_async_wait<2>();
         else cp_async_wait<3>();
         fence_async_smem();
         __syncthreads();
-
-        cur.advance(s_cum, p.seg, p.n_o, chunk);
-        const int rows = cur.rows(chunk);
-        if (tid == 0 && alive) {
-            tc_fence_after();
-            const uint32_t a_tile = base + (uint32_t)(n % NS) * buf_bytes;
-            const uint32_t b_tile = a_tile + (uint32_t)ablk * BLK_BYTES;
-            const int ksteps = (rows + 15) >> 4;
-            for (int rt = 0; rt < row_tiles; ++rt) {
-                for (int s = 0; s < ksteps; ++s) {
-                    uint64_t ad = smem_desc(a_tile + (uint32_t)(rt * 2) * BLK_BYTES + (uint32_t)s * 2048, BLK_BYTES, 1024);
-                    uint64_t bd = smem_desc(b_tile + (uint32_t)s * 2048, BLK_BYTES, 1024);
-                    tc_mma(tmem + (uint32_t)(rt * p.Cb), ad, bd, idesc, (fresh && s == 0) ? 0u : 1u);
+    };
+    auto multiply = [&](int slot, int rows, uint32_t bar) {  // one thread
+        tc_fence_after();
+        const uint32_t a_tile = base + (uint32_t)slot * buf_bytes;
+        const uint32_t b_tile = a_tile + (uint32_t)ablk * BLK;
+        const int ksteps = (rows + 15) >> 4;
+        for (int rt = 0; rt < row_tiles; ++rt) {
+            for (int s = 0; s < ksteps; ++s) {
+                uint64_t ad = smem_desc(a_tile + (uint32_t)(rt * 2) * BLK + (uint32_t)s * 2048, BLK, 1024);
+                uint64_t bd = smem_desc(b_tile + (uint32_t)s * 2048, BLK, 1024);
+                tc_mma(tmem + (uint32_t)(rt * p.Cb), ad, bd, idesc, (fresh && s == 0) ? 0u : 1u);
+            }
+        }
+        tc_commit(bar);
+    };
+    // a warp reads the 32 TMEM lanes of its quarter (warp % 4); the warps of a quarter share its columns
+    const int quarter = warp & 3, col_part = warp >> 2;
+    auto flush_tap = [&](int o) {
+        float *dst_o = p.acc + (int64_t)o * p.Ma * p.Cb;
+        for (int rt = 0; rt < row_tiles; ++rt) {
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                const int m0 = rt * 128 + quarter * 32 + half * 16;
+                if (m0 >= p.Ma) break;
+                const int ma = m0 + (lane >> 2), mb = ma + 8;
+                const int64_t da = ma < p.Ma ? ma : -1, db = mb < p.Ma ? mb : -1;
+                for (int c0 = col_part * 64; c0 < p.Cb; c0 += (NT / 128) * 64) {
+                    float v[32];
+                    tmem_ld_16x64(tmem + ((uint32_t)(quarter * 32 + half * 16) << 16) + (uint32_t)(rt * p.Cb + c0), v);
+                    scatter_block(dst_o, da, db, p.Cb, c0, lane, v);
                 }
             }
-            tc_commit(bar);
         }
-        fresh = false;
-        if ((chunk + 1 == hi) || cur.last_of_tap(chunk)) pending_tap = cur.tap;
-    }
-    if (lo < hi && alive) {
-        alive = __syncthreads_and(mbar_wait(bar, phase, 2u, &g_device_status));
-        tc_fence_after();
-        if (alive && pending_tap >= 0) flush_tap(pending_tap);
+    };
+    int pending_tap = -1;  // tap whose last MMA has been issued but whose sums are still in TMEM
+
+    if (!RING) {
+        uint32_t phase = 0;
+        if (lo < hi) {
+            cur.seek(s_cum, p.seg, p.n_o, lo);
+            pre = cur;
+            prefetch_indices(lo);
+        }
+        for (int chunk = lo; chunk < hi && alive; ++chunk) {
+            // the MMA of the previous chunk must be done before the buffer is refilled
+            if (chunk > lo) {
+                alive = __syncthreads_and(mbar_wait(bar0, phase, 2u, &g_device_status));
+                phase ^= 1u;
+                tc_fence_after();
+                if (alive && pending_tap >= 0) {
+                    flush_tap(pending_tap);
+                    pending_tap = -1;
+                    fresh = true;
+                    tc_fence_before();
+                }
+            }
+            issue_gather(pre, chunk, 0, true);
+            cp_async_commit();
+            prefetch_indices(chunk + 1);
+            wait_landed();
+            cur.advance(s_cum, p.seg, p.n_o, chunk);
+            if (tid == 0 && alive) multiply(0, cur.rows(chunk), bar0);
+            fresh = false;
+            if ((chunk + 1 == hi) || cur.last_of_tap(chunk)) pending_tap = cur.tap;
+        }
+        if (lo < hi && alive) {
+            alive = __syncthreads_and(mbar_wait(bar0, phase, 2u, &g_device_status));
+            tc_fence_after();
+            if (alive && pending_tap >= 0) flush_tap(pending_tap);
+        }
+    } else {
+        // Warp 0 issues the multiplies; warps 1 .. NT/32-1 copy.  One block barrier per iteration
+        // (the copies of all threads must be visible before the multiply reads the stage); the
+        // completion of a multiply is observed by every thread on the mbarrier itself.
+        constexpr int NCOPY = NT - 32;
+        const int ctid = tid - 32;           // copy thread number (negative: warp 0)
+        uint32_t phase0 = 0u, phase1 = 0u;   // parities of the two barriers (multiplies of even / odd chunks)
+        auto wait_multiply_all = [&](int n) {    // with a block barrier: every thread knows the outcome
+            const bool odd = n & 1;
+            const bool ok = __syncthreads_and(mbar_wait(odd ? bar1 : bar0, odd ? phase1 : phase0, 2u, &g_device_status));
+            if (odd) phase1 ^= 1u; else phase0 ^= 1u;
+            return ok;
+        };
+        auto wait_multiply_self = [&](int n) {   // this thread only
+            const bool odd = n & 1;
+            const bool ok = mbar_wait(odd ? bar1 : bar0, odd ? phase1 : phase0, 2u, &g_device_status);
+            if (odd) phase1 ^= 1u; else phase0 ^= 1u;
+            return ok;
+        };
+        // Index rows of chunk `chunk` into slot `islot` of the index ring, as 4-byte asynchronous
+        // copies in the caller's copy group: a plain load would come back behind the tens of KB of
+        // row copies already queued in the SM's memory pipeline.
+        auto fetch_indices = [&](int chunk, int islot) {
+            if (chunk < hi) {
+                pre.advance(s_cum, p.seg, p.n_o, chunk);
+                if (ctid >= 0 && ctid < pre.rows(chunk)) {
+                    const int64_t t = pre.first(chunk) + ctid;
+                    cp_async4(smem_u32(&s_ia[islot][ctid]), p.a_idx + t);
+                    cp_async4(smem_u32(&s_ib[islot][ctid]), p.b_idx + t);
+                }
+            }
+        };
+        Cursor fill;   // chunk whose rows are being copied
+        auto copy_chunk = [&](int chunk, int slot, int islot) {   // its index rows have landed
+            fill.advance(s_cum, p.seg, p.n_o, chunk);
+            const int rows = fill.rows(chunk);
+            if (ctid >= 0) {
+                const uint32_t a_tile = base + (uint32_t)slot * buf_bytes;
+                gather_tile<true, CHR>(a_tile, p.a, s_ia[islot], rows, p.Ma, ctid, NCOPY);
+                gather_tile<true, CHR>(a_tile + (uint32_t)ablk * BLK, p.b, s_ib[islot], rows, p.Cb, ctid, NCOPY);
+            }
+        };
+        auto next = [](int v, int mod) { return v + 1 == mod ? 0 : v + 1; };
+        int st_mma = 0, st_fill = NS - 1, ix_fill = NS - 1, ix_fetch = 2 * (NS - 1);   // all < IR = 2 NS
+        if (lo < hi) {
+            cur.seek(s_cum, p.seg, p.n_o, lo);
+            pre = cur;
+            fill = cur;
+            // prologue: index rows of chunks 0 .. 2(NS-1)-1, then the rows of chunks 0 .. NS-2
+            for (int m = 0; m < 2 * (NS - 1); ++m) fetch_indices(lo + m, m);
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+            for (int m = 0; m < NS - 1; ++m) {
+                if (lo + m < hi) copy_chunk(lo + m, m, m);
+                cp_async_commit();
+            }
+        }
+        // Iteration n: [flush a closed tap] - chunk n landed - multiply n - multiply n-1 done? -
+        // refill its stage with chunk n+NS-1 and fetch the index rows of chunk n+2(NS-1).  NS-1 copy
+        // groups before the loop and one per iteration, committed after the iteration's wait: chunk
+        // n (and the index rows fetched NS-1 iterations ago, which this iteration's copies read)
+        // has landed once at most NS-2 groups are pending.
+        bool failed = false;   // this thread's wait ran out; the block leaves the loop together at the barrier
+        for (int chunk = lo; chunk < hi; ++chunk) {
+            const int n = chunk - lo;
+            bool prev_waited = n == 0;
+            if (n > 0 && pending_tap >= 0) {
+                // the previous chunk closed its tap: its sums leave TMEM before this chunk starts a new one
+                alive = wait_multiply_all(n - 1);
+                prev_waited = true;
+                if (!alive) break;
+                tc_fence_after();
+                flush_tap(pending_tap);
+                pending_tap = -1;
+                fresh = true;
+                tc_fence_before();
+            }
+            if (NS == 2) cp_async_wait<0>();
+            else if (NS == 3) cp_async_wait<1>();
+            else cp_async_wait<2>();
+            fence_async_smem();
+            if (__syncthreads_or(failed)) {
+                alive = false;
+                break;
+            }
+            cur.advance(s_cum, p.seg, p.n_o, chunk);
+            if (tid == 0) multiply(st_mma, cur.rows(chunk), (n & 1) ? bar1 : bar0);
+            fresh = false;
+            if (!prev_waited) failed = !wait_multiply_self(n - 1);
+            // the stage of chunk n-1 (for n = 0: the one the prologue left empty) is free
+            if (!failed) {
+                if (chunk + NS - 1 < hi) copy_chunk(chunk + NS - 1, st_fill, ix_fill);
+                fetch_indices(chunk + 2 * (NS - 1), ix_fetch);
+            }
+            cp_async_commit();
+            st_mma = next(st_mma, NS), st_fill = next(st_fill, NS);
+            ix_fill = next(ix_fill, IR), ix_fetch = next(ix_fetch, IR);
+            if ((chunk + 1 == hi) || cur.last_of_tap(chunk)) pending_tap = cur.tap;
+        }
+        if (lo < hi && alive) {
+            alive = wait_multiply_all(hi - 1 - lo) && !__syncthreads_or(failed);
+            tc_fence_after();
+            if (alive && pending_tap >= 0) flush_tap(pending_tap);
+        }
     }
     cp_async_wait<0>();
     tc_fence_before();
@@ -588,10 +708,10 @@ uint32_t pow2_cols(int n) {
 
 // CTAs per SM: bounded by shared memory (227 KiB usable, 1 KiB reserved per
 // CTA), by TMEM (512 columns) and by registers / warp slots.
-int ctas_per_sm(size_t smem, uint32_t ncols, int regs_per_thread) {
+int ctas_per_sm(size_t smem, uint32_t ncols, int regs_per_thread, int threads = 128) {
     int by_smem = (int)((size_t)232448 / (smem + 1024));
     int by_tmem = (int)(512 / ncols);
-    int by_regs = 65536 / (((regs_per_thread * 32 + 255) / 256 * 256) * 4);  // 128-thread CTAs
+    int by_regs = 65536 / (((regs_per_thread * 32 + 255) / 256 * 256) * (threads / 32));
     int occ = std::min(by_smem, std::min(by_tmem, by_regs));
     if (occ > 8) occ = 8;
     return occ < 1 ? 1 : occ;
@@ -714,6 +834,23 @@ int mvmr_tensor(const MvmrArgs &a, cudaStream_t stream) {
     return PCX_OK;
 }
 
+// One instantiation of the VVOR kernel: its shared-memory opt-in, its resident CTAs, its launch.
+template <int NT, int CHR, bool RING>
+int launch_vvor(const VvorTcParams &p, int64_t chunks_upper, size_t smem, size_t static_smem, cudaStream_t stream) {
+    static int granted[64] = {};   // per device
+    static int regs = 0;
+    int dev = 0;
+    PCX_CUDA(cudaGetDevice(&dev));
+    if (int rc = ensure_dynamic_smem(vvor_tc_kernel<NT, CHR, RING>, smem, &granted[dev & 63])) return rc;
+    const int occ = ctas_per_sm(smem + static_smem, p.ncols, kernel_registers(vvor_tc_kernel<NT, CHR, RING>, &regs), NT);
+    const int64_t grid = std::min<int64_t>(chunks_upper, (int64_t)occ * num_sms());
+    prof_begin("vvor_tc_kernel", stream);
+    vvor_tc_kernel<NT, CHR, RING><<<(unsigned)grid, NT, smem, stream>>>(p);
+    prof_end(stream);
+    PCX_LAUNCH_CHECK();
+    return PCX_OK;
+}
+
 int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
     VvorTcParams p;
     p.a = (const uint16_t *)a.a, p.b = (const uint16_t *)a.b, p.a_idx = a.a_idx, p.b_idx = a.b_idx;
@@ -721,42 +858,60 @@ int vvor_tensor(const VvorArgs &a, cudaStream_t stream) {
     p.n_o = (int)a.n_o, p.Ma = a.Ma, p.Cb = a.Cb, p.fmt = a.dtype == PCX_BF16 ? 1 : 0;
     const int row_tiles = (a.Ma + 127) / 128;
     p.ncols = pow2_cols((row_tiles - 1) * a.Cb + (a.Cb + 63) / 64 * 64);  // flushed in blocks of 64 columns
+    const size_t blocks = (size_t)((a.Ma + 63) / 64 + (a.Cb + 63) / 64);
     // one stage = both operand tiles plus their index rows
-    const size_t buf = (size_t)((a.Ma + 63) / 64 + (a.Cb + 63) / 64) * BLK_BYTES + 2 * CH * sizeof(int32_t);
+    // (index rows: two per stage and operand, the ring variant fetches them ahead of the copies)
+    auto stage_bytes = [&](int chr) { return blocks * (size_t)chr * 128 + 4 * (size_t)chr * sizeof(int32_t); };
     const size_t fixed = 1024 + align_up((size_t)(a.n_o + 1) * 4, 16);  // alignment slack, chunk table
-    const size_t static_smem = 128;  // barrier, TMEM address, scan scratch
-    // One stage by default: measured on B200, more resident CTAs hide the gather
-    // latency better than a deeper ring inside fewer CTAs (PCX_VVOR_STAGES raises it).
-    int stages = 1, max_fit = 1;
-    for (int ns = MAX_STAGES; ns >= 1; --ns) {
-        size_t need = fixed + ns * buf + static_smem + 1024;
-        size_t budget = (ns * buf <= 100 * 1024) ? (232448 / 2) : 232448;
-        if (need <= budget) {
+    const size_t static_smem = 160;  // barriers, TMEM address, scan scratch
+    // Measured on B200 (27 taps, 3.2 M triplets over 90 000 rows; ms per call):
+    //  * three and more CTAs fit on an SM (narrow operands): chunks of 128 triplets, one stage, 128
+    //    threads -- more resident CTAs hide the gather latency better than a ring inside fewer CTAs;
+    //  * two fit (192 x 128, 256 x 128, 192 x 96): the same with 256 threads, 0.37 / 0.36 / 0.39
+    //    (ring of 64-triplet chunks in two CTAs 0.43 / 0.39 / 0.45, in one CTA of 512 threads 0.52 / 0.48 / 0.56);
+    //  * one fits (256 x 256: all of tensor memory): chunks of 64 triplets through a ring as deep
+    //    as fits (3 stages), 512 threads, 0.52 (one stage of 128 triplets: 0.63 with 512 threads,
+    //    0.83 with 128).
+    const int by_memory = ctas_per_sm(fixed + stage_bytes(128) + static_smem, p.ncols, 32);
+    int chr = by_memory >= 2 ? 128 : 64;
+    int threads = by_memory >= 3 ? 128 : by_memory == 2 ? 256 : 512;
+    if (const char *e = getenv("PCX_VVOR_CHUNK")) {
+        const int want = atoi(e);
+        if (want == 64 || want == 128) chr = want;
+    }
+    if (const char *e = getenv("PCX_VVOR_THREADS")) {
+        const int want = atoi(e);
+        if (want == 128 || want == 256 || want == 512) threads = want;
+    }
+    const size_t budget = by_memory >= 2 && threads <= 256 ? 232448 / 2 : 232448;   // keep two CTAs per SM where two fit
+    int max_fit = 1;
+    for (int ns = chr == 128 ? 1 : MAX_STAGES; ns >= 1; --ns)
+        if (fixed + ns * stage_bytes(chr) + static_smem + 1024 <= budget) {
             max_fit = ns;
             break;
         }
-    }
+    int stages = chr == 128 ? 1 : max_fit;
     if (const char *e = getenv("PCX_VVOR_STAGES")) {
-        int want = atoi(e);
+        const int want = atoi(e);
         if (want >= 1 && want <= max_fit) stages = want;
     }
     p.stages = stages;
-    size_t smem = fixed + stages * buf;
+    size_t smem = fixed + stages * stage_bytes(chr);
     smem = pad_for_tmem(smem, p.ncols);
     if (smem + static_smem > 232448 - 1024) PCX_FAIL(PCX_E_UNSUPPORTED, "vvor tensor kernel does not fit (smem %zu)", smem);
-    static int granted_vvor[64] = {};   // per device
-    int dev = 0;
-    PCX_CUDA(cudaGetDevice(&dev));
-    if (int rc = ensure_dynamic_smem(vvor_tc_kernel, smem, &granted_vvor[dev & 63])) return rc;
-    static int regs_vvor = 0;
-    const int occ = ctas_per_sm(smem + static_smem, p.ncols, kernel_registers(vvor_tc_kernel, &regs_vvor));
-    int64_t upper = a.T / CH + a.n_o + 1;
-    int64_t grid = std::min<int64_t>(upper, (int64_t)occ * num_sms());
-    prof_begin("vvor_tc_kernel", stream);
-    vvor_tc_kernel<<<(unsigned)grid, 128, smem, stream>>>(p);
-    prof_end(stream);
-    PCX_LAUNCH_CHECK();
-    return PCX_OK;
+    const int64_t upper = a.T / chr + a.n_o + 1;
+    if (chr == 128) {
+        if (threads == 128) return launch_vvor<128, 128, false>(p, upper, smem, static_smem, stream);
+        if (threads == 256) return launch_vvor<256, 128, false>(p, upper, smem, static_smem, stream);
+        return launch_vvor<512, 128, false>(p, upper, smem, static_smem, stream);
+    }
+    if (stages == 1) {
+        if (threads == 128) return launch_vvor<128, 64, false>(p, upper, smem, static_smem, stream);
+        if (threads == 256) return launch_vvor<256, 64, false>(p, upper, smem, static_smem, stream);
+        return launch_vvor<512, 64, false>(p, upper, smem, static_smem, stream);
+    }
+    if (threads <= 256) return launch_vvor<256, 64, true>(p, upper, smem, static_smem, stream);   // the ring wants the warps
+    return launch_vvor<512, 64, true>(p, upper, smem, static_smem, stream);
 }
 
 // Device address of the status word, for kernels of other translation units.

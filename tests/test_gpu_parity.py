@@ -252,6 +252,34 @@ def test_tensor_engine_forward_dgrad_wgrad(dtype, K, C, M):
     assert oso.rel_frobenius(out_cc.float().cpu().numpy(), out.float().cpu().numpy()) < TOL[dtype]
 
 
+@pytest.mark.parametrize("Ma,Cb", [(256, 256), (192, 128), (128, 256), (256, 96), (96, 192)])
+def test_wide_weight_gradient_many_chunks_per_cta(Ma, Cb):
+    """Wide operands run the weight gradient as chunks of 64 triplets through a ring of operand
+    buffers, one or two CTAs per SM: every CTA walks dozens of chunks and crosses several taps,
+    among them empty taps and taps shorter than a chunk."""
+    from pointelligence_b200 import _cabi
+
+    rng = np.random.default_rng(Ma * 7 + Cb)
+    K, n_a, n_b, T = 40, 2500, 3000, 420_000
+    share = rng.random(K) ** 3          # very uneven taps
+    share[[3, 17]] = 0.0                # two empty taps
+    k = np.sort(rng.choice(K, size=T, p=share / share.sum())).astype(np.int32)
+    k = np.concatenate([k, np.full(5, 3, np.int32)])        # a tap of five triplets
+    k.sort()
+    T = len(k)
+    ia, ib = rng.integers(0, n_a, T).astype(np.int32), rng.integers(0, n_b, T).astype(np.int32)
+    a = _t(rng.standard_normal((n_a, Ma)), torch.bfloat16)
+    b = _t(rng.standard_normal((n_b, Cb)), torch.bfloat16)
+    seg = _cabi.seg_offs_from_sorted(_t(k), K)
+    gw = _cabi.vvor(a.view(n_a, 1, Ma), _t(ia), b.view(n_b, 1, Cb), _t(ib), seg, None, K, _cabi.ENGINE_TENSOR)
+    assert _cabi.device_status() == 0
+    an, bn = (t.float().cpu().numpy().astype(np.float64) for t in (a, b))
+    ref = oso.vvor_f64_taps(an, ia, bn, ib, seg.cpu().numpy())        # one fp64 product per tap
+    assert oso.rel_frobenius(gw.float().cpu().numpy().reshape(K, Ma, Cb), ref) < TOL[torch.bfloat16]
+    assert torch.all(gw[17] == 0)
+
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("G,C,M", [(1, 3, 32), (1, 32, 20), (2, 16, 24), (1, 40, 72)])
 def test_odd_shapes_take_the_cuda_core_engine(dtype, G, C, M):
