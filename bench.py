@@ -59,8 +59,15 @@ KERNEL = 3
 METRIC = "pointconv3d_fwd_dgrad_wgrad_throughput"
 UNIT = "Gtriplets/s"
 CPU_CROP_POINTS = 20_000   # sub-scene the CPU arms are timed on (the reference's loops run ~0.1 Mtriplets/s)
-WORKLOAD = ("indoor150k_c64_bf16: PointConv3d fwd+dgrad+wgrad, 150000-point synthetic indoor scene, "
-            "R=5cm, 27 taps, C_in=C_out=64 bf16, fp32 accumulate")
+
+
+def workload_label(points=N_POINTS, channels=CHANNELS):
+    """Name of the convolution workload in the JSON line; the headline is the default (150 000 points, 64 channels)."""
+    return (f"indoor{points // 1000}k_c{channels}_bf16: PointConv3d fwd+dgrad+wgrad, {points}-point synthetic indoor "
+            f"scene, R=5cm, 27 taps, C_in=C_out={channels} bf16, fp32 accumulate")
+
+
+WORKLOAD = workload_label()
 
 
 def bind_to_gpu_numa_node(local_rank):
@@ -562,7 +569,7 @@ def run_ours(args, rank, local_rank, world):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": per_step_ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "points_per_rank": n, "triplets_rank0": T,
+            "config": {"workload": workload_label(args.points, args.channels), "points_per_rank": n, "triplets_rank0": T,
                        "triplets_per_point": T / n, "l2": "flushed between steps (256 MiB write)",
                        "collective": "all-reduce of dW per step" if world > 1 else "none", "numa_rank0": numa,
                        "mvmr_engine": args.engine,
