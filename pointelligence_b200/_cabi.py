@@ -320,11 +320,15 @@ def profile_records():
 #     large clouds (on the residual U-Net of the benchmark: 282 ms per step on the scatter kernel
 #     alone, 203 ms with this rule).
 # Sparse rulebooks over small accumulators and single-tap rulebooks (nothing to keep across taps)
-# stay on the scatter kernel.
+# stay on the scatter kernel.  So do rulebooks that are thin in tap space (fewer than 0.18 triplets
+# per output row and tap): their 128-row tiles are mostly padding.  The 125-tap stem of the benchmark
+# (16.5 triplets per row, 0.13 per row and tap, 16 input channels) takes 1.03 ms on the scatter kernel
+# against 2.56 ms plus its plan; the 27-tap layers of the finest level (0.23) stay planned.
 ENGINE_PLANNED = 3
 _PLANNED_DENSE_RATIO = float(os.environ.get("PCX_PLANNED_DENSE_RATIO", "12"))   # triplets per output row: always planned
 _PLANNED_MIN_RATIO = float(os.environ.get("PCX_PLANNED_MIN_RATIO", "4"))        # ... planned when the accumulator is large
 _PLANNED_MIN_ACC_BYTES = int(os.environ.get("PCX_PLANNED_MIN_ACC_BYTES", str(64 << 20)))
+_PLANNED_MIN_TAP_FILL = float(os.environ.get("PCX_PLANNED_MIN_TAP_FILL", "0.18"))  # triplets per output row and tap
 _PLANNED_ENABLED = os.environ.get("PCX_PLANNED", "1") != "0"
 
 
@@ -332,6 +336,8 @@ def _planned_pays(T, n_out, outw, K):
     if not _PLANNED_ENABLED or K <= 1 or n_out <= 0:
         return False
     ratio = T / n_out
+    if ratio / K < _PLANNED_MIN_TAP_FILL:
+        return False
     return ratio >= _PLANNED_DENSE_RATIO or (ratio >= _PLANNED_MIN_RATIO and n_out * outw * 4 >= _PLANNED_MIN_ACC_BYTES)
 
 

@@ -165,6 +165,7 @@ def test_automatic_engine_takes_the_planned_kernel_for_dense_or_large_layers():
     assert not _cabi._planned_pays(T=133_000, n_out=50_000, outw=256, K=27)      # too sparse
     assert _cabi._planned_pays(T=7_000_000, n_out=1_100_000, outw=32, K=27)
     assert not _cabi._planned_pays(T=1_100_000, n_out=1_100_000, outw=256, K=1)   # a single tap
+    assert not _cabi._planned_pays(T=18_200_000, n_out=1_100_000, outw=32, K=125)  # 0.13 triplets per row and tap: tiles of padding
     with pytest.raises(NotImplementedError):                   # fp32 has no tensor-core engine
         _cabi.mvmr(w.float(), x.float(), tj, ti, tseg, None, 4000, False, engine=_cabi.ENGINE_PLANNED)
 
@@ -223,6 +224,7 @@ def test_symmetric_rulebook_input_gradient_reuses_the_forward_plan(monkeypatch):
 
     dev = torch.device("cuda:0")
     monkeypatch.setattr(_cabi, "_PLANNED_DENSE_RATIO", 0.0)      # every tap-sorted bf16 layer takes the planned engine
+    monkeypatch.setattr(_cabi, "_PLANNED_MIN_TAP_FILL", 0.0)
     pts = torch.from_numpy(indoor_scene(20000, 9)).to(dev)
     n = pts.shape[0]
     smp = torch.zeros(n, dtype=torch.int64, device=dev)

@@ -56,6 +56,7 @@ def test_plan_is_prepared_with_the_indices(monkeypatch):
     from pointelligence_b200.layers.two_phase_conv import ConvOp
 
     monkeypatch.setattr(_cabi, "_PLANNED_DENSE_RATIO", 0.0)     # send every tap-sorted bf16 layer to the planned engine
+    monkeypatch.setattr(_cabi, "_PLANNED_MIN_TAP_FILL", 0.0)
     monkeypatch.setattr(_cabi, "_PLANNED_ENABLED", True)
     pts, x, batch = _toy(c=32)
     conv = PointConv3d(32, 32, kernel_size=3).cuda().to(torch.bfloat16)
