@@ -722,7 +722,7 @@ def run_block_ops(args, local_rank):
 
 
 def backbone_setup(args, rank, world, dev):
-    """Model, inputs and the step function of the backbone workload (configs 4 / 5 of the survey)."""
+    """Model, inputs and the step function of the backbone workload (indoor scenes, or LiDAR sweeps with `--scene lidar`)."""
     import torch
     import torch.nn.functional as F
 
@@ -881,7 +881,7 @@ def backbone_leg(args, rank, local_rank, world, dev, steps):
 
 
 def run_backbone(args, rank, local_rank, world):
-    """Secondary workload (configs 4 / 5 of the survey): one training step of the residual U-Net
+    """Secondary workload: one training step of the residual U-Net
     backbone -- geometry, forward, cross-entropy, backward, all-reduce of the parameter gradients
     (optimizer excluded) -- on 8 synthetic indoor scenes per rank (weak scaling).  One JSON line."""
     import torch
