@@ -252,7 +252,7 @@ def test_tensor_engine_forward_dgrad_wgrad(dtype, K, C, M):
     assert oso.rel_frobenius(out_cc.float().cpu().numpy(), out.float().cpu().numpy()) < TOL[dtype]
 
 
-@pytest.mark.parametrize("Ma,Cb", [(256, 256), (192, 128), (128, 256), (256, 96), (96, 192)])
+@pytest.mark.parametrize("Ma,Cb", [(256, 256), (192, 192), (256, 192), (208, 240), (192, 128), (128, 256), (256, 96), (96, 192)])
 def test_wide_weight_gradient_many_chunks_per_cta(Ma, Cb):
     """Wide operands run the weight gradient as chunks of 64 triplets through a ring of operand
     buffers, one or two CTAs per SM: every CTA walks dozens of chunks and crosses several taps,
